@@ -1,0 +1,69 @@
+# In-tree build of the native library and the Python extension.
+#   make -j            → memfabric_hybrid_b200/lib/libmf_core.so + memfabric_hybrid_b200/_pymf*.so + csrc/test/mf_native_tests
+#   make asan          → address+UB-sanitised host build of the native test binary
+# CUDA sources are compiled for sm_100a only; host code links the static CUDA runtime so the library also loads on a
+# machine without a GPU driver.
+CUDA_HOME ?= /usr/local/cuda
+NVCC      := $(CUDA_HOME)/bin/nvcc
+PYTHON    ?= python
+CXX       ?= g++
+
+PY_INC    := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_paths()['include'])")
+PYB_INC   := $(shell $(PYTHON) -c "import pybind11; print(pybind11.get_include())")
+PY_EXT    := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_config_var('EXT_SUFFIX'))")
+CUTLASS_INC ?= $(shell $(PYTHON) -c "import os, flashinfer; print(os.path.join(os.path.dirname(flashinfer.__file__), 'data', 'cutlass', 'include'))" 2>/dev/null)
+
+BUILD     := build
+OUTDIR    := memfabric_hybrid_b200/lib
+CXXFLAGS  := -std=c++17 -O2 -g -fPIC -Wall -Wextra -Wno-unused-parameter -fvisibility=default -pthread \
+             -fstack-protector-strong -D_FORTIFY_SOURCE=2 -I$(CUDA_HOME)/include -Iinclude -Icsrc
+NVFLAGS   := -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -Iinclude -Icsrc \
+             --expt-relaxed-constexpr -Xptxas -v
+LDFLAGS   := -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lrt -pthread -Wl,-z,relro,-z,now
+
+HOST_SRCS := $(wildcard csrc/util/*.cpp csrc/net/*.cpp csrc/store/*.cpp csrc/group/*.cpp csrc/hybm/*.cpp csrc/api/*.cpp)
+CUDA_SRCS := $(wildcard csrc/kernels/*.cu)
+HOST_OBJS := $(patsubst csrc/%.cpp,$(BUILD)/%.o,$(HOST_SRCS))
+CUDA_OBJS := $(patsubst csrc/%.cu,$(BUILD)/%.cu.o,$(CUDA_SRCS))
+TEST_SRCS := $(wildcard csrc/test/*.cpp)
+
+CORE      := $(OUTDIR)/libmf_core.so
+PYMOD     := memfabric_hybrid_b200/_pymf$(PY_EXT)
+TESTBIN   := csrc/test/mf_native_tests
+
+all: $(CORE) $(PYMOD) $(TESTBIN)
+
+$(BUILD)/%.o: csrc/%.cpp $(wildcard csrc/*/*.h include/mf/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(BUILD)/%.cu.o: csrc/%.cu $(wildcard csrc/*/*.h csrc/kernels/*.cuh include/mf/*.h include/mf/device/*.cuh)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVFLAGS) -c $< -o $@ 2> $@.ptxas.log || (cat $@.ptxas.log; false)
+
+$(CORE): $(HOST_OBJS) $(CUDA_OBJS)
+	@mkdir -p $(OUTDIR)
+	$(CXX) -shared -o $@ $^ $(LDFLAGS)
+
+PY_SRCS   := $(wildcard csrc/python/*.cpp)
+PY_OBJS   := $(patsubst csrc/%.cpp,$(BUILD)/%.py.o,$(PY_SRCS))
+$(BUILD)/%.py.o: csrc/%.cpp $(wildcard csrc/*/*.h include/mf/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -fvisibility=hidden -I$(PY_INC) -I$(PYB_INC) -c $< -o $@
+
+$(PYMOD): $(PY_OBJS) $(CORE)
+	$(CXX) -shared -o $@ $(PY_OBJS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/lib' $(LDFLAGS)
+
+$(TESTBIN): $(TEST_SRCS) $(CORE)
+	$(CXX) $(CXXFLAGS) -o $@ $(TEST_SRCS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' $(LDFLAGS)
+
+ASAN_FLAGS := -fsanitize=address,undefined -fno-omit-frame-pointer -O1
+asan:
+	@mkdir -p $(BUILD)/asan
+	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -DMF_NO_CUDA_KERNELS -o $(BUILD)/asan/mf_native_tests_asan \
+	    $(TEST_SRCS) $(HOST_SRCS) csrc/kernels/mf_kernels_stub.cpp $(LDFLAGS)
+
+clean:
+	rm -rf $(BUILD) $(CORE) $(PYMOD) $(TESTBIN)
+
+.PHONY: all clean asan

@@ -1,0 +1,508 @@
+#include "mf_data_op.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+#include <unistd.h>
+#include <unordered_map>
+
+#include "../kernels/mf_kernels.h"
+#include "../util/mf_log.h"
+#include "../util/mf_tracer.h"
+#include "mf_cuda.h"
+#include "mf_tag_info.h"
+
+namespace mf {
+namespace hybm {
+
+uint32_t DefaultSyncTimeoutMs()
+{
+    static uint32_t v = []() {
+        const char *e = std::getenv("MF_COPY_TIMEOUT_MS");
+        long t = e != nullptr ? std::strtol(e, nullptr, 10) : 0;
+        return (uint32_t)(t > 0 ? t : 30000);
+    }();
+    return v;
+}
+
+int BoundedStreamSync(int device, void *stream, uint32_t timeoutMs)
+{
+    cudaStream_t s = stream != nullptr ? (cudaStream_t)stream : cu::ThreadStream(device);
+    // Fast path: most copies finish within the first few hundred polls.
+    uint64_t deadline = NowNs() + (uint64_t)timeoutMs * 1000000ull;
+    uint32_t spins = 0;
+    while (true) {
+        cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) {
+            return BM_OK;
+        }
+        if (e != cudaErrorNotReady) {
+            MF_ERROR("data op: stream reported " << cu::ErrStr(e));
+            (void)cudaGetLastError();
+            return BM_ERROR;
+        }
+        if (++spins > 2000) {
+            if (NowNs() > deadline) {
+                MF_ERROR("data op: copy did not complete within " << timeoutMs << " ms");
+                return BM_TIMEOUT;
+            }
+            if (spins > 200000) {
+                usleep(50);
+            }
+        }
+    }
+}
+
+// =============================================================================================== kernel engine
+
+namespace {
+
+struct StageSlot {
+    mf_copy_desc_t *host{nullptr};
+    mf_copy_desc_t *dev{nullptr};
+    size_t cap{0};
+    cudaEvent_t ev{nullptr};
+    bool used{false};
+};
+
+struct ThreadCtx {
+    volatile uint32_t *flag{nullptr};  // pinned host word, device-visible under the same address
+    uint32_t *counter{nullptr};        // device word, self-resetting
+    uint32_t seq{0};
+    StageSlot slots[4];
+    int nextSlot{0};
+    std::vector<mf_copy_desc_t> scratch;
+};
+
+class KernelDataOp : public DataOperator {
+public:
+    explicit KernelDataOp(int device) : device_(device) {}
+    uint32_t Type() const override { return OP_KERNEL_LDST; }
+    const char *Name() const override { return "kernel_ldst"; }
+
+    int Initialize() override
+    {
+        MF_CHECK_RET(cu::Available() && device_ >= 0, BM_NOT_SUPPORTED, "kernel engine: no GPU");
+        MF_CUDA_CHECK_RET(cudaSetDevice(device_), BM_ERROR);
+        const char *e = std::getenv("MF_BATCH_SYNC");
+        flagSync_ = !(e != nullptr && std::strcmp(e, "stream") == 0);
+        return BM_OK;
+    }
+
+    bool Supports(CopyDirection dir, const ExtOptions &opt) const override
+    {
+        return dir < DIR_AUTO && opt.srcDeviceVisible && opt.dstDeviceVisible;
+    }
+
+    int DataCopy(const CopyParams &p, CopyDirection dir, const ExtOptions &opt) override
+    {
+        if (!Supports(dir, opt)) {
+            return BM_NOT_SUPPORTED;
+        }
+        cudaStream_t s = opt.stream != nullptr ? (cudaStream_t)opt.stream : cu::ThreadStream(device_);
+        int rc = mf_k_xcopy(p.dest, p.src, p.dataSize, 0, (mf_stream_t)s);
+        if (rc != MF_K_OK) {
+            MF_ERROR("kernel engine: xcopy launch failed");
+            return BM_ERROR;
+        }
+        if (opt.flags & FLAG_ASYNC_COPY) {
+            return BM_OK;
+        }
+        return BoundedStreamSync(device_, s, DefaultSyncTimeoutMs());
+    }
+
+    int BatchDataCopy(const BatchCopyParams &p, CopyDirection dir, const ExtOptions &opt) override
+    {
+        if (!Supports(dir, opt)) {
+            return BM_NOT_SUPPORTED;
+        }
+        ThreadCtx *ctx = Ctx();
+        MF_CHECK_RET(ctx != nullptr, BM_ERROR, "kernel engine: cannot set up the per-thread batch context");
+        cudaStream_t s = opt.stream != nullptr ? (cudaStream_t)opt.stream : cu::ThreadStream(device_);
+        // 1. Coalesce runs that are contiguous on both sides, split anything too long for a 32-bit length.
+        std::vector<mf_copy_desc_t> &d = ctx->scratch;
+        d.clear();
+        constexpr uint64_t kMaxLen = 1ull << 31;
+        uint32_t chunks = 0;
+        auto push = [&](uint64_t src, uint64_t dst, uint64_t len) {
+            while (len > 0) {
+                uint64_t part = std::min(len, kMaxLen);
+                d.push_back(mf_copy_desc_t{src, dst, (uint32_t)part, 0});
+                src += part;
+                dst += part;
+                len -= part;
+            }
+        };
+        uint64_t curS = 0, curD = 0, curL = 0;
+        for (uint32_t i = 0; i < p.batchSize; i++) {
+            uint64_t sa = (uint64_t)p.sources[i], da = (uint64_t)p.destinations[i], len = p.dataSizes[i];
+            if (len == 0) {
+                continue;
+            }
+            if (curL != 0 && sa == curS + curL && da == curD + curL) {
+                curL += len;
+                continue;
+            }
+            if (curL != 0) {
+                push(curS, curD, curL);
+            }
+            curS = sa;
+            curD = da;
+            curL = len;
+        }
+        if (curL != 0) {
+            push(curS, curD, curL);
+        }
+        if (d.empty()) {
+            return BM_OK;
+        }
+        for (auto &e : d) {
+            e.chunkStart = chunks;
+            chunks += (e.len + MF_BATCH_CHUNK_BYTES - 1) / MF_BATCH_CHUNK_BYTES;
+        }
+        const bool sync = !(opt.flags & FLAG_ASYNC_COPY);
+        const bool useFlag = sync && flagSync_ && opt.stream == nullptr;
+        const mf_copy_desc_t *devTable = nullptr;
+        if (d.size() > MF_BATCH_INLINE_MAX) {
+            // 2. Large tables: stage in pinned memory and copy to the device ahead of the kernel, on the same stream.
+            StageSlot &slot = ctx->slots[ctx->nextSlot];
+            ctx->nextSlot = (ctx->nextSlot + 1) % 4;
+            if (slot.used) {
+                cudaEventSynchronize(slot.ev);  // the previous H2D from this slot must have been consumed
+            }
+            if (slot.cap < d.size()) {
+                if (slot.host != nullptr) {
+                    cudaStreamSynchronize(s);
+                    cudaFreeHost(slot.host);
+                    cudaFree(slot.dev);
+                }
+                size_t cap = std::max<size_t>(d.size() * 2, 4096);
+                MF_CUDA_CHECK_RET(cudaHostAlloc((void **)&slot.host, cap * sizeof(mf_copy_desc_t), cudaHostAllocDefault), BM_MALLOC_FAILED);
+                MF_CUDA_CHECK_RET(cudaMalloc((void **)&slot.dev, cap * sizeof(mf_copy_desc_t)), BM_MALLOC_FAILED);
+                slot.cap = cap;
+                if (slot.ev == nullptr) {
+                    MF_CUDA_CHECK_RET(cudaEventCreateWithFlags(&slot.ev, cudaEventDisableTiming), BM_ERROR);
+                }
+            }
+            std::memcpy(slot.host, d.data(), d.size() * sizeof(mf_copy_desc_t));
+            MF_CUDA_CHECK_RET(cudaMemcpyAsync(slot.dev, slot.host, d.size() * sizeof(mf_copy_desc_t), cudaMemcpyHostToDevice, s), BM_ERROR);
+            cudaEventRecord(slot.ev, s);
+            slot.used = true;
+            devTable = slot.dev;
+        }
+        uint32_t seq = ++ctx->seq;
+        int rc = mf_k_batch_xcopy(d.data(), devTable, (uint32_t)d.size(), chunks, useFlag ? ctx->counter : nullptr,
+                                  useFlag ? ctx->flag : nullptr, seq, 0, (mf_stream_t)s);
+        if (rc != MF_K_OK) {
+            MF_ERROR("kernel engine: batch launch failed");
+            return BM_ERROR;
+        }
+        if (!sync) {
+            return BM_OK;
+        }
+        if (useFlag) {
+            // 3. Completion word written by the last CTA; bounded poll, then fall back to the stream for the verdict.
+            uint64_t deadline = NowNs() + (uint64_t)DefaultSyncTimeoutMs() * 1000000ull;
+            uint32_t spins = 0;
+            while (*ctx->flag != seq) {
+                if ((++spins & 0x3ff) == 0 && NowNs() > deadline) {
+                    MF_ERROR("kernel engine: batch completion word not seen in time");
+                    return BM_TIMEOUT;
+                }
+            }
+            return BM_OK;
+        }
+        return BoundedStreamSync(device_, s, DefaultSyncTimeoutMs());
+    }
+
+    int Wait() override { return BoundedStreamSync(device_, nullptr, DefaultSyncTimeoutMs()); }
+
+private:
+    ThreadCtx *Ctx()
+    {
+        thread_local std::unordered_map<const KernelDataOp *, ThreadCtx> ctxs;
+        ThreadCtx &c = ctxs[this];
+        if (c.flag == nullptr) {
+            cudaSetDevice(device_);
+            void *hp = nullptr;
+            if (cudaHostAlloc(&hp, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            std::memset(hp, 0, 64);
+            void *dp = nullptr;
+            if (cudaMalloc(&dp, 64) != cudaSuccess || cudaMemset(dp, 0, 64) != cudaSuccess) {
+                (void)cudaGetLastError();
+                cudaFreeHost(hp);
+                return nullptr;
+            }
+            c.flag = (volatile uint32_t *)hp;
+            c.counter = (uint32_t *)dp;
+        }
+        return &c;
+    }
+
+    int device_;
+    bool flagSync_{true};
+};
+
+// =============================================================================================== copy engine
+
+class CopyEngineDataOp : public DataOperator {
+public:
+    explicit CopyEngineDataOp(int device) : device_(device) {}
+    uint32_t Type() const override { return OP_COPY_ENGINE; }
+    const char *Name() const override { return "copy_engine"; }
+    int Initialize() override
+    {
+        MF_CHECK_RET(cu::Available() && device_ >= 0, BM_NOT_SUPPORTED, "copy engine: no GPU");
+        return BM_OK;
+    }
+    bool Supports(CopyDirection dir, const ExtOptions &) const override { return dir < DIR_AUTO; }
+
+    int DataCopy(const CopyParams &p, CopyDirection, const ExtOptions &opt) override
+    {
+        cudaStream_t s = opt.stream != nullptr ? (cudaStream_t)opt.stream : cu::ThreadStream(device_);
+        MF_CUDA_CHECK_RET(cudaMemcpyAsync(p.dest, p.src, p.dataSize, cudaMemcpyDefault, s), BM_ERROR);
+        if (opt.flags & FLAG_ASYNC_COPY) {
+            return BM_OK;
+        }
+        return BoundedStreamSync(device_, s, DefaultSyncTimeoutMs());
+    }
+
+    int BatchDataCopy(const BatchCopyParams &p, CopyDirection, const ExtOptions &opt) override
+    {
+        cudaStream_t s = opt.stream != nullptr ? (cudaStream_t)opt.stream : cu::ThreadStream(device_);
+        // One cudaMemcpyAsync per coalesced run.
+        uint64_t curS = 0, curD = 0, curL = 0;
+        auto flush = [&]() -> int {
+            if (curL == 0) {
+                return BM_OK;
+            }
+            MF_CUDA_CHECK_RET(cudaMemcpyAsync((void *)curD, (const void *)curS, curL, cudaMemcpyDefault, s), BM_ERROR);
+            return BM_OK;
+        };
+        for (uint32_t i = 0; i < p.batchSize; i++) {
+            uint64_t sa = (uint64_t)p.sources[i], da = (uint64_t)p.destinations[i], len = p.dataSizes[i];
+            if (len == 0) {
+                continue;
+            }
+            if (curL != 0 && sa == curS + curL && da == curD + curL) {
+                curL += len;
+                continue;
+            }
+            int rc = flush();
+            if (rc != BM_OK) {
+                return rc;
+            }
+            curS = sa;
+            curD = da;
+            curL = len;
+        }
+        int rc = flush();
+        if (rc != BM_OK) {
+            return rc;
+        }
+        if (opt.flags & FLAG_ASYNC_COPY) {
+            return BM_OK;
+        }
+        return BoundedStreamSync(device_, s, DefaultSyncTimeoutMs());
+    }
+
+    int Wait() override { return BoundedStreamSync(device_, nullptr, DefaultSyncTimeoutMs()); }
+
+private:
+    int device_;
+};
+
+// =============================================================================================== CPU engine
+
+void ParallelMemcpy(void *dst, const void *src, size_t n)
+{
+    constexpr size_t kParallelMin = 16ull << 20;
+    if (n < kParallelMin) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    unsigned hw = std::thread::hardware_concurrency();
+    unsigned parts = std::min<unsigned>(hw > 1 ? hw / 2 : 1, 4);
+    if (parts <= 1) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    size_t share = (n / parts + 4095) & ~(size_t)4095;
+    std::vector<std::thread> ts;
+    for (unsigned i = 1; i < parts; i++) {
+        size_t off = share * i;
+        if (off >= n) {
+            break;
+        }
+        size_t len = std::min(share, n - off);
+        ts.emplace_back([=]() { std::memcpy((char *)dst + off, (const char *)src + off, len); });
+    }
+    std::memcpy(dst, src, std::min(share, n));
+    for (auto &t : ts) {
+        t.join();
+    }
+}
+
+class CpuDataOp : public DataOperator {
+public:
+    uint32_t Type() const override { return OP_HOST_RDMA | OP_HOST_TCP | OP_HOST_URMA; }
+    const char *Name() const override { return "cpu_memcpy"; }
+    bool Supports(CopyDirection dir, const ExtOptions &) const override
+    {
+        // Host-to-host legs only: the CPU cannot dereference HBM.
+        return dir == DIR_LH_TO_GH || dir == DIR_GH_TO_LH || dir == DIR_GH_TO_GH;
+    }
+    int DataCopy(const CopyParams &p, CopyDirection dir, const ExtOptions &opt) override
+    {
+        if (!Supports(dir, opt)) {
+            return BM_NOT_SUPPORTED;
+        }
+        ParallelMemcpy(p.dest, p.src, p.dataSize);
+        return BM_OK;
+    }
+    int BatchDataCopy(const BatchCopyParams &p, CopyDirection dir, const ExtOptions &opt) override
+    {
+        if (!Supports(dir, opt)) {
+            return BM_NOT_SUPPORTED;
+        }
+        for (uint32_t i = 0; i < p.batchSize; i++) {
+            ParallelMemcpy(p.destinations[i], p.sources[i], p.dataSizes[i]);
+        }
+        return BM_OK;
+    }
+};
+
+}  // namespace
+
+std::shared_ptr<DataOperator> MakeKernelDataOp(int device) { return std::make_shared<KernelDataOp>(device); }
+std::shared_ptr<DataOperator> MakeCopyEngineDataOp(int device) { return std::make_shared<CopyEngineDataOp>(device); }
+std::shared_ptr<DataOperator> MakeCpuDataOp() { return std::make_shared<CpuDataOp>(); }
+
+// =============================================================================================== compose
+
+ComposeDataOp::ComposeDataOp(int device, uint32_t allowedOps, std::shared_ptr<TagInfo> tags)
+    : device_(device), allowed_(allowedOps), tags_(std::move(tags))
+{
+}
+
+int ComposeDataOp::Initialize()
+{
+    engines_.clear();
+    const bool gpu = cu::Available() && device_ >= 0;
+    if (gpu && (allowed_ & (OP_KERNEL_LDST | OP_DEVICE_RDMA | OP_COPY_ENGINE))) {
+        // The two GPU engines back each other up: whichever the caller asked for, a failure of one falls through to
+        // the other (reference: SDMA → DEVICE_RDMA → … fall-through, hybm_compose_data_op.cpp:94-111).
+        auto k = MakeKernelDataOp(device_);
+        if (k->Initialize() == BM_OK) {
+            engines_.push_back(k);
+        }
+        auto c = MakeCopyEngineDataOp(device_);
+        if (c->Initialize() == BM_OK) {
+            engines_.push_back(c);
+        }
+    }
+    engines_.push_back(MakeCpuDataOp());
+    return BM_OK;
+}
+
+static bool HostOnly(CopyDirection d) { return d == DIR_LH_TO_GH || d == DIR_GH_TO_LH || d == DIR_GH_TO_GH; }
+static bool TouchesHost(CopyDirection d)
+{
+    PtrClass s = SrcClassOf(d), t = DstClassOf(d);
+    return s == PC_LOCAL_HOST || s == PC_GLOBAL_HOST || t == PC_LOCAL_HOST || t == PC_GLOBAL_HOST;
+}
+
+std::vector<std::shared_ptr<DataOperator>> ComposeDataOp::Candidates(CopyDirection dir, const ExtOptions &opt, uint64_t bytes, bool batch) const
+{
+    uint32_t mask = allowed_;
+    if (tags_) {
+        mask = tags_->AllowedOps(opt.srcRank, opt.dstRank, allowed_);
+    }
+    // Rank order of preference for this call.
+    std::vector<uint32_t> order;
+    constexpr uint32_t kCpuBits = OP_HOST_RDMA | OP_HOST_TCP | OP_HOST_URMA;
+    constexpr uint64_t kCopyEngineMin = 1ull << 20;
+    if (HostOnly(dir)) {
+        order = {kCpuBits, OP_COPY_ENGINE, OP_KERNEL_LDST};
+    } else if (opt.flags & FLAG_COPY_KERNEL) {
+        order = {OP_KERNEL_LDST, OP_COPY_ENGINE, kCpuBits};
+    } else if (!opt.srcDeviceVisible || !opt.dstDeviceVisible) {
+        order = {OP_COPY_ENGINE, kCpuBits};
+    } else if (TouchesHost(dir) && !batch && bytes >= kCopyEngineMin) {
+        order = {OP_COPY_ENGINE, OP_KERNEL_LDST, kCpuBits};  // big host legs: DMA engines saturate PCIe without SMs
+    } else {
+        order = {OP_KERNEL_LDST, OP_COPY_ENGINE, kCpuBits};
+    }
+    std::vector<std::shared_ptr<DataOperator>> out;
+    for (uint32_t want : order) {
+        for (auto &e : engines_) {
+            uint32_t t = e->Type();
+            bool isCpu = (t & kCpuBits) != 0;
+            // DEVICE_RDMA shares the kernel engine; host engines are always admissible for host-only legs.
+            bool permitted = isCpu ? (HostOnly(dir) || (mask & kCpuBits)) : ((mask & t) || (t == OP_KERNEL_LDST && (mask & OP_DEVICE_RDMA)));
+            if ((t & want) && permitted && e->Supports(dir, opt) && std::find(out.begin(), out.end(), e) == out.end()) {
+                out.push_back(e);
+            }
+        }
+    }
+    return out;
+}
+
+int ComposeDataOp::DataCopy(const CopyParams &p, CopyDirection dir, const ExtOptions &opt)
+{
+    int ret = BM_NOT_SUPPORTED;
+    MF_TRACE_SCOPE(MF_TP(TM_DATAOP, (int)dir), DirectionName(dir), &ret);
+    auto cands = Candidates(dir, opt, p.dataSize, false);
+    for (auto &e : cands) {
+        ret = e->DataCopy(p, dir, opt);
+        if (ret == BM_OK) {
+            return ret;
+        }
+        MF_WARN("data op: engine " << e->Name() << " failed (" << ret << ") for " << DirectionName(dir) << ", trying the next one");
+    }
+    if (cands.empty()) {
+        MF_ERROR("data op: no engine can serve " << DirectionName(dir) << " between ranks " << opt.srcRank << " and " << opt.dstRank);
+    }
+    return ret;
+}
+
+int ComposeDataOp::BatchDataCopy(const BatchCopyParams &p, CopyDirection dir, const ExtOptions &opt)
+{
+    int ret = BM_NOT_SUPPORTED;
+    MF_TRACE_SCOPE(MF_TP(TM_DATAOP, 32 + (int)dir), "BATCH_COPY", &ret);
+    uint64_t bytes = 0;
+    for (uint32_t i = 0; i < p.batchSize; i++) {
+        bytes += p.dataSizes[i];
+    }
+    auto cands = Candidates(dir, opt, bytes, true);
+    for (auto &e : cands) {
+        ret = e->BatchDataCopy(p, dir, opt);
+        if (ret == BM_OK) {
+            return ret;
+        }
+        MF_WARN("data op: engine " << e->Name() << " failed (" << ret << ") for batch " << DirectionName(dir) << ", trying the next one");
+    }
+    if (cands.empty()) {
+        MF_ERROR("data op: no engine can serve batch " << DirectionName(dir));
+    }
+    return ret;
+}
+
+int ComposeDataOp::Wait()
+{
+    int ret = BM_OK;
+    for (auto &e : engines_) {
+        if (e->Type() == OP_KERNEL_LDST) {  // both GPU engines share the calling thread's stream
+            ret = e->Wait();
+            break;
+        }
+    }
+    return ret;
+}
+
+}  // namespace hybm
+}  // namespace mf

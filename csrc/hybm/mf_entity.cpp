@@ -1,0 +1,702 @@
+#include "mf_entity.h"
+
+#include <cstring>
+#include <pthread.h>
+#include <unistd.h>
+
+#include "../util/mf_log.h"
+#include "../util/mf_tracer.h"
+#include "mf_cuda.h"
+#include "mf_fd_channel.h"
+
+namespace mf {
+namespace hybm {
+
+// ---------------------------------------------------------------------------------------------- lifecycle
+
+static std::mutex g_initMu;
+static int g_initCount = 0;
+static int g_device = -1;
+
+static void AtForkChild()
+{
+    // The child owns no threads of the parent: forget the descriptor server and the init count so it can start afresh.
+    FdChannel::Instance().ResetAfterFork();
+    new (&g_initMu) std::mutex();
+    g_initCount = 0;
+    g_device = -1;
+}
+
+int HybmInit(int deviceId, uint64_t /*flags*/)
+{
+    std::lock_guard<std::mutex> g(g_initMu);
+    if (g_initCount > 0) {
+        MF_CHECK_RET(deviceId == g_device, BM_INVALID_PARAM,
+                     "hybm: already initialised with device " << g_device << ", cannot switch to " << deviceId);
+        g_initCount++;
+        return BM_OK;
+    }
+    static bool forkHook = false;
+    if (!forkHook) {
+        pthread_atfork(nullptr, nullptr, AtForkChild);
+        forkHook = true;
+    }
+    if (deviceId >= 0) {
+        MF_CHECK_RET(cu::Available(), BM_NOT_SUPPORTED, "hybm: device " << deviceId << " requested but no CUDA device is visible");
+        MF_CHECK_RET(deviceId < cu::DeviceCount(), BM_INVALID_PARAM, "hybm: device id " << deviceId << " out of range");
+        cu::DeviceCaps caps;
+        MF_CHECK_RET(cu::ProbeDevice(deviceId, &caps) == 0, BM_ERROR, "hybm: cannot probe device " << deviceId);
+        MF_CHECK_RET(caps.vmm && caps.posixFdHandle, BM_NOT_SUPPORTED,
+                     "hybm: device " << deviceId << " lacks virtual memory management or POSIX-fd handle export");
+        MF_CUDA_CHECK_RET(cudaSetDevice(deviceId), BM_ERROR);
+        MF_CUDA_CHECK_RET(cudaFree(nullptr), BM_ERROR);
+        MF_INFO("hybm: device " << deviceId << " sms=" << caps.smCount << " driver=" << caps.driverVersion << " runtime=" << caps.runtimeVersion
+                                << " multicast=" << caps.multicast << " fabric=" << caps.fabricHandle << " numa=" << caps.numaNode);
+    }
+    const char *trace = std::getenv("MF_TRACE_DIR");
+    if (trace != nullptr) {
+        Tracer::Instance().Init(trace);
+    }
+    g_device = deviceId;
+    g_initCount = 1;
+    return BM_OK;
+}
+
+void HybmUninit()
+{
+    std::lock_guard<std::mutex> g(g_initMu);
+    if (g_initCount == 0) {
+        return;
+    }
+    if (--g_initCount == 0) {
+        EntityFactory::Instance().DestroyAll();
+        g_device = -1;
+    }
+}
+
+bool HybmInited()
+{
+    std::lock_guard<std::mutex> g(g_initMu);
+    return g_initCount > 0;
+}
+
+int HybmDevice() { return g_device; }
+
+// ---------------------------------------------------------------------------------------------- entity
+
+MemEntity::MemEntity(uint32_t id, const Options &opt) : id_(id), opt_(opt) {}
+
+MemEntity::~MemEntity()
+{
+    Unmap();
+    UnreserveMemorySpace();
+    if (devMeta_ != nullptr) {
+        cudaFree(devMeta_);
+    }
+    if (devCtx_ != nullptr) {
+        cudaFree(devCtx_);
+    }
+    VaManager::Instance().RemoveEntity(id_);
+}
+
+int MemEntity::Initialize()
+{
+    MF_CHECK_RET(opt_.rankCount > 0 && opt_.rankCount <= RANK_MAX && opt_.rankId < opt_.rankCount, BM_INVALID_PARAM,
+                 "entity: invalid rank " << opt_.rankId << "/" << opt_.rankCount);
+    MF_CHECK_RET(opt_.maxHBMSize % GRANULE == 0 && opt_.maxDRAMSize % GRANULE == 0, BM_INVALID_PARAM,
+                 "entity: pool sizes must be multiples of 2 MiB");
+    tags_ = std::make_shared<TagInfo>();
+    int rc = tags_->Init(opt_.rankId, opt_.tag, opt_.tagOpInfo);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    SegmentOptions so;
+    so.entityId = id_;
+    so.rankId = opt_.rankId;
+    so.rankCount = opt_.rankCount;
+    so.devId = opt_.devId;
+    so.flags = opt_.flags;
+    so.role = opt_.role;
+    if (opt_.scene == SCENE_TRANS) {
+        if (opt_.devId >= 0 && cu::Available()) {
+            so.type = SEG_USER_MEM;
+            user_ = MemSegment::Create(so);
+            MF_CHECK_RET(user_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the user-memory segment");
+        }
+    } else if ((opt_.memType & MEM_TYPE_DEVICE) && opt_.maxHBMSize > 0) {
+        so.type = SEG_DEVICE_VMM;
+        so.windowSize = opt_.deviceVASpace != 0 ? opt_.deviceVASpace : opt_.maxHBMSize;
+        hbm_ = MemSegment::Create(so);
+        MF_CHECK_RET(hbm_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the HBM segment");
+    }
+    if ((opt_.memType & MEM_TYPE_HOST) && opt_.maxDRAMSize > 0) {
+        so.type = SEG_HOST_SHM;
+        so.windowSize = opt_.hostVASpace != 0 ? opt_.hostVASpace : opt_.maxDRAMSize;
+        so.shmFd = opt_.dramShmFd;
+        dram_ = MemSegment::Create(so);
+        MF_CHECK_RET(dram_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the DRAM segment");
+    }
+    if (opt_.bmType == INIT_HOST || opt_.scene != SCENE_SHM) {
+        dataOp_ = std::make_shared<ComposeDataOp>(opt_.devId, opt_.dataOpType, tags_);
+        rc = dataOp_->Initialize();
+        if (rc != BM_OK) {
+            return rc;
+        }
+    } else {
+        // Kernel-initiated entities still get a host data operator: it costs nothing and lets tests stage data.
+        dataOp_ = std::make_shared<ComposeDataOp>(opt_.devId, OP_KERNEL_LDST | OP_COPY_ENGINE, tags_);
+        dataOp_->Initialize();
+    }
+    hostMeta_.entityId = id_;
+    hostMeta_.rankId = opt_.rankId;
+    hostMeta_.rankCount = opt_.rankCount;
+    if (opt_.devId >= 0 && cu::Available()) {
+        MF_CUDA_CHECK_RET(cudaSetDevice(opt_.devId), BM_ERROR);
+        MF_CUDA_CHECK_RET(cudaMalloc((void **)&devMeta_, sizeof(DeviceMeta)), BM_MALLOC_FAILED);
+        MF_CUDA_CHECK_RET(cudaMalloc(&devCtx_, EXTRA_CONTEXT_MAX), BM_MALLOC_FAILED);
+        hostMeta_.extraContextAddr = (uint64_t)devCtx_;
+        rc = UpdateDeviceMeta();
+    }
+    return rc;
+}
+
+int MemEntity::UpdateDeviceMeta()
+{
+    if (devMeta_ == nullptr) {
+        return BM_OK;
+    }
+    MF_CUDA_CHECK_RET(cudaMemcpy(devMeta_, &hostMeta_, sizeof(DeviceMeta), cudaMemcpyHostToDevice), BM_ERROR);
+    return BM_OK;
+}
+
+int MemEntity::ReserveMemorySpace(uint64_t hbmHint, uint64_t dramHint)
+{
+    MF_CHECK_RET(!reserved_, BM_ERROR, "entity: memory space already reserved");
+    uint64_t base = 0;
+    if (hbm_) {
+        int rc = hbm_->ReserveMemorySpace(hbmHint, &base);
+        if (rc != BM_OK) {
+            return rc;
+        }
+        hostMeta_.hbmBase = base;
+        hostMeta_.symmetricSize = hbm_->WindowSize();
+    }
+    if (dram_) {
+        int rc = dram_->ReserveMemorySpace(dramHint, &base);
+        if (rc != BM_OK) {
+            if (hbm_) {
+                hbm_->UnreserveMemorySpace();
+            }
+            return rc;
+        }
+        hostMeta_.dramBase = base;
+        hostMeta_.dramWindowSize = dram_->WindowSize();
+    }
+    reserved_ = true;
+    return UpdateDeviceMeta();
+}
+
+int MemEntity::UnreserveMemorySpace()
+{
+    if (!reserved_) {
+        return BM_OK;
+    }
+    if (hbm_) {
+        hbm_->Unmap();
+        hbm_->UnreserveMemorySpace();
+    }
+    if (dram_) {
+        dram_->Unmap();
+        dram_->UnreserveMemorySpace();
+    }
+    reserved_ = false;
+    return BM_OK;
+}
+
+std::shared_ptr<MemSegment> MemEntity::Segment(uint32_t memType) const
+{
+    if (memType == MEM_TYPE_DEVICE) {
+        return hbm_ ? hbm_ : user_;
+    }
+    return dram_;
+}
+
+uint64_t MemEntity::MemoryPtr(uint32_t memType) const
+{
+    auto s = memType == MEM_TYPE_DEVICE ? hbm_ : dram_;
+    return s ? s->Base() : 0;
+}
+
+uint64_t MemEntity::WindowSize(uint32_t memType) const
+{
+    auto s = memType == MEM_TYPE_DEVICE ? hbm_ : dram_;
+    return s ? s->WindowSize() : 0;
+}
+
+// Slice handles are only unique per segment: bit 1 of the handle's low nibble tags user-registered slices so that the
+// three segments never collide.
+static constexpr uint64_t kUserSliceTag = 1ull << 1;
+
+int MemEntity::AllocLocalMemory(uint64_t size, uint32_t memType, uint32_t flags, uint64_t *sliceHandle)
+{
+    auto seg = memType == MEM_TYPE_DEVICE ? hbm_ : (memType == MEM_TYPE_HOST ? dram_ : nullptr);
+    MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: no segment of memory type " << memType);
+    MF_CHECK_RET(reserved_, BM_NOT_INITIALIZED, "entity: reserve the memory space first");
+    MemSlice s;
+    int rc = seg->AllocLocalMemory(size, flags | (opt_.flags & FLAG_CREATE_WITH_SHM), &s);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    *sliceHandle = s.ToHandle();
+    return BM_OK;
+}
+
+int MemEntity::RegisterLocalMemory(uint64_t addr, uint64_t size, uint32_t /*flags*/, uint64_t *sliceHandle)
+{
+    if (!user_) {
+        SegmentOptions so;
+        so.type = SEG_USER_MEM;
+        so.entityId = id_;
+        so.rankId = opt_.rankId;
+        so.rankCount = opt_.rankCount;
+        so.devId = opt_.devId;
+        user_ = MemSegment::Create(so);
+        MF_CHECK_RET(user_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the user-memory segment");
+    }
+    MemSlice s;
+    int rc = user_->RegisterMemory(addr, size, &s);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    *sliceHandle = s.ToHandle() | kUserSliceTag;
+    return BM_OK;
+}
+
+std::shared_ptr<MemSegment> MemEntity::SegmentOfSlice(uint64_t handle, MemSlice *slice)
+{
+    bool userSlice = (handle & kUserSliceTag) != 0;
+    uint16_t index = 0;
+    uint32_t memType = 0;
+    if (!MemSlice::Decode(handle & ~kUserSliceTag, &index, &memType)) {
+        return nullptr;
+    }
+    std::shared_ptr<MemSegment> seg = userSlice ? user_ : (memType == MEM_TYPE_DEVICE ? hbm_ : dram_);
+    if (!seg || !seg->FindSlice(index, slice)) {
+        return nullptr;
+    }
+    return seg;
+}
+
+int MemEntity::FreeLocalMemory(uint64_t sliceHandle)
+{
+    MemSlice s;
+    auto seg = SegmentOfSlice(sliceHandle, &s);
+    MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: invalid slice handle");
+    return seg->ReleaseSlice(s);
+}
+
+int MemEntity::SliceVa(uint64_t sliceHandle, uint64_t *va, uint64_t *size)
+{
+    MemSlice s;
+    auto seg = SegmentOfSlice(sliceHandle, &s);
+    MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: invalid slice handle");
+    if (va != nullptr) {
+        *va = s.vAddress;
+    }
+    if (size != nullptr) {
+        *size = s.size;
+    }
+    return BM_OK;
+}
+
+int MemEntity::Export(uint64_t sliceHandle, uint32_t flags, ExchangeInfo *out)
+{
+    MF_CHECK_RET(out != nullptr, BM_INVALID_PARAM, "entity: null exchange info");
+    std::memset(out, 0, sizeof(*out));
+    if (sliceHandle == 0 || (flags & FLAG_EXPORT_ENTITY)) {
+        EntityExport e{};
+        e.magic = ENTITY_EXPORT_MAGIC;
+        e.entityId = id_;
+        e.rank = opt_.rankId;
+        e.role = opt_.role;
+        e.devId = opt_.devId;
+        e.pid = (uint32_t)getpid();
+        std::strncpy(e.tag, opt_.tag, sizeof(e.tag) - 1);
+        std::strncpy(e.hostId, HostIdentity().c_str(), sizeof(e.hostId) - 1);
+        std::memcpy(out->desc, &e, sizeof(e));
+        out->descLen = sizeof(e);
+        return BM_OK;
+    }
+    MemSlice s;
+    auto seg = SegmentOfSlice(sliceHandle, &s);
+    MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: invalid slice handle");
+    std::string blob;
+    int rc = seg->Export(s, &blob);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    MF_CHECK_RET(blob.size() <= EXCHANGE_DESC_MAX, BM_ERROR, "entity: export blob too large");
+    std::memcpy(out->desc, blob.data(), blob.size());
+    out->descLen = (uint32_t)blob.size();
+    return BM_OK;
+}
+
+int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresses, uint32_t /*flags*/)
+{
+    MF_CHECK_RET(infos != nullptr && count > 0, BM_INVALID_PARAM, "entity: nothing to import");
+    for (uint32_t i = 0; i < count; i++) {
+        const ExchangeInfo &x = infos[i];
+        MF_CHECK_RET(x.descLen >= 4 && x.descLen <= EXCHANGE_DESC_MAX, BM_INVALID_PARAM, "entity: malformed exchange info #" << i);
+        uint32_t magic;
+        std::memcpy(&magic, x.desc, 4);
+        if (magic == ENTITY_EXPORT_MAGIC) {
+            MF_CHECK_RET(x.descLen == sizeof(EntityExport), BM_INVALID_PARAM, "entity: malformed entity info #" << i);
+            EntityExport e;
+            std::memcpy(&e, x.desc, sizeof(e));
+            e.tag[sizeof(e.tag) - 1] = '\0';
+            int rc = tags_->AddRankTag(e.rank, e.tag);
+            if (rc != BM_OK) {
+                return rc;
+            }
+            if (addresses != nullptr) {
+                addresses[i] = nullptr;
+            }
+            continue;
+        }
+        MF_CHECK_RET(magic == SLICE_EXPORT_MAGIC && x.descLen == sizeof(SliceExport), BM_INVALID_PARAM, "entity: unknown exchange info #" << i);
+        SliceExport e;
+        std::memcpy(&e, x.desc, sizeof(e));
+        std::shared_ptr<MemSegment> seg;
+        if (e.segType == SEG_DEVICE_VMM) {
+            seg = hbm_;
+        } else if (e.segType == SEG_HOST_SHM) {
+            seg = dram_;
+        } else if (e.segType == SEG_USER_MEM) {
+            if (!user_) {
+                uint64_t dummy = 0;
+                // Importing a registered buffer needs a user segment even if this side registered nothing itself.
+                SegmentOptions so;
+                so.type = SEG_USER_MEM;
+                so.entityId = id_;
+                so.rankId = opt_.rankId;
+                so.rankCount = opt_.rankCount;
+                so.devId = opt_.devId;
+                user_ = MemSegment::Create(so);
+                (void)dummy;
+            }
+            seg = user_;
+        }
+        MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: no local segment for imported slice type " << e.segType);
+        std::vector<uint64_t> local;
+        std::string blob((const char *)x.desc, x.descLen);
+        int rc = seg->Import({blob}, &local);
+        if (rc != BM_OK) {
+            return rc;
+        }
+        if (addresses != nullptr) {
+            addresses[i] = local.empty() ? nullptr : (void *)local[0];
+        }
+    }
+    return BM_OK;
+}
+
+int MemEntity::Mmap()
+{
+    std::unique_lock<std::shared_mutex> lk(mapMu_);
+    for (auto &seg : {hbm_, dram_, user_}) {
+        if (seg) {
+            int rc = seg->Mmap();
+            if (rc != BM_OK) {
+                return rc;
+            }
+        }
+    }
+    return BM_OK;
+}
+
+int MemEntity::Unmap()
+{
+    std::unique_lock<std::shared_mutex> lk(mapMu_);
+    for (auto &seg : {hbm_, dram_, user_}) {
+        if (seg) {
+            seg->Unmap();
+        }
+    }
+    return BM_OK;
+}
+
+int MemEntity::RemoveImported(uint32_t rank)
+{
+    std::unique_lock<std::shared_mutex> lk(mapMu_);
+    for (auto &seg : {hbm_, dram_, user_}) {
+        if (seg) {
+            seg->RemoveImported({rank});
+        }
+    }
+    tags_->RemoveRankTag(rank);
+    return BM_OK;
+}
+
+int MemEntity::SetExtraContext(const void *ctx, uint32_t size)
+{
+    MF_CHECK_RET(ctx != nullptr && size > 0 && size <= EXTRA_CONTEXT_MAX, BM_INVALID_PARAM, "entity: extra context must be 1..65536 bytes");
+    MF_CHECK_RET(devCtx_ != nullptr, BM_NOT_SUPPORTED, "entity: no device to hold the extra context");
+    MF_CUDA_CHECK_RET(cudaMemcpy(devCtx_, ctx, size, cudaMemcpyHostToDevice), BM_ERROR);
+    hostMeta_.extraContextSize = size;
+    return UpdateDeviceMeta();
+}
+
+uint32_t MemEntity::ReachTypes(uint32_t rank)
+{
+    if (rank >= opt_.rankCount) {
+        return 0;
+    }
+    uint32_t base = 0;
+    if (hbm_ || user_) {
+        base |= OP_KERNEL_LDST | OP_COPY_ENGINE;
+    }
+    if (dram_) {
+        base |= OP_HOST_RDMA;
+    }
+    return tags_->AllowedOps(opt_.rankId, rank, base & (opt_.dataOpType | OP_HOST_RDMA | OP_KERNEL_LDST | OP_COPY_ENGINE));
+}
+
+bool MemEntity::AddressInEntity(uint64_t addr, uint64_t len)
+{
+    if (hbm_ && hbm_->InWindow(addr, len)) {
+        return true;
+    }
+    if (dram_ && dram_->InWindow(addr, len)) {
+        return true;
+    }
+    AllocatedRange a;
+    return VaManager::Instance().FindAllocated(addr, len, &a) && a.entityId == id_;
+}
+
+uint32_t MemEntity::RankOfAddress(uint64_t addr)
+{
+    if (hbm_ && hbm_->InWindow(addr, 1)) {
+        return hbm_->RankOf(addr);
+    }
+    if (dram_ && dram_->InWindow(addr, 1)) {
+        return dram_->RankOf(addr);
+    }
+    AllocatedRange a;
+    if (VaManager::Instance().FindAllocated(addr, 1, &a) && a.entityId == id_) {
+        return a.ownerRank;
+    }
+    return RANK_MAX;
+}
+
+PtrClass MemEntity::Classify(uint64_t addr, bool *deviceVisible)
+{
+    bool vis = true;
+    PtrClass pc;
+    if (hbm_ && hbm_->InWindow(addr, 1)) {
+        pc = PC_GLOBAL_DEVICE;
+    } else if (dram_ && dram_->InWindow(addr, 1)) {
+        pc = PC_GLOBAL_HOST;
+        vis = dram_->DeviceAccessible() && opt_.devId >= 0 && cu::Available();
+    } else {
+        AllocatedRange a;
+        if (VaManager::Instance().FindAllocated(addr, 1, &a)) {
+            pc = a.memType == MEM_TYPE_DEVICE ? PC_GLOBAL_DEVICE : PC_GLOBAL_HOST;
+            if (pc == PC_GLOBAL_HOST) {
+                vis = false;
+            }
+        } else {
+            pc = PC_LOCAL_HOST;
+            vis = false;
+            if (opt_.devId >= 0 && cu::Available()) {
+                cudaPointerAttributes attr{};
+                if (cudaPointerGetAttributes(&attr, (const void *)addr) == cudaSuccess) {
+                    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
+                        pc = PC_LOCAL_DEVICE;
+                        vis = true;
+                    } else if (attr.type == cudaMemoryTypeHost) {
+                        vis = true;  // pinned or registered: kernels can read it in place
+                    }
+                } else {
+                    (void)cudaGetLastError();
+                }
+            }
+        }
+    }
+    if (deviceVisible != nullptr) {
+        *deviceVisible = vis;
+    }
+    return pc;
+}
+
+int MemEntity::ResolveDirection(uint64_t src, uint64_t dst, CopyDirection *dir, ExtOptions *opt)
+{
+    bool sv = true, dv = true;
+    PtrClass sc = Classify(src, &sv), dc = Classify(dst, &dv);
+    if (*dir == DIR_AUTO) {
+        *dir = DirectionOf(sc, dc);
+        MF_CHECK_RET(*dir != DIR_BUTT, BM_INVALID_PARAM,
+                     "copy: neither " << VaManager::Instance().VaToInfo(src) << " nor " << VaManager::Instance().VaToInfo(dst) << " is in the pool");
+    } else {
+        // The caller's direction decides what the non-pool side is; the pool side(s) must really be in this entity.
+        PtrClass wantS = SrcClassOf(*dir), wantD = DstClassOf(*dir);
+        if (wantS == PC_GLOBAL_HOST || wantS == PC_GLOBAL_DEVICE) {
+            MF_CHECK_RET(sc == wantS, BM_INVALID_PARAM, "copy: source " << VaManager::Instance().VaToInfo(src) << " is not " << DirectionName(*dir) << "'s pool side");
+        } else if (sc == PC_GLOBAL_HOST || sc == PC_GLOBAL_DEVICE) {
+            // A pool address used as a "local" buffer is fine: treat it by what it really is.
+            wantS = sc;
+        }
+        if (wantD == PC_GLOBAL_HOST || wantD == PC_GLOBAL_DEVICE) {
+            MF_CHECK_RET(dc == wantD, BM_INVALID_PARAM, "copy: destination " << VaManager::Instance().VaToInfo(dst) << " is not " << DirectionName(*dir) << "'s pool side");
+        } else if (dc == PC_GLOBAL_HOST || dc == PC_GLOBAL_DEVICE) {
+            wantD = dc;
+        }
+        CopyDirection real = DirectionOf(wantS, wantD);
+        if (real != DIR_BUTT) {
+            *dir = real;
+        }
+    }
+    uint32_t sr = RankOfAddress(src), dr = RankOfAddress(dst);
+    opt->srcRank = sr == RANK_MAX ? opt_.rankId : sr;
+    opt->dstRank = dr == RANK_MAX ? opt_.rankId : dr;
+    opt->srcDeviceVisible = sv;
+    opt->dstDeviceVisible = dv;
+    return BM_OK;
+}
+
+int MemEntity::CopyData(const CopyParams &p, CopyDirection dir, void *stream, uint32_t flags)
+{
+    MF_CHECK_RET(p.src != nullptr && p.dest != nullptr, BM_INVALID_PARAM, "copy: null pointer");
+    MF_CHECK_RET(dataOp_ != nullptr, BM_NOT_SUPPORTED, "copy: this entity has no host data operator");
+    if (p.dataSize == 0) {
+        return BM_OK;
+    }
+    std::shared_lock<std::shared_mutex> lk(mapMu_);
+    ExtOptions opt;
+    opt.stream = stream;
+    opt.flags = flags;
+    int rc = ResolveDirection((uint64_t)p.src, (uint64_t)p.dest, &dir, &opt);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    if (SrcClassOf(dir) >= PC_GLOBAL_HOST) {
+        MF_CHECK_RET(AddressInEntity((uint64_t)p.src, p.dataSize), BM_INVALID_PARAM,
+                     "copy: " << p.dataSize << " bytes from " << VaManager::Instance().VaToInfo((uint64_t)p.src) << " leave the pool");
+    }
+    if (DstClassOf(dir) >= PC_GLOBAL_HOST) {
+        MF_CHECK_RET(AddressInEntity((uint64_t)p.dest, p.dataSize), BM_INVALID_PARAM,
+                     "copy: " << p.dataSize << " bytes to " << VaManager::Instance().VaToInfo((uint64_t)p.dest) << " leave the pool");
+    }
+    return dataOp_->DataCopy(p, dir, opt);
+}
+
+int MemEntity::BatchCopyData(const BatchCopyParams &p, CopyDirection dir, void *stream, uint32_t flags)
+{
+    MF_CHECK_RET(p.sources != nullptr && p.destinations != nullptr && p.dataSizes != nullptr && p.batchSize > 0, BM_INVALID_PARAM,
+                 "batch copy: empty or null parameters");
+    MF_CHECK_RET(dataOp_ != nullptr, BM_NOT_SUPPORTED, "batch copy: this entity has no host data operator");
+    std::shared_lock<std::shared_mutex> lk(mapMu_);
+    ExtOptions opt;
+    opt.stream = stream;
+    opt.flags = flags;
+    // Direction and visibility are taken from the first element (all elements of a batch share a direction); the bounds
+    // of every element's pool side are checked.
+    int rc = ResolveDirection((uint64_t)p.sources[0], (uint64_t)p.destinations[0], &dir, &opt);
+    if (rc != BM_OK) {
+        return rc;
+    }
+    const bool srcPool = SrcClassOf(dir) >= PC_GLOBAL_HOST, dstPool = DstClassOf(dir) >= PC_GLOBAL_HOST;
+    for (uint32_t i = 0; i < p.batchSize; i++) {
+        MF_CHECK_RET(p.sources[i] != nullptr && p.destinations[i] != nullptr, BM_INVALID_PARAM, "batch copy: null pointer at #" << i);
+        if (srcPool) {
+            MF_CHECK_RET(AddressInEntity((uint64_t)p.sources[i], p.dataSizes[i]), BM_INVALID_PARAM, "batch copy: source #" << i << " leaves the pool");
+        }
+        if (dstPool) {
+            MF_CHECK_RET(AddressInEntity((uint64_t)p.destinations[i], p.dataSizes[i]), BM_INVALID_PARAM,
+                         "batch copy: destination #" << i << " leaves the pool");
+        }
+    }
+    return dataOp_->BatchDataCopy(p, dir, opt);
+}
+
+int MemEntity::Wait()
+{
+    MF_CHECK_RET(dataOp_ != nullptr, BM_NOT_SUPPORTED, "wait: this entity has no host data operator");
+    if (opt_.devId < 0 || !cu::Available()) {
+        return BM_OK;
+    }
+    return dataOp_->Wait();
+}
+
+// ---------------------------------------------------------------------------------------------- factory
+
+EntityFactory &EntityFactory::Instance()
+{
+    static EntityFactory *f = new EntityFactory();
+    return *f;
+}
+
+std::shared_ptr<MemEntity> EntityFactory::Create(uint32_t id, const Options &opt, int *rc)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    if (id >= ENTITY_MAX || entities_.count(id)) {
+        MF_ERROR("entity factory: id " << id << " is invalid or already in use");
+        if (rc != nullptr) {
+            *rc = BM_INVALID_PARAM;
+        }
+        return nullptr;
+    }
+    auto e = std::make_shared<MemEntity>(id, opt);
+    int r = e->Initialize();
+    if (rc != nullptr) {
+        *rc = r;
+    }
+    if (r != BM_OK) {
+        return nullptr;
+    }
+    entities_[id] = e;
+    return e;
+}
+
+std::shared_ptr<MemEntity> EntityFactory::Find(uint32_t id)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = entities_.find(id);
+    return it == entities_.end() ? nullptr : it->second;
+}
+
+std::shared_ptr<MemEntity> EntityFactory::FindByPtr(const void *p)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto &kv : entities_) {
+        if (kv.second.get() == p) {
+            return kv.second;
+        }
+    }
+    return nullptr;
+}
+
+void EntityFactory::Destroy(uint32_t id)
+{
+    std::shared_ptr<MemEntity> e;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = entities_.find(id);
+        if (it == entities_.end()) {
+            return;
+        }
+        e = it->second;
+        entities_.erase(it);
+    }
+}
+
+void EntityFactory::DestroyAll()
+{
+    std::map<uint32_t, std::shared_ptr<MemEntity>> all;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        all.swap(entities_);
+    }
+}
+
+}  // namespace hybm
+}  // namespace mf

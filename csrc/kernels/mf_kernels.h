@@ -1,0 +1,54 @@
+// Host-callable launchers of the library's CUDA kernels (C linkage, raw pointers and a cudaStream_t). Every launcher
+// returns 0 on success or a negative code; nothing here synchronises unless stated.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *mf_stream_t;
+
+enum { MF_K_OK = 0, MF_K_INVALID = -2, MF_K_LAUNCH_FAILED = -1, MF_K_TIMEOUT = -7, MF_K_TOO_LARGE = -3 };
+
+// ------------------------------------------------------------------------------------------------ xcopy (K1 / K2)
+
+// Single copy of n bytes between any two device-visible addresses (local HBM, peer HBM over NVLink, pinned host).
+// ctas 0 = pick from the size.
+int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_stream_t stream);
+
+typedef struct {
+    uint64_t src;
+    uint64_t dst;
+    uint32_t len;         // bytes, < 4 GiB (the host splits longer copies)
+    uint32_t chunkStart;  // index of this descriptor's first chunk in the launch-wide chunk numbering
+} mf_copy_desc_t;
+
+enum { MF_BATCH_INLINE_MAX = 168, MF_BATCH_CHUNK_BYTES = 32768 };
+
+// Batch of `count` independent copies in ONE launch. Descriptors must have chunkStart filled (prefix sum of
+// ceil(len / MF_BATCH_CHUNK_BYTES)); totalChunks is the grand total. count <= MF_BATCH_INLINE_MAX travels in the kernel
+// parameters; larger batches must pass `descsDev`, a device-readable copy of the table. `doneCounter` (device, zero
+// before first use, self-resetting) and `hostFlag` (pinned host word, may be NULL) implement completion signalling:
+// the last CTA stores `flagValue` to *hostFlag with system-scope release semantics.
+int mf_k_batch_xcopy(const mf_copy_desc_t *descs, const mf_copy_desc_t *descsDev, uint32_t count, uint32_t totalChunks,
+                     uint32_t *doneCounter, volatile uint32_t *hostFlag, uint32_t flagValue, int ctas, mf_stream_t stream);
+
+// ------------------------------------------------------------------------------------------------ test support (K7)
+
+// dst[i] = hash(seed, i) for i in [0, n) bytes; deterministic on host and device (see mf_k_pattern_byte_host).
+int mf_k_fill_pattern(void *dst, size_t n, uint64_t seed, mf_stream_t stream);
+// Counts bytes where buf[i] != hash(seed, i) into *mismatch (device-visible uint64, zeroed by the call).
+int mf_k_check_pattern(const void *buf, size_t n, uint64_t seed, unsigned long long *mismatch, mf_stream_t stream);
+// 64-bit order-independent checksum (sum of FNV-mixed 8-byte words, tail bytes zero-padded) into *out.
+int mf_k_checksum(const void *buf, size_t n, unsigned long long *out, mf_stream_t stream);
+unsigned char mf_k_pattern_byte_host(uint64_t seed, uint64_t index);
+unsigned long long mf_k_checksum_host(const void *buf, size_t n);
+
+// SM count of the current device (cached per device), 0 without a GPU.
+int mf_k_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif

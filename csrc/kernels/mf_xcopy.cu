@@ -1,0 +1,310 @@
+// xcopy kernels: the data plane for every device-visible leg of a copy.
+//
+// mf_xcopy_kernel        one contiguous copy, any alignment. Contract of the reference's hybm_copy_kernel
+//                        (src/hybm/csrc/copy_extend/hybm_copy_kernel.cpp:44-83): split the byte range over the grid in
+//                        aligned shares and move each share load→store; bit-exact result.
+// mf_batch_xcopy_kernel  N independent {src,dst,len} copies in one launch plus a completion word. Contract of
+//                        hybm_batch_copy_kernel and its parameter-slot protocol (hybm_copy_kernel.cpp:85-124,
+//                        src/hybm/csrc/data_operation/host/hybm_data_op_sdma.cpp:504-543). Differences by design:
+//                        work is balanced by BYTES (fixed-size chunks found by binary search over a prefix table)
+//                        rather than by descriptor index, small tables ride in the kernel parameters, and completion is
+//                        one counter + one system-scope release store instead of a chain of blocks spinning on each other
+//                        (no device-side wait exists in this kernel, so nothing can hang).
+// Blackwell mapping: 16-byte streaming loads with L1 bypass, 8 loads in flight per thread before the first store,
+// 512-thread CTAs at two per SM (128 KiB in flight per SM — enough to cover HBM3e and NVLink latency), persistent grid.
+#include <cuda_runtime.h>
+
+#include "mf_copy_device.cuh"
+#include "mf_kernels.h"
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kUnroll = 8;
+
+__global__ void __launch_bounds__(kThreads, 2)
+mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n, size_t tileBytes)
+{
+    // Tile 0 is stretched by `lead` bytes so that every later tile starts on a 16-byte boundary of dst.
+    const size_t lead = (16 - ((uintptr_t)dst & 15)) & 15;
+    const size_t body = n > lead ? n - lead : 0;
+    const size_t ntiles = body == 0 ? 1 : (body + tileBytes - 1) / tileBytes;
+    for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        size_t begin = t == 0 ? 0 : lead + t * tileBytes;
+        size_t end = lead + (t + 1) * tileBytes;
+        if (end > n) {
+            end = n;
+        }
+        mf::dev::CopySpan<kUnroll>(dst + begin, src + begin, end - begin, threadIdx.x, kThreads);
+    }
+}
+
+struct BatchInline {
+    uint32_t count;
+    uint32_t totalChunks;
+    uint32_t flagValue;
+    uint32_t pad;
+    uint32_t *doneCounter;
+    volatile uint32_t *hostFlag;
+    mf_copy_desc_t d[MF_BATCH_INLINE_MAX];
+};
+static_assert(sizeof(BatchInline) <= 4096 + 32, "inline batch must fit the classic kernel parameter space");
+
+__device__ __forceinline__ void BatchBody(const mf_copy_desc_t *__restrict__ d, uint32_t count, uint32_t totalChunks)
+{
+    for (uint32_t c = blockIdx.x; c < totalChunks; c += gridDim.x) {
+        // Last descriptor whose chunkStart <= c. All threads search the same value: uniform, cache-resident accesses.
+        uint32_t lo = 0, hi = count;
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (d[mid].chunkStart <= c) {
+                lo = mid;
+            } else {
+                hi = mid;
+            }
+        }
+        const uint64_t off = (uint64_t)(c - d[lo].chunkStart) * MF_BATCH_CHUNK_BYTES;
+        uint64_t len = d[lo].len - off;
+        if (len > MF_BATCH_CHUNK_BYTES) {
+            len = MF_BATCH_CHUNK_BYTES;
+        }
+        mf::dev::CopySpan<4>((unsigned char *)(d[lo].dst + off), (const unsigned char *)(d[lo].src + off), len, threadIdx.x, kThreads);
+    }
+}
+
+__device__ __forceinline__ void BatchSignal(uint32_t *doneCounter, volatile uint32_t *hostFlag, uint32_t flagValue)
+{
+    if (doneCounter == nullptr) {
+        return;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();  // this CTA's copies are visible system-wide before it is counted
+        unsigned prev = atomicAdd(doneCounter, 1u);
+        if (prev == gridDim.x - 1) {
+            *doneCounter = 0;  // self-reset for the next launch that uses this slot
+            __threadfence_system();
+            if (hostFlag != nullptr) {
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hostFlag), "r"(flagValue) : "memory");
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 2) mf_batch_xcopy_inline_kernel(const __grid_constant__ BatchInline p)
+{
+    BatchBody(p.d, p.count, p.totalChunks);
+    BatchSignal(p.doneCounter, p.hostFlag, p.flagValue);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+mf_batch_xcopy_table_kernel(const mf_copy_desc_t *__restrict__ d, uint32_t count, uint32_t totalChunks, uint32_t *doneCounter,
+                            volatile uint32_t *hostFlag, uint32_t flagValue)
+{
+    BatchBody(d, count, totalChunks);
+    BatchSignal(doneCounter, hostFlag, flagValue);
+}
+
+// ---------------------------------------------------------------------------------------------- test support
+
+__host__ __device__ __forceinline__ uint64_t Mix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__host__ __device__ __forceinline__ unsigned char PatternByte(uint64_t seed, uint64_t index)
+{
+    uint64_t w = Mix64(seed ^ (index >> 3));
+    return (unsigned char)(w >> ((index & 7) * 8));
+}
+
+__global__ void mf_fill_pattern_kernel(unsigned char *dst, size_t n, uint64_t seed)
+{
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = PatternByte(seed, i);
+    }
+}
+
+__global__ void mf_check_pattern_kernel(const unsigned char *buf, size_t n, uint64_t seed, unsigned long long *mismatch)
+{
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    unsigned long long bad = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        bad += buf[i] != PatternByte(seed, i);
+    }
+    if (bad) {
+        atomicAdd(mismatch, bad);
+    }
+}
+
+__global__ void mf_checksum_kernel(const unsigned char *buf, size_t n, unsigned long long *out)
+{
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t words = (n + 7) / 8;
+    unsigned long long acc = 0;
+    for (size_t w = (size_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += stride) {
+        uint64_t v = 0;
+        size_t base = w * 8;
+        for (int b = 0; b < 8 && base + b < n; b++) {
+            v |= (uint64_t)buf[base + b] << (8 * b);
+        }
+        acc += Mix64(v ^ (uint64_t)w);
+    }
+    if (acc) {
+        atomicAdd(out, acc);
+    }
+}
+
+int SmCount()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int LaunchResult()
+{
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MF_K_OK : MF_K_LAUNCH_FAILED;
+}
+
+}  // namespace
+
+extern "C" int mf_k_sm_count(void) { return SmCount(); }
+
+extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_stream_t stream)
+{
+    if (n == 0) {
+        return MF_K_OK;
+    }
+    if (dst == nullptr || src == nullptr) {
+        return MF_K_INVALID;
+    }
+    const int sms = SmCount();
+    if (sms <= 0) {
+        return MF_K_LAUNCH_FAILED;
+    }
+    const size_t maxCtas = (size_t)sms * 2;
+    // Tile = what one CTA moves per loop trip. Large copies use 64 KiB (8 × 16 B per thread); mid-size copies shrink the
+    // tile so that every SM gets work; 8 KiB is the floor (one 16-byte vector per thread).
+    size_t tile = 64 * 1024;
+    while (tile > 8 * 1024 && n / tile < maxCtas) {
+        tile >>= 1;
+    }
+    size_t ntiles = (n + tile - 1) / tile;
+    size_t grid = ctas > 0 ? (size_t)ctas : (ntiles < maxCtas ? ntiles : maxCtas);
+    mf_xcopy_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>((unsigned char *)dst, (const unsigned char *)src, n, tile);
+    return LaunchResult();
+}
+
+extern "C" int mf_k_batch_xcopy(const mf_copy_desc_t *descs, const mf_copy_desc_t *descsDev, uint32_t count, uint32_t totalChunks,
+                                uint32_t *doneCounter, volatile uint32_t *hostFlag, uint32_t flagValue, int ctas, mf_stream_t stream)
+{
+    if (count == 0 || totalChunks == 0) {
+        return MF_K_OK;
+    }
+    const int sms = SmCount();
+    if (sms <= 0) {
+        return MF_K_LAUNCH_FAILED;
+    }
+    unsigned maxCtas = (unsigned)sms * 2;
+    unsigned grid = ctas > 0 ? (unsigned)ctas : (totalChunks < maxCtas ? totalChunks : maxCtas);
+    if (count <= MF_BATCH_INLINE_MAX && descs != nullptr) {
+        BatchInline p;
+        p.count = count;
+        p.totalChunks = totalChunks;
+        p.flagValue = flagValue;
+        p.pad = 0;
+        p.doneCounter = doneCounter;
+        p.hostFlag = hostFlag;
+        for (uint32_t i = 0; i < count; i++) {
+            p.d[i] = descs[i];
+        }
+        mf_batch_xcopy_inline_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
+        return LaunchResult();
+    }
+    if (descsDev == nullptr) {
+        return MF_K_INVALID;
+    }
+    mf_batch_xcopy_table_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(descsDev, count, totalChunks, doneCounter, hostFlag, flagValue);
+    return LaunchResult();
+}
+
+extern "C" int mf_k_fill_pattern(void *dst, size_t n, uint64_t seed, mf_stream_t stream)
+{
+    if (n == 0) {
+        return MF_K_OK;
+    }
+    size_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) {
+        blocks = 148 * 16;
+    }
+    mf_fill_pattern_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((unsigned char *)dst, n, seed);
+    return LaunchResult();
+}
+
+extern "C" int mf_k_check_pattern(const void *buf, size_t n, uint64_t seed, unsigned long long *mismatch, mf_stream_t stream)
+{
+    if (cudaMemsetAsync(mismatch, 0, sizeof(unsigned long long), (cudaStream_t)stream) != cudaSuccess) {
+        return LaunchResult();
+    }
+    if (n == 0) {
+        return MF_K_OK;
+    }
+    size_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) {
+        blocks = 148 * 16;
+    }
+    mf_check_pattern_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const unsigned char *)buf, n, seed, mismatch);
+    return LaunchResult();
+}
+
+extern "C" int mf_k_checksum(const void *buf, size_t n, unsigned long long *out, mf_stream_t stream)
+{
+    if (cudaMemsetAsync(out, 0, sizeof(unsigned long long), (cudaStream_t)stream) != cudaSuccess) {
+        return LaunchResult();
+    }
+    if (n == 0) {
+        return MF_K_OK;
+    }
+    size_t blocks = ((n + 7) / 8 + 255) / 256;
+    if (blocks > 148 * 16) {
+        blocks = 148 * 16;
+    }
+    mf_checksum_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const unsigned char *)buf, n, out);
+    return LaunchResult();
+}
+
+extern "C" unsigned char mf_k_pattern_byte_host(uint64_t seed, uint64_t index) { return PatternByte(seed, index); }
+
+extern "C" unsigned long long mf_k_checksum_host(const void *buf, size_t n)
+{
+    const unsigned char *p = (const unsigned char *)buf;
+    size_t words = (n + 7) / 8;
+    unsigned long long acc = 0;
+    for (size_t w = 0; w < words; w++) {
+        uint64_t v = 0;
+        size_t base = w * 8;
+        for (int b = 0; b < 8 && base + b < n; b++) {
+            v |= (uint64_t)p[base + b] << (8 * b);
+        }
+        acc += Mix64(v ^ (uint64_t)w);
+    }
+    return acc;
+}

@@ -1,0 +1,797 @@
+#include "mf_rpc.h"
+
+#include <arpa/inet.h>
+#include <cerrno>
+#include <cstring>
+#include <fcntl.h>
+#include <ifaddrs.h>
+#include <netdb.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <sys/epoll.h>
+#include <sys/eventfd.h>
+#include <sys/socket.h>
+#include <unistd.h>
+#include <vector>
+
+#include "../util/mf_log.h"
+
+namespace mf {
+namespace net {
+
+// ---------------------------------------------------------------------------------------------- URL / address helpers
+
+bool ParseUrl(const std::string &urlIn, Endpoint *out)
+{
+    std::string url = urlIn;
+    bool v6 = false;
+    if (url.rfind("tcp6://", 0) == 0) {
+        url = url.substr(7);
+        v6 = true;
+    } else if (url.rfind("tcp://", 0) == 0) {
+        url = url.substr(6);
+    }
+    if (url.empty()) {
+        return false;
+    }
+    std::string host, port;
+    if (url[0] == '[') {
+        size_t rb = url.find(']');
+        if (rb == std::string::npos || rb + 1 >= url.size() || url[rb + 1] != ':') {
+            return false;
+        }
+        host = url.substr(1, rb - 1);
+        port = url.substr(rb + 2);
+        v6 = true;
+    } else {
+        size_t c = url.rfind(':');
+        if (c == std::string::npos || c == 0) {
+            return false;
+        }
+        host = url.substr(0, c);
+        port = url.substr(c + 1);
+        if (host.find(':') != std::string::npos) {
+            v6 = true;  // bare IPv6 literal followed by :port
+        }
+    }
+    if (host.empty() || port.empty() || port.size() > 5) {
+        return false;
+    }
+    for (char ch : port) {
+        if (ch < '0' || ch > '9') {
+            return false;
+        }
+    }
+    long p = std::strtol(port.c_str(), nullptr, 10);
+    if (p <= 0 || p > 65535) {
+        return false;
+    }
+    // Validate literals early so a typo fails at parse time rather than at connect time.
+    unsigned char buf[16];
+    if (v6) {
+        if (inet_pton(AF_INET6, host.c_str(), buf) != 1) {
+            return false;
+        }
+    } else if (std::isdigit((unsigned char)host[0])) {
+        if (inet_pton(AF_INET, host.c_str(), buf) != 1) {
+            return false;
+        }
+    }
+    out->host = host;
+    out->port = (uint16_t)p;
+    out->v6 = v6;
+    return true;
+}
+
+static int Resolve(const Endpoint &ep, sockaddr_storage *ss, socklen_t *len, bool passive)
+{
+    addrinfo hints{};
+    hints.ai_family = ep.v6 ? AF_INET6 : AF_UNSPEC;
+    hints.ai_socktype = SOCK_STREAM;
+    hints.ai_flags = AI_NUMERICSERV | (passive ? AI_PASSIVE : 0);
+    addrinfo *res = nullptr;
+    std::string port = std::to_string(ep.port);
+    int rc = getaddrinfo(ep.host.c_str(), port.c_str(), &hints, &res);
+    if (rc != 0 || res == nullptr) {
+        return -1;
+    }
+    std::memcpy(ss, res->ai_addr, res->ai_addrlen);
+    *len = res->ai_addrlen;
+    freeaddrinfo(res);
+    return 0;
+}
+
+std::string LocalIpToward(const Endpoint &target)
+{
+    sockaddr_storage ss{};
+    socklen_t len = 0;
+    if (Resolve(target, &ss, &len, false) != 0) {
+        return "";
+    }
+    int fd = ::socket(ss.ss_family, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+    if (fd < 0) {
+        return "";
+    }
+    std::string out;
+    if (::connect(fd, (sockaddr *)&ss, len) == 0) {
+        sockaddr_storage me{};
+        socklen_t ml = sizeof(me);
+        if (getsockname(fd, (sockaddr *)&me, &ml) == 0) {
+            char buf[INET6_ADDRSTRLEN] = {0};
+            if (me.ss_family == AF_INET) {
+                inet_ntop(AF_INET, &((sockaddr_in *)&me)->sin_addr, buf, sizeof(buf));
+            } else {
+                inet_ntop(AF_INET6, &((sockaddr_in6 *)&me)->sin6_addr, buf, sizeof(buf));
+            }
+            out = buf;
+        }
+    }
+    ::close(fd);
+    return out;
+}
+
+std::vector<std::string> LocalIpv4List()
+{
+    std::vector<std::string> out;
+    ifaddrs *ifs = nullptr;
+    if (getifaddrs(&ifs) != 0) {
+        return out;
+    }
+    for (ifaddrs *p = ifs; p != nullptr; p = p->ifa_next) {
+        if (p->ifa_addr == nullptr || p->ifa_addr->sa_family != AF_INET) {
+            continue;
+        }
+        char buf[INET_ADDRSTRLEN] = {0};
+        inet_ntop(AF_INET, &((sockaddr_in *)p->ifa_addr)->sin_addr, buf, sizeof(buf));
+        if (std::strncmp(buf, "127.", 4) != 0) {
+            out.emplace_back(buf);
+        }
+    }
+    freeifaddrs(ifs);
+    return out;
+}
+
+static void SetNonBlock(int fd)
+{
+    int fl = fcntl(fd, F_GETFL, 0);
+    fcntl(fd, F_SETFL, fl | O_NONBLOCK);
+}
+
+static void SetNoDelay(int fd)
+{
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+}
+
+static std::string Encode(const Frame &f)
+{
+    WireHeader h{kWireMagic, f.type, f.result, (uint32_t)f.body.size(), f.seq};
+    std::string out;
+    out.resize(sizeof(h) + f.body.size());
+    std::memcpy(&out[0], &h, sizeof(h));
+    if (!f.body.empty()) {
+        std::memcpy(&out[sizeof(h)], f.body.data(), f.body.size());
+    }
+    return out;
+}
+
+// ---------------------------------------------------------------------------------------------- server
+
+struct RpcServer::Conn {
+    int fd{-1};
+    LinkId id{0};
+    bool hello{false};
+    bool dead{false};
+    std::string in;
+    std::deque<std::string> out;  // guarded by RpcServer::mu_
+    size_t outOff{0};
+    bool wantWrite{false};
+};
+
+RpcServer::RpcServer() = default;
+RpcServer::~RpcServer() { Stop(); }
+
+void RpcServer::SetHandlers(MsgHandler onMsg, LinkUpHandler onUp, LinkDownHandler onDown)
+{
+    onMsg_ = std::move(onMsg);
+    onUp_ = std::move(onUp);
+    onDown_ = std::move(onDown);
+}
+
+int RpcServer::Start(const Endpoint &ep)
+{
+    if (running_.load()) {
+        return 0;
+    }
+    sockaddr_storage ss{};
+    socklen_t len = 0;
+    if (Resolve(ep, &ss, &len, true) != 0) {
+        MF_ERROR("rpc server: cannot resolve " << ep.host);
+        return -EINVAL;
+    }
+    listenFd_ = ::socket(ss.ss_family, SOCK_STREAM | SOCK_CLOEXEC, 0);
+    if (listenFd_ < 0) {
+        return -errno;
+    }
+    int one = 1;
+    setsockopt(listenFd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+    if (::bind(listenFd_, (sockaddr *)&ss, len) != 0) {
+        int e = errno;
+        ::close(listenFd_);
+        listenFd_ = -1;
+        return -e;
+    }
+    if (::listen(listenFd_, 512) != 0) {
+        int e = errno;
+        ::close(listenFd_);
+        listenFd_ = -1;
+        return -e;
+    }
+    sockaddr_storage me{};
+    socklen_t ml = sizeof(me);
+    getsockname(listenFd_, (sockaddr *)&me, &ml);
+    port_ = ntohs(me.ss_family == AF_INET ? ((sockaddr_in *)&me)->sin_port : ((sockaddr_in6 *)&me)->sin6_port);
+    SetNonBlock(listenFd_);
+    epfd_ = epoll_create1(EPOLL_CLOEXEC);
+    wakeFd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+    epoll_event ev{};
+    ev.events = EPOLLIN;
+    ev.data.fd = listenFd_;
+    epoll_ctl(epfd_, EPOLL_CTL_ADD, listenFd_, &ev);
+    ev.data.fd = wakeFd_;
+    epoll_ctl(epfd_, EPOLL_CTL_ADD, wakeFd_, &ev);
+    running_.store(true);
+    io_ = std::thread([this]() { Loop(); });
+    return 0;
+}
+
+void RpcServer::Stop()
+{
+    if (!running_.exchange(false)) {
+        return;
+    }
+    Wake();
+    if (io_.joinable()) {
+        io_.join();
+    }
+    std::vector<std::shared_ptr<Conn>> all;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        for (auto &kv : conns_) {
+            all.push_back(kv.second);
+        }
+        conns_.clear();
+        byFd_.clear();
+    }
+    for (auto &c : all) {
+        ::close(c->fd);
+    }
+    ::close(listenFd_);
+    ::close(epfd_);
+    ::close(wakeFd_);
+    listenFd_ = epfd_ = wakeFd_ = -1;
+}
+
+void RpcServer::Wake()
+{
+    uint64_t one = 1;
+    if (wakeFd_ >= 0) {
+        ssize_t r = ::write(wakeFd_, &one, sizeof(one));
+        (void)r;
+    }
+}
+
+size_t RpcServer::LinkCount()
+{
+    std::lock_guard<std::mutex> g(mu_);
+    return conns_.size();
+}
+
+int RpcServer::Send(LinkId link, const Frame &f)
+{
+    std::string bytes = Encode(f);
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = conns_.find(link);
+    if (it == conns_.end() || it->second->dead) {
+        return -1;
+    }
+    Conn &c = *it->second;
+    size_t off = 0;
+    if (c.out.empty()) {
+        // Fast path: nothing queued, try to push the bytes out right now.
+        while (off < bytes.size()) {
+            ssize_t n = ::send(c.fd, bytes.data() + off, bytes.size() - off, MSG_NOSIGNAL | MSG_DONTWAIT);
+            if (n > 0) {
+                off += (size_t)n;
+            } else if (n < 0 && errno == EINTR) {
+                continue;
+            } else {
+                break;  // EAGAIN or error: the I/O thread finishes or drops it
+            }
+        }
+        if (off == bytes.size()) {
+            return 0;
+        }
+    }
+    c.out.emplace_back(bytes.substr(off));
+    if (!c.wantWrite) {
+        c.wantWrite = true;
+        epoll_event ev{};
+        ev.events = EPOLLIN | EPOLLOUT;
+        ev.data.fd = c.fd;
+        epoll_ctl(epfd_, EPOLL_CTL_MOD, c.fd, &ev);
+    }
+    return 0;
+}
+
+void RpcServer::CloseLink(LinkId link)
+{
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        pendingClose_.push_back(link);
+    }
+    Wake();
+}
+
+void RpcServer::Accept()
+{
+    while (true) {
+        int fd = ::accept4(listenFd_, nullptr, nullptr, SOCK_CLOEXEC | SOCK_NONBLOCK);
+        if (fd < 0) {
+            return;
+        }
+        SetNoDelay(fd);
+        auto c = std::make_shared<Conn>();
+        c->fd = fd;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            c->id = nextLink_++;
+            conns_[c->id] = c;
+            byFd_[fd] = c->id;
+        }
+        epoll_event ev{};
+        ev.events = EPOLLIN;
+        ev.data.fd = fd;
+        epoll_ctl(epfd_, EPOLL_CTL_ADD, fd, &ev);
+    }
+}
+
+void RpcServer::Drop(const std::shared_ptr<Conn> &c)
+{
+    bool wasUp;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        if (c->dead) {
+            return;
+        }
+        c->dead = true;
+        wasUp = c->hello;
+        conns_.erase(c->id);
+        byFd_.erase(c->fd);
+    }
+    epoll_ctl(epfd_, EPOLL_CTL_DEL, c->fd, nullptr);
+    ::close(c->fd);
+    if (wasUp && onDown_) {
+        onDown_(c->id);
+    }
+}
+
+void RpcServer::Flush(const std::shared_ptr<Conn> &c)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    while (!c->out.empty()) {
+        std::string &front = c->out.front();
+        ssize_t n = ::send(c->fd, front.data() + c->outOff, front.size() - c->outOff, MSG_NOSIGNAL | MSG_DONTWAIT);
+        if (n > 0) {
+            c->outOff += (size_t)n;
+            if (c->outOff == front.size()) {
+                c->out.pop_front();
+                c->outOff = 0;
+            }
+        } else if (n < 0 && errno == EINTR) {
+            continue;
+        } else {
+            break;
+        }
+    }
+    if (c->out.empty() && c->wantWrite) {
+        c->wantWrite = false;
+        epoll_event ev{};
+        ev.events = EPOLLIN;
+        ev.data.fd = c->fd;
+        epoll_ctl(epfd_, EPOLL_CTL_MOD, c->fd, &ev);
+    }
+}
+
+void RpcServer::OnReadable(const std::shared_ptr<Conn> &c)
+{
+    char buf[65536];
+    while (true) {
+        ssize_t n = ::recv(c->fd, buf, sizeof(buf), 0);
+        if (n > 0) {
+            c->in.append(buf, (size_t)n);
+            if ((size_t)n < sizeof(buf)) {
+                break;
+            }
+        } else if (n == 0) {
+            Drop(c);
+            return;
+        } else if (errno == EINTR) {
+            continue;
+        } else if (errno == EAGAIN || errno == EWOULDBLOCK) {
+            break;
+        } else {
+            Drop(c);
+            return;
+        }
+    }
+    size_t pos = 0;
+    while (c->in.size() - pos >= sizeof(WireHeader)) {
+        WireHeader h;
+        std::memcpy(&h, c->in.data() + pos, sizeof(h));
+        if (h.magic != kWireMagic || h.bodyLen > kMaxBodyLen) {
+            MF_WARN("rpc server: bad frame on link " << c->id << ", dropping the link");
+            Drop(c);
+            return;
+        }
+        if (c->in.size() - pos < sizeof(h) + h.bodyLen) {
+            break;
+        }
+        Frame f;
+        f.type = h.type;
+        f.result = h.result;
+        f.seq = h.seq;
+        f.body.assign(c->in.data() + pos + sizeof(h), h.bodyLen);
+        pos += sizeof(h) + h.bodyLen;
+        if (!c->hello) {
+            HelloBody hb{};
+            bool ok = f.type == MSG_HELLO && f.body.size() == sizeof(hb);
+            if (ok) {
+                std::memcpy(&hb, f.body.data(), sizeof(hb));
+                ok = hb.version == kWireVersion;
+            }
+            if (ok && onUp_) {
+                ok = onUp_(c->id, hb.peerId);
+            }
+            Frame ack;
+            ack.type = MSG_HELLO_ACK;
+            ack.seq = f.seq;
+            ack.result = (int16_t)(ok ? 0 : -1);
+            c->hello = ok;
+            Send(c->id, ack);
+            if (!ok) {
+                Flush(c);
+                Drop(c);
+                return;
+            }
+            continue;
+        }
+        if (onMsg_) {
+            onMsg_(c->id, f);
+        }
+        if (c->dead) {
+            return;
+        }
+    }
+    if (pos > 0) {
+        c->in.erase(0, pos);
+    }
+}
+
+void RpcServer::Loop()
+{
+    std::vector<epoll_event> evs(128);
+    while (running_.load()) {
+        int n = epoll_wait(epfd_, evs.data(), (int)evs.size(), 200);
+        if (n < 0 && errno != EINTR) {
+            break;
+        }
+        for (int i = 0; i < n; i++) {
+            int fd = evs[i].data.fd;
+            if (fd == listenFd_) {
+                Accept();
+                continue;
+            }
+            if (fd == wakeFd_) {
+                uint64_t v;
+                ssize_t r = ::read(wakeFd_, &v, sizeof(v));
+                (void)r;
+                continue;
+            }
+            std::shared_ptr<Conn> c;
+            {
+                std::lock_guard<std::mutex> g(mu_);
+                auto it = byFd_.find(fd);
+                if (it != byFd_.end()) {
+                    auto ct = conns_.find(it->second);
+                    if (ct != conns_.end()) {
+                        c = ct->second;
+                    }
+                }
+            }
+            if (!c) {
+                continue;
+            }
+            if (evs[i].events & (EPOLLHUP | EPOLLERR)) {
+                // Deliver what is still readable first so that a request followed by close is not lost.
+                OnReadable(c);
+                Drop(c);
+                continue;
+            }
+            if (evs[i].events & EPOLLOUT) {
+                Flush(c);
+            }
+            if (evs[i].events & EPOLLIN) {
+                OnReadable(c);
+            }
+        }
+        std::deque<LinkId> closing;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            closing.swap(pendingClose_);
+        }
+        for (LinkId id : closing) {
+            std::shared_ptr<Conn> c;
+            {
+                std::lock_guard<std::mutex> g(mu_);
+                auto it = conns_.find(id);
+                if (it != conns_.end()) {
+                    c = it->second;
+                }
+            }
+            if (c) {
+                Drop(c);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- client
+
+RpcClient::RpcClient() = default;
+RpcClient::~RpcClient() { Close(); }
+
+static bool ReadFull(int fd, void *buf, size_t len)
+{
+    char *p = (char *)buf;
+    while (len > 0) {
+        ssize_t n = ::recv(fd, p, len, 0);
+        if (n > 0) {
+            p += n;
+            len -= (size_t)n;
+        } else if (n < 0 && errno == EINTR) {
+            continue;
+        } else {
+            return false;
+        }
+    }
+    return true;
+}
+
+static bool WriteFull(int fd, const void *buf, size_t len)
+{
+    const char *p = (const char *)buf;
+    while (len > 0) {
+        ssize_t n = ::send(fd, p, len, MSG_NOSIGNAL);
+        if (n > 0) {
+            p += n;
+            len -= (size_t)n;
+        } else if (n < 0 && errno == EINTR) {
+            continue;
+        } else {
+            return false;
+        }
+    }
+    return true;
+}
+
+int RpcClient::Connect(const Endpoint &ep, uint64_t peerId, int retries, int retryDelayMs)
+{
+    Close();
+    closing_.store(false);
+    sockaddr_storage ss{};
+    socklen_t len = 0;
+    if (Resolve(ep, &ss, &len, false) != 0) {
+        MF_ERROR("rpc client: cannot resolve " << ep.host);
+        return -1;
+    }
+    for (int attempt = 0; attempt < retries && !closing_.load(); attempt++) {
+        int fd = ::socket(ss.ss_family, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        if (fd < 0) {
+            return -1;
+        }
+        if (::connect(fd, (sockaddr *)&ss, len) == 0) {
+            SetNoDelay(fd);
+            // Handshake: hello → ack, done synchronously before the reader thread exists.
+            HelloBody hb{kWireVersion, 0, 0, peerId};
+            Frame hello;
+            hello.type = MSG_HELLO;
+            hello.body.assign((const char *)&hb, sizeof(hb));
+            std::string bytes = Encode(hello);
+            WireHeader h{};
+            timeval tv{10, 0};
+            setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+            bool ok = WriteFull(fd, bytes.data(), bytes.size()) && ReadFull(fd, &h, sizeof(h)) && h.magic == kWireMagic &&
+                      h.type == MSG_HELLO_ACK && h.bodyLen == 0 && h.result == RPC_OK;
+            if (ok) {
+                tv = timeval{0, 0};
+                setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+                fd_ = fd;
+                connected_.store(true);
+                reader_ = std::thread([this]() { ReaderLoop(); });
+                return 0;
+            }
+            ::close(fd);
+            MF_WARN("rpc client: handshake with " << ep.host << ":" << ep.port << " rejected");
+            return -2;
+        }
+        ::close(fd);
+        if (attempt + 1 < retries) {
+            usleep((useconds_t)retryDelayMs * 1000);
+        }
+    }
+    return -1;
+}
+
+void RpcClient::Close()
+{
+    closing_.store(true);
+    if (fd_ >= 0) {
+        ::shutdown(fd_, SHUT_RDWR);
+    }
+    if (reader_.joinable()) {
+        if (reader_.get_id() == std::this_thread::get_id()) {
+            reader_.detach();
+        } else {
+            reader_.join();
+        }
+    }
+    if (fd_ >= 0) {
+        ::close(fd_);
+        fd_ = -1;
+    }
+    connected_.store(false);
+    FailAll();
+}
+
+void RpcClient::FailAll()
+{
+    std::unordered_map<uint32_t, std::shared_ptr<Pending>> all;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        all.swap(pending_);
+    }
+    for (auto &kv : all) {
+        std::lock_guard<std::mutex> g(kv.second->mu);
+        kv.second->failed = true;
+        kv.second->done = true;
+        kv.second->cv.notify_all();
+    }
+}
+
+int RpcClient::SendFrame(uint16_t type, uint32_t seq, const std::string &body)
+{
+    Frame f;
+    f.type = type;
+    f.seq = seq;
+    f.body = body;
+    std::string bytes = Encode(f);
+    std::lock_guard<std::mutex> g(sendMu_);
+    if (!connected_.load() || fd_ < 0) {
+        return -1;
+    }
+    return WriteFull(fd_, bytes.data(), bytes.size()) ? 0 : -1;
+}
+
+int RpcClient::Call(uint16_t type, const std::string &body, Frame *reply, int64_t timeoutMs)
+{
+    if (!connected_.load()) {
+        return RPC_IO_ERROR;
+    }
+    uint32_t seq = nextSeq_.fetch_add(1);
+    if (seq == 0) {
+        seq = nextSeq_.fetch_add(1);
+    }
+    auto p = std::make_shared<Pending>();
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        pending_[seq] = p;
+    }
+    if (SendFrame(type, seq, body) != 0) {
+        std::lock_guard<std::mutex> g(mu_);
+        pending_.erase(seq);
+        return RPC_IO_ERROR;
+    }
+    std::unique_lock<std::mutex> lk(p->mu);
+    if (timeoutMs < 0) {
+        p->cv.wait(lk, [&]() { return p->done; });
+    } else if (!p->cv.wait_for(lk, std::chrono::milliseconds(timeoutMs), [&]() { return p->done; })) {
+        lk.unlock();
+        std::lock_guard<std::mutex> g(mu_);
+        pending_.erase(seq);
+        return RPC_TIMEOUT;
+    }
+    if (p->failed) {
+        return RPC_IO_ERROR;
+    }
+    if (reply != nullptr) {
+        *reply = std::move(p->reply);
+    }
+    return RPC_OK;
+}
+
+uint32_t RpcClient::CallPersistent(uint16_t type, const std::string &body, PersistCb cb)
+{
+    if (!connected_.load()) {
+        return 0;
+    }
+    uint32_t seq = nextSeq_.fetch_add(1);
+    if (seq == 0) {
+        seq = nextSeq_.fetch_add(1);
+    }
+    auto p = std::make_shared<Pending>();
+    p->persist = std::move(cb);
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        pending_[seq] = p;
+    }
+    if (SendFrame(type, seq, body) != 0) {
+        std::lock_guard<std::mutex> g(mu_);
+        pending_.erase(seq);
+        return 0;
+    }
+    return seq;
+}
+
+void RpcClient::Cancel(uint32_t seq)
+{
+    std::lock_guard<std::mutex> g(mu_);
+    pending_.erase(seq);
+}
+
+void RpcClient::ReaderLoop()
+{
+    while (!closing_.load()) {
+        WireHeader h{};
+        if (!ReadFull(fd_, &h, sizeof(h)) || h.magic != kWireMagic || h.bodyLen > kMaxBodyLen) {
+            break;
+        }
+        Frame f;
+        f.type = h.type;
+        f.result = h.result;
+        f.seq = h.seq;
+        f.body.resize(h.bodyLen);
+        if (h.bodyLen > 0 && !ReadFull(fd_, &f.body[0], h.bodyLen)) {
+            break;
+        }
+        std::shared_ptr<Pending> p;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            auto it = pending_.find(f.seq);
+            if (it == pending_.end()) {
+                continue;  // late reply of a timed-out call
+            }
+            p = it->second;
+            if (!p->persist) {
+                pending_.erase(it);
+            }
+        }
+        if (p->persist) {
+            p->persist(f);
+        } else {
+            std::lock_guard<std::mutex> g(p->mu);
+            p->reply = std::move(f);
+            p->done = true;
+            p->cv.notify_all();
+        }
+    }
+    bool wasConnected = connected_.exchange(false);
+    FailAll();
+    if (wasConnected && !closing_.load() && onBroken_) {
+        onBroken_();
+    }
+}
+
+}  // namespace net
+}  // namespace mf
