@@ -6,7 +6,9 @@
 CUDA_HOME ?= /usr/local/cuda
 NVCC      := $(CUDA_HOME)/bin/nvcc
 PYTHON    ?= python
-CXX       ?= g++
+# The system compiler, deliberately not $CXX from the environment: a wrapper toolchain that links libstdc++ statically
+# would put a second C++ runtime into a process that already has torch's, and the two do not mix.
+CXX       := /usr/bin/g++
 
 PY_INC    := $(shell $(PYTHON) -c "import sysconfig; print(sysconfig.get_paths()['include'])")
 PYB_INC   := $(shell $(PYTHON) -c "import pybind11; print(pybind11.get_include())")
@@ -17,7 +19,7 @@ BUILD     := build
 OUTDIR    := memfabric_hybrid_b200/lib
 CXXFLAGS  := -std=c++17 -O2 -g -fPIC -Wall -Wextra -Wno-unused-parameter -fvisibility=default -pthread \
              -fstack-protector-strong -D_FORTIFY_SOURCE=2 -I$(CUDA_HOME)/include -Iinclude -Icsrc
-NVFLAGS   := -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -Iinclude -Icsrc \
+NVFLAGS   := -ccbin /usr/bin/g++ -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -Iinclude -Icsrc \
              --expt-relaxed-constexpr -Xptxas -v
 LDFLAGS   := -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lrt -pthread -Wl,-z,relro,-z,now
 

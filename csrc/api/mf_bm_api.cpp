@@ -618,11 +618,12 @@ extern "C" int32_t mf_bm_copy_batch(mf_bm_t handle, mf_batch_copy_params *params
 }
 extern "C" int32_t mf_bm_copy_on_stream(mf_bm_t handle, mf_copy_params *params, mf_bm_copy_type t, void *stream, uint32_t flags)
 {
-    return CopyImpl(handle, params, t, stream, flags | MF_ASYNC_COPY_FLAG);
+    // A null handle here means CUDA's default stream, not "pick one for me": hand the engines the explicit legacy-stream handle.
+    return CopyImpl(handle, params, t, stream != nullptr ? stream : (void *)cudaStreamLegacy, flags | MF_ASYNC_COPY_FLAG);
 }
 extern "C" int32_t mf_bm_copy_batch_on_stream(mf_bm_t handle, mf_batch_copy_params *params, mf_bm_copy_type t, void *stream, uint32_t flags)
 {
-    return BatchImpl(handle, params, t, stream, flags | MF_ASYNC_COPY_FLAG);
+    return BatchImpl(handle, params, t, stream != nullptr ? stream : (void *)cudaStreamLegacy, flags | MF_ASYNC_COPY_FLAG);
 }
 
 extern "C" int32_t mf_bm_wait(mf_bm_t handle)

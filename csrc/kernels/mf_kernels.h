@@ -46,6 +46,10 @@ int mf_k_checksum(const void *buf, size_t n, unsigned long long *out, mf_stream_
 unsigned char mf_k_pattern_byte_host(uint64_t seed, uint64_t index);
 unsigned long long mf_k_checksum_host(const void *buf, size_t n);
 
+// cudaMemcpyAsync(cudaMemcpyDefault) issued from inside the library (so that every CUDA call of a process that uses
+// the bindings goes through one runtime instance). Returns the cudaError_t value.
+int mf_k_memcpy_async(void *dst, const void *src, size_t n, mf_stream_t stream);
+
 // SM count of the current device (cached per device), 0 without a GPU.
 int mf_k_sm_count(void);
 

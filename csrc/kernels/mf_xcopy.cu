@@ -188,6 +188,11 @@ int LaunchResult()
 
 extern "C" int mf_k_sm_count(void) { return SmCount(); }
 
+extern "C" int mf_k_memcpy_async(void *dst, const void *src, size_t n, mf_stream_t stream)
+{
+    return (int)cudaMemcpyAsync(dst, src, n, cudaMemcpyDefault, (cudaStream_t)stream);
+}
+
 extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_stream_t stream)
 {
     if (n == 0) {

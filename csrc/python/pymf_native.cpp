@@ -34,11 +34,20 @@ struct PyServer {
     store::StoreServer s;
 };
 
+// The last reference to a Python callable may be dropped on a native thread: take the GIL for the decref.
+std::shared_ptr<py::function> HoldPy(py::function fn)
+{
+    return std::shared_ptr<py::function>(new py::function(std::move(fn)), [](py::function *p) {
+        py::gil_scoped_acquire gil;
+        delete p;
+    });
+}
+
 // Python callbacks are invoked from native threads: take the GIL, never let an exception escape.
 template <typename... A>
 std::function<void(A...)> WrapCb(py::function fn)
 {
-    auto holder = std::make_shared<py::function>(std::move(fn));
+    auto holder = HoldPy(std::move(fn));
     return [holder](A... a) {
         py::gil_scoped_acquire gil;
         try {
@@ -98,7 +107,7 @@ void BindNative(py::module_ &m)
         .def("set_mute", [](PyServer &s, bool mute) { s.s.SetMute(mute); });
 
     py::class_<store::ConfigStore, store::StorePtr>(n, "ConfigStore")
-        .def("set", [](store::ConfigStore &s, const std::string &k, py::bytes v) { return s.Set(k, std::string(v)); }, py::call_guard<py::gil_scoped_release>())
+        .def("set", [](store::ConfigStore &s, const std::string &k, const std::string &v) { return s.Set(k, v); }, py::call_guard<py::gil_scoped_release>())
         .def("get", [](store::ConfigStore &s, const std::string &k, int64_t timeoutMs) {
             std::string v;
             int rc;
@@ -137,7 +146,7 @@ void BindNative(py::module_ &m)
             }
             return py::make_tuple(rc, py::bytes(prev));
         })
-        .def("write", [](store::ConfigStore &s, const std::string &k, py::bytes v, uint32_t off) { return s.Write(k, std::string(v), off); },
+        .def("write", [](store::ConfigStore &s, const std::string &k, const std::string &v, uint32_t off) { return s.Write(k, v, off); },
              py::call_guard<py::gil_scoped_release>())
         .def("watch", [](store::ConfigStore &s, const std::string &k, py::function cb) {
             auto f = WrapCb<int, std::string, py::bytes>(std::move(cb));
@@ -192,7 +201,7 @@ void BindNative(py::module_ &m)
                      if (cb.is_none()) {
                          return nullptr;
                      }
-                     auto holder = std::make_shared<py::function>(cb.cast<py::function>());
+                     auto holder = HoldPy(cb.cast<py::function>());
                      return [holder](uint32_t r) {
                          py::gil_scoped_acquire gil;
                          try {
@@ -352,6 +361,9 @@ void BindNative(py::module_ &m)
     n.def("xcopy", [](uint64_t dst, uint64_t src, uint64_t nbytes, int ctas, uint64_t stream) {
         return mf_k_xcopy((void *)dst, (const void *)src, nbytes, ctas, (mf_stream_t)stream);
     }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("ctas") = 0, py::arg("stream") = 0);
+    n.def("copy_engine", [](uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream) {
+        return mf_k_memcpy_async((void *)dst, (const void *)src, nbytes, (mf_stream_t)stream);
+    }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("stream") = 0);
     n.def("batch_xcopy_inline", [](std::vector<uint64_t> srcs, std::vector<uint64_t> dsts, std::vector<uint64_t> sizes, int ctas, uint64_t stream) {
         std::vector<mf_copy_desc_t> d;
         uint32_t chunks = 0;

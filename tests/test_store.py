@@ -1,0 +1,291 @@
+"""Config store over loopback: every operation of the protocol, blocking gets, timeouts, watches, prefixes, large and binary
+values, heartbeat supervision, rank-down notification, server loss and reconnect. Scenarios follow the reference's store
+tests (test/ut/testcase/smem/acc_config_store_test.cpp:68-462)."""
+import threading
+import time
+
+import pytest
+
+ST_OK, ST_NOT_EXIST, ST_TIMEOUT, ST_IO_ERROR, ST_INVALID_KEY = 0, -404, -601, -602, -401
+
+
+@pytest.fixture
+def pair(mf, port):
+    n = mf.native
+    srv = n.TcpStore("127.0.0.1", port, True, 4, 0)
+    assert srv.startup(5, 100) == 0
+    cli = n.TcpStore("127.0.0.1", port, False, 4, 1)
+    assert cli.startup(5, 100) == 0
+    yield srv, cli
+    cli.shutdown()
+    srv.shutdown()
+
+
+def test_url_parsing(mf):
+    p = mf.native.parse_url
+    assert p("tcp://127.0.0.1:5000") == ("127.0.0.1", 5000, False)
+    assert p("tcp://[::1]:6000") == ("::1", 6000, True)
+    assert p("tcp6://[fe80::1]:7") == ("fe80::1", 7, True)
+    assert p("10.1.2.3:80") == ("10.1.2.3", 80, False)
+    for bad in ["", "tcp://", "tcp://1.2.3.4", "tcp://1.2.3.4:0", "tcp://1.2.3.4:70000", "tcp://300.1.1.1:5", "tcp://[::1]6000", "tcp://1.2.3.4:12ab"]:
+        assert p(bad) is None, bad
+
+
+def test_message_codec(mf):
+    n = mf.native
+    buf = n.pack_message(1234, ["k1", "key2"], [b"\x00\x01binary\xff", b""])
+    assert n.unpack_message(buf) == (1234, ["k1", "key2"], [b"\x00\x01binary\xff", b""])
+    assert n.unpack_message(buf[:-1]) is None
+    assert n.unpack_message(buf + b"x") is None
+    assert n.unpack_message(b"short") is None
+    assert n.unpack_message(n.pack_message(-1, ["k"] * 11, [])) is None
+
+
+def test_set_get_remove(pair):
+    srv, cli = pair
+    assert cli.set("a", b"1") == ST_OK
+    assert srv.get("a", 0) == (ST_OK, b"1")
+    assert cli.set("a", b"2") == ST_OK
+    assert cli.get("a", 0) == (ST_OK, b"2")
+    assert cli.remove("a") == ST_OK
+    assert cli.remove("a") == ST_NOT_EXIST
+    assert cli.get("a", 0)[0] == ST_NOT_EXIST
+    assert cli.set("", b"x") == ST_INVALID_KEY
+    assert cli.set("k" * 1025, b"x") == ST_INVALID_KEY
+
+
+def test_blocking_get_is_woken_by_set(pair):
+    srv, cli = pair
+    out = {}
+
+    def waiter():
+        out["r"] = cli.get("later", 5000)
+
+    t = threading.Thread(target=waiter)
+    t.start()
+    time.sleep(0.1)
+    assert srv.set("later", b"now") == ST_OK
+    t.join(5)
+    assert out["r"] == (ST_OK, b"now")
+
+
+def test_get_timeout(pair):
+    _, cli = pair
+    t0 = time.time()
+    rc, _ = cli.get("never", 200)
+    assert rc == ST_TIMEOUT
+    assert 0.15 < time.time() - t0 < 2.0
+
+
+def test_add_append_cas_write(pair):
+    srv, cli = pair
+    assert cli.add("cnt", 5) == (ST_OK, 5)
+    assert srv.add("cnt", -2) == (ST_OK, 3)
+    assert cli.get("cnt", 0) == (ST_OK, b"3")
+    assert cli.append("log", b"ab") == (ST_OK, 2)
+    assert srv.append("log", b"cde") == (ST_OK, 5)
+    assert cli.get("log", 0) == (ST_OK, b"abcde")
+    # cas: expected "" matches an absent key; the previous value comes back either way
+    assert cli.cas("lock", b"", b"A") == (ST_OK, b"")
+    assert srv.cas("lock", b"", b"B") == (ST_OK, b"A")
+    assert srv.cas("lock", b"A", b"C") == (ST_OK, b"A")
+    assert cli.get("lock", 0) == (ST_OK, b"C")
+    # write at an offset zero-fills the gap
+    assert cli.write("slots", b"XY", 4) == ST_OK
+    assert cli.get("slots", 0) == (ST_OK, b"\x00\x00\x00\x00XY")
+    assert cli.write("slots", b"Q", 0) == ST_OK
+    assert cli.get("slots", 0) == (ST_OK, b"Q\x00\x00\x00XY")
+
+
+def test_add_and_append_wake_waiters(pair):
+    srv, cli = pair
+    got = []
+    t = threading.Thread(target=lambda: got.append(cli.get("c2", 3000)))
+    t.start()
+    time.sleep(0.05)
+    srv.add("c2", 7)
+    t.join(3)
+    assert got == [(ST_OK, b"7")]
+
+
+def test_large_and_binary_values(pair):
+    _, cli = pair
+    blob = bytes(range(256)) * 4096 * 8  # 8 MiB
+    assert cli.set("big", blob) == ST_OK
+    assert cli.get("big", 0) == (ST_OK, blob)
+
+
+def test_prefix_and_nested_prefix(mf, pair):
+    srv, cli = pair
+    p1 = mf.native.prefix_store(cli, "A_")
+    p2 = mf.native.prefix_store(p1, "(3)_")
+    assert p2.common_prefix() == "A_(3)_"
+    assert p2.set("k", b"v") == ST_OK
+    assert srv.get("A_(3)_k", 0) == (ST_OK, b"v")
+    assert p1.get("(3)_k", 0) == (ST_OK, b"v")
+    assert p2.get("k", 0) == (ST_OK, b"v")
+    assert p1.get("k", 0)[0] == ST_NOT_EXIST
+
+
+def test_watch_and_unwatch(pair):
+    srv, cli = pair
+    seen = []
+    rc, wid = cli.watch("w1", lambda r, k, v: seen.append((r, k, v)))
+    assert rc == ST_OK
+    rc2, wid2 = cli.watch("w2", lambda r, k, v: seen.append("w2"))
+    assert cli.unwatch(wid2) == ST_OK
+    srv.set("w1", b"hello")
+    srv.set("w2", b"ignored")
+    deadline = time.time() + 3
+    while not seen and time.time() < deadline:
+        time.sleep(0.01)
+    time.sleep(0.1)
+    assert seen == [(ST_OK, "w1", b"hello")]
+    assert cli.unwatch(wid) == ST_NOT_EXIST  # one-shot: already consumed
+
+
+def test_auto_ranking_hands_out_lowest_free(mf, port):
+    n = mf.native
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    clients = [n.TcpStore("127.0.0.1", port, False, 0, -1) for _ in range(3)]
+    for c in clients:
+        assert c.startup(5, 100) == 0
+    ranks = [int(c.get("AutoRanking#job", 1000)[1]) for c in clients]
+    assert sorted(ranks) == [0, 1, 2]
+    assert int(clients[1].get("AutoRanking#job", 1000)[1]) == ranks[1]  # stable per link
+    clients[0].shutdown()
+    time.sleep(0.3)
+    late = n.TcpStore("127.0.0.1", port, False, 0, -1)
+    assert late.startup(5, 100) == 0
+    assert int(late.get("AutoRanking#job", 1000)[1]) == ranks[0]  # the freed id is reused
+    for c in clients[1:] + [late]:
+        c.shutdown()
+    srv.stop()
+
+
+def test_rank_down_notification_on_close(mf, port):
+    n = mf.native
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    a = n.TcpStore("127.0.0.1", port, False, 2, 0)
+    b = n.TcpStore("127.0.0.1", port, False, 2, 1)
+    assert a.startup(5, 100) == 0 and b.startup(5, 100) == 0
+    down = []
+    assert a.watch_rank_down(lambda r: down.append(r))[0] == ST_OK
+    time.sleep(0.1)
+    b.shutdown()
+    deadline = time.time() + 3
+    while not down and time.time() < deadline:
+        time.sleep(0.01)
+    assert down == [1]
+    a.shutdown()
+    srv.stop()
+
+
+def test_heartbeat_loss_marks_rank_down(mf, port):
+    n = mf.native
+    n.set_heartbeat_ms(50, 3)
+    try:
+        srv = n.StoreServer()
+        assert srv.start("127.0.0.1", port) == 0
+        a = n.TcpStore("127.0.0.1", port, False, 2, 0)
+        b = n.TcpStore("127.0.0.1", port, False, 2, 1)
+        assert a.startup(5, 100) == 0 and b.startup(5, 100) == 0
+        down = []
+        a.watch_rank_down(lambda r: down.append(r))
+        time.sleep(0.3)
+        assert down == [] and srv.alive_links() == 2  # heartbeats keep both alive
+        b.set_drop_heartbeat(True)  # the process is alive, its socket is open, but it went silent
+        deadline = time.time() + 5
+        while not down and time.time() < deadline:
+            time.sleep(0.02)
+        assert down == [1]
+        a.shutdown()
+        b.shutdown()
+        srv.stop()
+    finally:
+        n.set_heartbeat_ms(2000, 3)
+
+
+def test_store_cleared_when_last_client_leaves(mf, port):
+    n = mf.native
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    a = n.TcpStore("127.0.0.1", port, False, 1, 0)
+    assert a.startup(5, 100) == 0
+    a.set("k", b"v")
+    assert srv.size() == 1
+    a.shutdown()
+    deadline = time.time() + 3
+    while srv.size() != 0 and time.time() < deadline:
+        time.sleep(0.02)
+    assert srv.size() == 0
+    srv.stop()
+
+
+def test_get_when_server_exits_then_reconnect(mf, port):
+    n = mf.native
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    c = n.TcpStore("127.0.0.1", port, False, 1, 0)
+    assert c.startup(5, 100) == 0
+    broken, again = [], []
+    c.set_broken_handler(lambda: broken.append(1))
+    c.set_reconnect_handler(lambda: again.append(1))
+    res = []
+    t = threading.Thread(target=lambda: res.append(c.get("never", -1)))
+    t.start()
+    time.sleep(0.1)
+    srv.stop()
+    t.join(5)
+    assert res and res[0][0] == ST_IO_ERROR  # the blocked get fails instead of hanging
+    deadline = time.time() + 3
+    while not broken and time.time() < deadline:
+        time.sleep(0.01)
+    assert broken
+    assert c.set("x", b"1") == ST_IO_ERROR
+    srv2 = n.StoreServer()
+    assert srv2.start("127.0.0.1", port) == 0
+    assert c.reconnect(5) == ST_OK
+    assert again
+    assert c.set("x", b"1") == ST_OK
+    c.shutdown()
+    srv2.stop()
+
+
+def test_second_server_on_same_port_reports_in_use(mf, port):
+    n = mf.native
+    s1, s2 = n.StoreServer(), n.StoreServer()
+    assert s1.start("127.0.0.1", port) == 0
+    assert s2.start("127.0.0.1", port) == -98  # EADDRINUSE
+    s1.stop()
+
+
+def test_ipv6_loopback(mf, port):
+    n = mf.native
+    srv = n.StoreServer()
+    if srv.start("::1", port) != 0:
+        pytest.skip("no IPv6 loopback here")
+    c = n.TcpStore("::1", port, False, 1, 0)
+    assert c.startup(3, 100) == 0
+    assert c.set("v6", b"ok") == ST_OK and c.get("v6", 0) == (ST_OK, b"ok")
+    c.shutdown()
+    srv.stop()
+
+
+def test_ha_store_delegates(mf, pair):
+    srv, cli = pair
+    ha = mf.native.ha_store(cli)
+    assert ha.set("h", b"1") == ST_OK and srv.get("h", 0) == (ST_OK, b"1")
+
+
+def test_create_config_store_api(mf, port):
+    url = f"tcp://127.0.0.1:{port}"
+    assert mf.create_config_store(url) == 0
+    assert mf.create_config_store("tcp://nonsense") != 0
+    c = mf.native.TcpStore("127.0.0.1", port, False, 1, 0)
+    assert c.startup(3, 100) == 0
+    assert c.add("n", 1) == (ST_OK, 1)
+    c.shutdown()
+    mf.destroy_config_store(url)
