@@ -171,22 +171,32 @@ public:
             if (slot.used) {
                 cudaEventSynchronize(slot.ev);  // the previous H2D from this slot must have been consumed
             }
-            if (slot.cap < d.size()) {
+            // Table layout: descriptors, then one uint32 per chunk naming its descriptor.
+            const size_t descBytes = d.size() * sizeof(mf_copy_desc_t);
+            const size_t bytes = descBytes + (size_t)chunks * sizeof(uint32_t);
+            if (slot.cap < bytes) {
                 if (slot.host != nullptr) {
                     cudaStreamSynchronize(s);
                     cudaFreeHost(slot.host);
                     cudaFree(slot.dev);
                 }
-                size_t cap = std::max<size_t>(d.size() * 2, 4096);
-                MF_CUDA_CHECK_RET(cudaHostAlloc((void **)&slot.host, cap * sizeof(mf_copy_desc_t), cudaHostAllocDefault), BM_MALLOC_FAILED);
-                MF_CUDA_CHECK_RET(cudaMalloc((void **)&slot.dev, cap * sizeof(mf_copy_desc_t)), BM_MALLOC_FAILED);
+                size_t cap = std::max<size_t>(bytes * 2, 256 * 1024);
+                MF_CUDA_CHECK_RET(cudaHostAlloc((void **)&slot.host, cap, cudaHostAllocDefault), BM_MALLOC_FAILED);
+                MF_CUDA_CHECK_RET(cudaMalloc((void **)&slot.dev, cap), BM_MALLOC_FAILED);
                 slot.cap = cap;
                 if (slot.ev == nullptr) {
                     MF_CUDA_CHECK_RET(cudaEventCreateWithFlags(&slot.ev, cudaEventDisableTiming), BM_ERROR);
                 }
             }
-            std::memcpy(slot.host, d.data(), d.size() * sizeof(mf_copy_desc_t));
-            MF_CUDA_CHECK_RET(cudaMemcpyAsync(slot.dev, slot.host, d.size() * sizeof(mf_copy_desc_t), cudaMemcpyHostToDevice, s), BM_ERROR);
+            std::memcpy(slot.host, d.data(), descBytes);
+            uint32_t *map = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(slot.host) + descBytes);
+            for (uint32_t i = 0; i < d.size(); i++) {
+                const uint32_t n = (d[i].len + MF_BATCH_CHUNK_BYTES - 1) / MF_BATCH_CHUNK_BYTES;
+                for (uint32_t c = 0; c < n; c++) {
+                    map[d[i].chunkStart + c] = i;
+                }
+            }
+            MF_CUDA_CHECK_RET(cudaMemcpyAsync(slot.dev, slot.host, bytes, cudaMemcpyHostToDevice, s), BM_ERROR);
             cudaEventRecord(slot.ev, s);
             slot.used = true;
             devTable = slot.dev;

@@ -56,6 +56,13 @@ public:
     PtrClass Classify(uint64_t addr, bool *deviceVisible);
     const DeviceMeta *DeviceMetaPtr() const { return devMeta_; }
     DeviceMeta HostMeta() const { return hostMeta_; }
+    // Publishes the signal area and (optionally) the NVLS multicast alias to device code.
+    int SetMetaExtras(uint64_t signalBase, uint64_t multicastBase)
+    {
+        hostMeta_.signalBase = signalBase;
+        hostMeta_.multicastBase = multicastBase;
+        return UpdateDeviceMeta();
+    }
     std::shared_ptr<MemSegment> Segment(uint32_t memType) const;
     std::shared_ptr<ComposeDataOp> DataOp() const { return dataOp_; }
 

@@ -17,6 +17,7 @@ constexpr uint64_t GRANULE = 2 * MiB;  // cuMemGetAllocationGranularity(recommen
 constexpr uint32_t RANK_MAX = 1024;
 constexpr uint64_t GVA_WINDOW_BEGIN = 32 * TiB;
 constexpr uint64_t GVA_WINDOW_END = 96 * TiB;
+constexpr uint64_t GVA_HOST_BEGIN = 64 * TiB;  // host-DRAM windows are searched from here, HBM windows from the start
 constexpr uint32_t ENTITY_MAX = 512;
 constexpr uint32_t EXTRA_CONTEXT_MAX = 64 * 1024;
 constexpr uint32_t EXCHANGE_DESC_MAX = 512;

@@ -393,7 +393,7 @@ public:
     {
         MF_CHECK_RET(base_ == 0, BM_ERROR, "host segment: window already reserved");
         uint64_t total = opt_.windowSize * opt_.rankCount;
-        uint64_t want = VaManager::Instance().FindFreeWindow(total, hint);
+        uint64_t want = VaManager::Instance().FindFreeWindow(total, hint != 0 ? hint : GVA_HOST_BEGIN);
         MF_CHECK_RET(want != 0, BM_MALLOC_FAILED, "host segment: GVA window exhausted");
         void *p = ::mmap((void *)want, total, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED_NOREPLACE, -1, 0);
         if (p == MAP_FAILED || (uint64_t)p != want) {

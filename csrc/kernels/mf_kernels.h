@@ -29,11 +29,35 @@ enum { MF_BATCH_INLINE_MAX = 168, MF_BATCH_CHUNK_BYTES = 32768 };
 
 // Batch of `count` independent copies in ONE launch. Descriptors must have chunkStart filled (prefix sum of
 // ceil(len / MF_BATCH_CHUNK_BYTES)); totalChunks is the grand total. count <= MF_BATCH_INLINE_MAX travels in the kernel
-// parameters; larger batches must pass `descsDev`, a device-readable copy of the table. `doneCounter` (device, zero
+// parameters; larger batches must pass `descsDev`, a device-readable copy of the table that is followed directly by
+// uint32 map[totalChunks] giving each chunk's descriptor index. `doneCounter` (device, zero
 // before first use, self-resetting) and `hostFlag` (pinned host word, may be NULL) implement completion signalling:
 // the last CTA stores `flagValue` to *hostFlag with system-scope release semantics.
 int mf_k_batch_xcopy(const mf_copy_desc_t *descs, const mf_copy_desc_t *descsDev, uint32_t count, uint32_t totalChunks,
                      uint32_t *doneCounter, volatile uint32_t *hostFlag, uint32_t flagValue, int ctas, mf_stream_t stream);
+
+// ------------------------------------------------------------------------------------------------ allreduce + RMSNorm (K4)
+
+// One block per (emulated) rank, resident in device memory. x must lie in the symmetric heap (peers read it at the same
+// offset); residualOut must lie in the heap for the two-shot and NVLS algorithms (peers write it); the rest is local.
+typedef struct {
+    const void *meta;      // MfDeviceMeta of this rank (device pointer)
+    const void *x;         // [T, H] bf16, this rank's addend
+    const void *residual;  // [T, H] bf16 or NULL
+    const void *weight;    // [H] bf16
+    void *residualOut;     // [T, H] bf16: residual + sum_r x_r (may be NULL for one-shot)
+    void *out;             // [T, H] bf16: RMSNorm(residualOut) * weight
+    int *status;           // device int, zero before launch; receives MF_DEV_ERR_* | peer << 8 on a bounded-wait expiry
+    void *reserved;
+} mf_allreduce_args_t;
+
+enum { MF_AR_AUTO = 0, MF_AR_ONESHOT = 1, MF_AR_TWOSHOT = 2, MF_AR_NVLS = 3 };
+
+// argsDev: device array of nEmulatedRanks blocks (1 in production; R when a test runs all ranks of a fake heap on one GPU
+// as slices of one cooperative launch). rankCount must equal meta->rankCount. epoch: strictly increasing per (heap,
+// channel), identical on all ranks (mf_shm_next_epoch). H: multiple of 8, at most 16384. timeoutNs 0 = 2 s.
+int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRanks, int rankCount, int T, int H, float eps, int algo,
+                           uint32_t channel, uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 
 // ------------------------------------------------------------------------------------------------ test support (K7)
 

@@ -50,17 +50,24 @@ struct BatchInline {
 };
 static_assert(sizeof(BatchInline) <= 4096 + 32, "inline batch must fit the classic kernel parameter space");
 
-__device__ __forceinline__ void BatchBody(const mf_copy_desc_t *__restrict__ d, uint32_t count, uint32_t totalChunks)
+__device__ __forceinline__ void BatchBody(const mf_copy_desc_t *__restrict__ d, uint32_t count, uint32_t totalChunks,
+                                          const uint32_t *__restrict__ chunkMap)
 {
     for (uint32_t c = blockIdx.x; c < totalChunks; c += gridDim.x) {
-        // Last descriptor whose chunkStart <= c. All threads search the same value: uniform, cache-resident accesses.
-        uint32_t lo = 0, hi = count;
-        while (hi - lo > 1) {
-            uint32_t mid = (lo + hi) >> 1;
-            if (d[mid].chunkStart <= c) {
-                lo = mid;
-            } else {
-                hi = mid;
+        uint32_t lo = 0;
+        if (chunkMap != nullptr) {
+            lo = chunkMap[c];  // table in global memory: one load instead of a chain of dependent ones
+        } else {
+            // Last descriptor whose chunkStart <= c. The table sits in the constant bank (kernel parameters), all
+            // threads search the same value: uniform, a few cycles per step.
+            uint32_t hi = count;
+            while (hi - lo > 1) {
+                uint32_t mid = (lo + hi) >> 1;
+                if (d[mid].chunkStart <= c) {
+                    lo = mid;
+                } else {
+                    hi = mid;
+                }
             }
         }
         const uint64_t off = (uint64_t)(c - d[lo].chunkStart) * MF_BATCH_CHUNK_BYTES;
@@ -93,15 +100,16 @@ __device__ __forceinline__ void BatchSignal(uint32_t *doneCounter, volatile uint
 
 __global__ void __launch_bounds__(kThreads, 2) mf_batch_xcopy_inline_kernel(const __grid_constant__ BatchInline p)
 {
-    BatchBody(p.d, p.count, p.totalChunks);
+    BatchBody(p.d, p.count, p.totalChunks, nullptr);
     BatchSignal(p.doneCounter, p.hostFlag, p.flagValue);
 }
 
+// The chunk → descriptor map follows the descriptor table in the same device buffer.
 __global__ void __launch_bounds__(kThreads, 2)
 mf_batch_xcopy_table_kernel(const mf_copy_desc_t *__restrict__ d, uint32_t count, uint32_t totalChunks, uint32_t *doneCounter,
                             volatile uint32_t *hostFlag, uint32_t flagValue)
 {
-    BatchBody(d, count, totalChunks);
+    BatchBody(d, count, totalChunks, reinterpret_cast<const uint32_t *>(d + count));
     BatchSignal(doneCounter, hostFlag, flagValue);
 }
 

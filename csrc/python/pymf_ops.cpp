@@ -1,2 +1,38 @@
+// `ops` submodule: raw launchers of the fused compute+collective kernels. Arguments are device addresses (ints) and a
+// CUDA stream handle; the torch-facing wrappers live in memfabric_hybrid_b200/ops.
+#include <pybind11/stl.h>
+
+#include "../kernels/mf_kernels.h"
 #include "pymf_parts.h"
-void BindOps(pybind11::module_ &) {}
+
+namespace py = pybind11;
+
+void BindOps(py::module_ &m)
+{
+    py::module_ ops = m.def_submodule("ops", "raw launchers of the fused kernels");
+
+    ops.attr("AR_AUTO") = (int)MF_AR_AUTO;
+    ops.attr("AR_ONESHOT") = (int)MF_AR_ONESHOT;
+    ops.attr("AR_TWOSHOT") = (int)MF_AR_TWOSHOT;
+    ops.attr("AR_NVLS") = (int)MF_AR_NVLS;
+    ops.attr("ALLREDUCE_ARGS_BYTES") = (int)sizeof(mf_allreduce_args_t);
+
+    // Packs one argument block (to be copied to device memory by the caller).
+    ops.def("pack_allreduce_args", [](uint64_t meta, uint64_t x, uint64_t residual, uint64_t weight, uint64_t residualOut, uint64_t out, uint64_t status) {
+        mf_allreduce_args_t a{};
+        a.meta = (const void *)meta;
+        a.x = (const void *)x;
+        a.residual = (const void *)residual;
+        a.weight = (const void *)weight;
+        a.residualOut = (void *)residualOut;
+        a.out = (void *)out;
+        a.status = (int *)status;
+        return py::bytes((const char *)&a, sizeof(a));
+    });
+    ops.def("allreduce_rmsnorm", [](uint64_t argsDev, int nEmulated, int rankCount, int T, int H, float eps, int algo, uint32_t channel, uint64_t epoch,
+                                    uint64_t timeoutNs, int ctas, uint64_t stream) {
+        return mf_k_allreduce_rmsnorm((const mf_allreduce_args_t *)argsDev, nEmulated, rankCount, T, H, eps, algo, channel, epoch, timeoutNs, ctas,
+                                      (mf_stream_t)stream);
+    }, py::arg("args_dev"), py::arg("n_emulated"), py::arg("rank_count"), py::arg("T"), py::arg("H"), py::arg("eps"), py::arg("algo"),
+            py::arg("channel"), py::arg("epoch"), py::arg("timeout_ns") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
+}

@@ -115,7 +115,7 @@ def test_all_directions_roundtrip(mf, pool):
     assert (out_ld.cpu().numpy() == ref).all()
     out_ld.zero_()
     torch.cuda.synchronize()  # the pool's synchronous copies run on the library's own stream, not on torch's
-    assert h.copy_data(gd + 1, out_ld.data_ptr(), n, T.AUTO, 0) == 0, mf.get_last_err_msg()
+    assert h.copy_data(gd + 8 * MiB, out_ld.data_ptr(), n, T.AUTO, 0) == 0, mf.get_last_err_msg()
     assert (out_ld.cpu().numpy() == ref).all()
     # local → local is not a pool operation
     assert h.copy_data(ld.data_ptr(), out_ld.data_ptr(), n, T.AUTO, 0) != 0
