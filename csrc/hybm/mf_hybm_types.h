@@ -14,6 +14,7 @@ namespace hybm {
 
 constexpr uint64_t KiB = 1024ull, MiB = 1024ull * KiB, GiB = 1024ull * MiB, TiB = 1024ull * GiB;
 constexpr uint64_t GRANULE = 2 * MiB;  // cuMemGetAllocationGranularity(recommended) on B200; also huge-page size
+constexpr uint64_t WINDOW_ALIGN = GiB;  // start alignment and minimum length of a reserved GVA window
 constexpr uint32_t RANK_MAX = 1024;
 constexpr uint64_t GVA_WINDOW_BEGIN = 32 * TiB;
 constexpr uint64_t GVA_WINDOW_END = 96 * TiB;

@@ -98,7 +98,7 @@ public:
         MF_CHECK_RET(base_ == 0, BM_ERROR, "device segment: window already reserved");
         MF_CUDA_CHECK_RET(cudaSetDevice(opt_.devId), BM_ERROR);
         MF_CUDA_CHECK_RET(cudaFree(nullptr), BM_ERROR);  // make sure the primary context exists
-        uint64_t total = opt_.windowSize * opt_.rankCount;
+        uint64_t total = ReservedBytes();
         uint64_t want = VaManager::Instance().FindFreeWindow(total, hint);
         MF_CHECK_RET(want != 0, BM_MALLOC_FAILED, "device segment: GVA window exhausted");
         CUdeviceptr got = 0;
@@ -126,7 +126,7 @@ public:
         }
         const cu::DriverApi *d = cu::Driver();
         if (d != nullptr) {
-            d->MemAddressFree((CUdeviceptr)base_, opt_.windowSize * opt_.rankCount);
+            d->MemAddressFree((CUdeviceptr)base_, ReservedBytes());
         }
         VaManager::Instance().RemoveReserved(base_);
         base_ = 0;
@@ -392,7 +392,7 @@ public:
     int ReserveMemorySpace(uint64_t hint, uint64_t *base) override
     {
         MF_CHECK_RET(base_ == 0, BM_ERROR, "host segment: window already reserved");
-        uint64_t total = opt_.windowSize * opt_.rankCount;
+        uint64_t total = ReservedBytes();
         uint64_t want = VaManager::Instance().FindFreeWindow(total, hint != 0 ? hint : GVA_HOST_BEGIN);
         MF_CHECK_RET(want != 0, BM_MALLOC_FAILED, "host segment: GVA window exhausted");
         void *p = ::mmap((void *)want, total, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED_NOREPLACE, -1, 0);
@@ -414,7 +414,7 @@ public:
         if (base_ == 0) {
             return BM_OK;
         }
-        ::munmap((void *)base_, opt_.windowSize * opt_.rankCount);
+        ::munmap((void *)base_, ReservedBytes());
         VaManager::Instance().RemoveReserved(base_);
         base_ = 0;
         return BM_OK;

@@ -101,6 +101,14 @@ public:
     // True if GPU kernels on the local device can dereference addresses of this segment.
     virtual bool DeviceAccessible() const = 0;
 
+    // Bytes of address space actually reserved for the window: padded to whole GiB. The CUDA driver honours a requested
+    // address only for reservations that do not share its internal VA blocks with neighbours, so windows are kept at
+    // least 1 GiB long and 1 GiB aligned (address space is free; physical memory is only what the slices map).
+    uint64_t ReservedBytes() const
+    {
+        const uint64_t need = opt_.windowSize * opt_.rankCount;
+        return need <= WINDOW_ALIGN ? WINDOW_ALIGN : (need + WINDOW_ALIGN - 1) / WINDOW_ALIGN * WINDOW_ALIGN;
+    }
     uint64_t Base() const { return base_; }
     uint64_t WindowSize() const { return opt_.windowSize; }
     uint64_t LocalAllocated() const { return localUsed_; }

@@ -39,8 +39,8 @@ static uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 uint64_t VaManager::FindFreeWindow(uint64_t size, uint64_t hint)
 {
     std::lock_guard<std::mutex> g(mu_);
-    size = AlignUp(size, GRANULE);
-    uint64_t cur = hint != 0 ? AlignUp(hint, GRANULE) : GVA_WINDOW_BEGIN;
+    size = AlignUp(size, WINDOW_ALIGN);
+    uint64_t cur = hint != 0 ? AlignUp(hint, WINDOW_ALIGN) : GVA_WINDOW_BEGIN;
     if (cur < GVA_WINDOW_BEGIN) {
         cur = GVA_WINDOW_BEGIN;
     }
@@ -52,7 +52,7 @@ uint64_t VaManager::FindFreeWindow(uint64_t size, uint64_t hint)
         if (b >= cur + size) {
             break;
         }
-        cur = AlignUp(e, GRANULE);
+        cur = AlignUp(e, WINDOW_ALIGN);
     }
     if (cur + size > GVA_WINDOW_END) {
         return 0;
