@@ -59,6 +59,23 @@ enum { MF_AR_AUTO = 0, MF_AR_ONESHOT = 1, MF_AR_TWOSHOT = 2, MF_AR_NVLS = 3 };
 int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRanks, int rankCount, int T, int H, float eps, int algo,
                            uint32_t channel, uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 
+// ------------------------------------------------------------------------------------------------ MoE expert FFN (K5b)
+
+enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1 };
+
+// Grouped block-scaled FP8 GEMM on tcgen05 tensor cores. Group g owns rows [groupOffset[g], groupOffset[g] + groupCount[g])
+// of A (group starts must be multiples of 128 rows; rows between count and the next start are ignored) and weights
+// b[g] = [N, K]. a: [rowsTotal, K] e4m3, aScale: [rowsTotal, K/128] fp32, b: [G, N, K] e4m3, bScale: [G, N/128, K/128]
+// fp32. out is bf16: [rowsTotal, N] for MF_GEMM_EPI_BF16; [rowsTotal, N/2] for MF_GEMM_EPI_SWIGLU, where every 64-row
+// chunk of b[g] holds 32 gate rows followed by the 32 matching up rows and out = silu(gate) * up. N and K: multiples of 128.
+// groupOffset/groupCount live on the device (the routing result never visits the host). status: device int or NULL.
+int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, const float *bScale, void *out, const int *groupOffset,
+                          const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas, mf_stream_t stream);
+
+// bf16 [rows, K] → e4m3 [rows, K] + fp32 scales [rows, K/128] (scale = amax/448 per 128 elements). rowLimit (device int,
+// may be NULL) caps the number of rows actually processed.
+int mf_k_quant_rows_fp8(const void *x, void *q, float *scale, int rows, int K, const int *rowLimit, mf_stream_t stream);
+
 // ------------------------------------------------------------------------------------------------ test support (K7)
 
 // dst[i] = hash(seed, i) for i in [0, n) bytes; deterministic on host and device (see mf_k_pattern_byte_host).

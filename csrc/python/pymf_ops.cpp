@@ -29,6 +29,17 @@ void BindOps(py::module_ &m)
         a.status = (int *)status;
         return py::bytes((const char *)&a, sizeof(a));
     });
+    ops.attr("GEMM_EPI_BF16") = (int)MF_GEMM_EPI_BF16;
+    ops.attr("GEMM_EPI_SWIGLU") = (int)MF_GEMM_EPI_SWIGLU;
+    ops.def("moe_grouped_gemm", [](uint64_t a, uint64_t aScale, uint64_t b, uint64_t bScale, uint64_t out, uint64_t groupOffset, uint64_t groupCount,
+                                   int G, int rowsTotal, int N, int K, int mode, uint64_t status, int ctas, uint64_t stream) {
+        return mf_k_moe_grouped_gemm((const void *)a, (const float *)aScale, (const void *)b, (const float *)bScale, (void *)out,
+                                     (const int *)groupOffset, (const int *)groupCount, G, rowsTotal, N, K, mode, (int *)status, ctas, (mf_stream_t)stream);
+    }, py::arg("a"), py::arg("a_scale"), py::arg("b"), py::arg("b_scale"), py::arg("out"), py::arg("group_offset"), py::arg("group_count"), py::arg("G"),
+            py::arg("rows_total"), py::arg("N"), py::arg("K"), py::arg("mode"), py::arg("status") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
+    ops.def("quant_rows_fp8", [](uint64_t x, uint64_t q, uint64_t scale, int rows, int K, uint64_t rowLimit, uint64_t stream) {
+        return mf_k_quant_rows_fp8((const void *)x, (void *)q, (float *)scale, rows, K, (const int *)rowLimit, (mf_stream_t)stream);
+    }, py::arg("x"), py::arg("q"), py::arg("scale"), py::arg("rows"), py::arg("K"), py::arg("row_limit") = 0, py::arg("stream") = 0);
     ops.def("allreduce_rmsnorm", [](uint64_t argsDev, int nEmulated, int rankCount, int T, int H, float eps, int algo, uint32_t channel, uint64_t epoch,
                                     uint64_t timeoutNs, int ctas, uint64_t stream) {
         return mf_k_allreduce_rmsnorm((const mf_allreduce_args_t *)argsDev, nEmulated, rankCount, T, H, eps, algo, channel, epoch, timeoutNs, ctas,
