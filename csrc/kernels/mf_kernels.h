@@ -4,6 +4,12 @@
 #include <cstddef>
 #include <cstdint>
 
+#ifdef __CUDACC__
+#include <vector_types.h>
+#else
+struct int4;  // only pointers to it cross this interface in host code
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -71,6 +77,49 @@ enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1 };
 // groupOffset/groupCount live on the device (the routing result never visits the host). status: device int or NULL.
 int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, const float *bScale, void *out, const int *groupOffset,
                           const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas, mf_stream_t stream);
+
+// ------------------------------------------------------------------------------------------------ MoE dispatch / combine (K5a, K5c)
+
+// Per-rank argument blocks (device memory). "heap" fields must sit at the same offset of the symmetric heap on every rank.
+typedef struct {
+    const void *meta;     // MfDeviceMeta of this rank
+    const void *x;        // [T, H] bf16 tokens of this rank
+    const int *topkIdx;   // [T, K] global expert ids
+    const float *topkW;   // [T, K] renormalised routing weights
+    int *cnt;             // heap: [R][E] pair counts, row s written by rank s on every rank
+    void *recvX;          // heap: [cap][H] e4m3
+    float *recvScale;     // heap: [cap][H/128]
+    int4 *recvMeta;       // heap: [cap] {source rank, token, k, weight bits}
+    int *localCnt;        // [E] scratch, zero before the first call (the kernel leaves it zero)
+    int *cursor;          // [E] scratch, zero before the first call (the kernel leaves it zero)
+    int *expertOffset;    // out: [E/R + 1] first row of each local expert (multiples of 128); last = rows in use
+    int *expertCount;     // out: [E/R] valid rows of each local expert
+    int *sendSlot;        // out (optional): [T, K] row each pair was written to on its owner
+    int *status;          // device int, zero before launch
+    int T;
+    int cap;
+} mf_moe_dispatch_args_t;
+
+typedef struct {
+    const void *meta;
+    const void *y;            // [cap][H] bf16 expert outputs (local)
+    const int4 *recvMeta;     // as filled by dispatch (local side of the heap buffer)
+    const int *expertOffset;  // as filled by dispatch
+    const int *expertCount;
+    void *retY;               // heap: [Tmax * K][H] bf16 landing zone at the source rank
+    const float *topkW;       // [T, K]
+    void *out;                // [T, H] bf16
+    int *status;
+    int T;
+    int reserved;
+} mf_moe_combine_args_t;
+
+// H: hidden (multiple of 128), K: experts per token, E: experts in total (multiple of the rank count). Both kernels are
+// cooperative launches; epoch must grow by one per call and channel on every rank alike.
+int mf_k_moe_dispatch(const mf_moe_dispatch_args_t *argsDev, int nEmulatedRanks, int rankCount, int H, int K, int E, uint32_t channel,
+                      uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
+int mf_k_moe_combine(const mf_moe_combine_args_t *argsDev, int nEmulatedRanks, int rankCount, int H, int K, int EL, uint32_t channel,
+                     uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 
 // bf16 [rows, K] → e4m3 [rows, K] + fp32 scales [rows, K/128] (scale = amax/448 per 128 elements). rowLimit (device int,
 // may be NULL) caps the number of rows actually processed.

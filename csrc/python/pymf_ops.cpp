@@ -2,6 +2,8 @@
 // CUDA stream handle; the torch-facing wrappers live in memfabric_hybrid_b200/ops.
 #include <pybind11/stl.h>
 
+#include <cuda_runtime.h>
+
 #include "../kernels/mf_kernels.h"
 #include "pymf_parts.h"
 
@@ -40,6 +42,57 @@ void BindOps(py::module_ &m)
     ops.def("quant_rows_fp8", [](uint64_t x, uint64_t q, uint64_t scale, int rows, int K, uint64_t rowLimit, uint64_t stream) {
         return mf_k_quant_rows_fp8((const void *)x, (void *)q, (float *)scale, rows, K, (const int *)rowLimit, (mf_stream_t)stream);
     }, py::arg("x"), py::arg("q"), py::arg("scale"), py::arg("rows"), py::arg("K"), py::arg("row_limit") = 0, py::arg("stream") = 0);
+    ops.attr("MOE_DISPATCH_ARGS_BYTES") = (int)sizeof(mf_moe_dispatch_args_t);
+    ops.attr("MOE_COMBINE_ARGS_BYTES") = (int)sizeof(mf_moe_combine_args_t);
+    ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvScale,
+                                         uint64_t recvMeta, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
+                                         uint64_t sendSlot, uint64_t status, int T, int cap) {
+        mf_moe_dispatch_args_t a{};
+        a.meta = (const void *)meta;
+        a.x = (const void *)x;
+        a.topkIdx = (const int *)topkIdx;
+        a.topkW = (const float *)topkW;
+        a.cnt = (int *)cnt;
+        a.recvX = (void *)recvX;
+        a.recvScale = (float *)recvScale;
+        a.recvMeta = (int4 *)recvMeta;
+        a.localCnt = (int *)localCnt;
+        a.cursor = (int *)cursor;
+        a.expertOffset = (int *)expertOffset;
+        a.expertCount = (int *)expertCount;
+        a.sendSlot = (int *)sendSlot;
+        a.status = (int *)status;
+        a.T = T;
+        a.cap = cap;
+        return py::bytes((const char *)&a, sizeof(a));
+    });
+    ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t expertOffset, uint64_t expertCount, uint64_t retY,
+                                        uint64_t topkW, uint64_t out, uint64_t status, int T) {
+        mf_moe_combine_args_t a{};
+        a.meta = (const void *)meta;
+        a.y = (const void *)y;
+        a.recvMeta = (const int4 *)recvMeta;
+        a.expertOffset = (const int *)expertOffset;
+        a.expertCount = (const int *)expertCount;
+        a.retY = (void *)retY;
+        a.topkW = (const float *)topkW;
+        a.out = (void *)out;
+        a.status = (int *)status;
+        a.T = T;
+        return py::bytes((const char *)&a, sizeof(a));
+    });
+    ops.def("moe_dispatch", [](uint64_t argsDev, int nEmulated, int rankCount, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs,
+                               int ctas, uint64_t stream) {
+        return mf_k_moe_dispatch((const mf_moe_dispatch_args_t *)argsDev, nEmulated, rankCount, H, K, E, channel, epoch, timeoutNs, ctas,
+                                 (mf_stream_t)stream);
+    }, py::arg("args_dev"), py::arg("n_emulated"), py::arg("rank_count"), py::arg("H"), py::arg("K"), py::arg("E"), py::arg("channel"), py::arg("epoch"),
+            py::arg("timeout_ns") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
+    ops.def("moe_combine", [](uint64_t argsDev, int nEmulated, int rankCount, int H, int K, int EL, uint32_t channel, uint64_t epoch, uint64_t timeoutNs,
+                              int ctas, uint64_t stream) {
+        return mf_k_moe_combine((const mf_moe_combine_args_t *)argsDev, nEmulated, rankCount, H, K, EL, channel, epoch, timeoutNs, ctas,
+                                (mf_stream_t)stream);
+    }, py::arg("args_dev"), py::arg("n_emulated"), py::arg("rank_count"), py::arg("H"), py::arg("K"), py::arg("EL"), py::arg("channel"), py::arg("epoch"),
+            py::arg("timeout_ns") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
     ops.def("allreduce_rmsnorm", [](uint64_t argsDev, int nEmulated, int rankCount, int T, int H, float eps, int algo, uint32_t channel, uint64_t epoch,
                                     uint64_t timeoutNs, int ctas, uint64_t stream) {
         return mf_k_allreduce_rmsnorm((const mf_allreduce_args_t *)argsDev, nEmulated, rankCount, T, H, eps, algo, channel, epoch, timeoutNs, ctas,
