@@ -118,11 +118,9 @@ int MemEntity::Initialize()
     so.flags = opt_.flags;
     so.role = opt_.role;
     if (opt_.scene == SCENE_TRANS) {
-        if (opt_.devId >= 0 && cu::Available()) {
-            so.type = SEG_USER_MEM;
-            user_ = MemSegment::Create(so);
-            MF_CHECK_RET(user_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the user-memory segment");
-        }
+        so.type = SEG_USER_MEM;
+        user_ = MemSegment::Create(so);
+        MF_CHECK_RET(user_ != nullptr, BM_NEW_OBJECT_FAILED, "entity: cannot create the user-memory segment");
     } else if ((opt_.memType & MEM_TYPE_DEVICE) && opt_.maxHBMSize > 0) {
         so.type = SEG_DEVICE_VMM;
         so.windowSize = opt_.deviceVASpace != 0 ? opt_.deviceVASpace : opt_.maxHBMSize;

@@ -788,6 +788,16 @@ public:
             }
         } else {
             e.handleKind = HK_NONE;  // plain host memory of another process cannot be mapped; peers reach it through the owner
+            for (auto &kv : hostBlocks_) {
+                if (e.gva >= kv.first && e.gva + e.size <= kv.first + kv.second.size) {
+                    e.handleKind = HK_FD_HOST;
+                    e.fdToken = kv.second.token;
+                    e.fileOffset = e.gva - kv.first;
+                    e.windowSize = kv.second.size;
+                    std::strncpy(e.fdName, FdChannel::Instance().Name().c_str(), sizeof(e.fdName) - 1);
+                    break;
+                }
+            }
         }
         blob->assign((const char *)&e, sizeof(e));
         return BM_OK;
@@ -815,6 +825,27 @@ public:
     }
 
     int Mmap() override { return BM_OK; }
+
+    int AdoptHostBlock(uint64_t addr, uint64_t size, int fd) override
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        uint64_t token = FdChannel::Instance().Publish(fd);
+        MF_CHECK_RET(token != 0, BM_ERROR, "user segment: cannot publish the host block");
+        hostBlocks_[addr] = HostBlock{size, token};
+        return BM_OK;
+    }
+
+    int DropHostBlock(uint64_t addr) override
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = hostBlocks_.find(addr);
+        if (it == hostBlocks_.end()) {
+            return BM_INVALID_PARAM;
+        }
+        FdChannel::Instance().Unpublish(it->second.token);
+        hostBlocks_.erase(it);
+        return BM_OK;
+    }
 
     int RemoveImported(const std::vector<uint32_t> &ranks) override
     {
@@ -851,7 +882,13 @@ private:
         uint64_t mappedSize;
         uint64_t local;       // alias of the registered range
         uint64_t size;
+        uint64_t remoteBlock{0};  // owner-side start of the host block (HK_FD_HOST)
     };
+    struct HostBlock {
+        uint64_t size;
+        uint64_t token;
+    };
+    std::map<uint64_t, HostBlock> hostBlocks_;
 
     int Open(const SliceExport &e, uint64_t *local)
     {
@@ -863,7 +900,7 @@ private:
             return BM_OK;
         }
         MF_CHECK_RET(HostIdentity() == e.hostId, BM_NOT_SUPPORTED, "user segment: rank " << e.rank << " is on another host");
-        Opened o{e.rank, e.handleKind, 0, 0, 0, e.size};
+        Opened o{e.rank, e.handleKind, 0, 0, 0, e.size, 0};
         if (e.handleKind == HK_CUDA_IPC) {
             cudaSetDevice(opt_.devId);
             // An allocation may carry several registrations: open it once.
@@ -910,6 +947,34 @@ private:
             o.mappedBase = (uint64_t)va;
             o.mappedSize = sz;
             o.local = o.mappedBase + e.fileOffset;
+        } else if (e.handleKind == HK_FD_HOST) {
+            // One mapping per (rank, block): registrations inside the same block share it.
+            const uint64_t blockBase = e.gva - e.fileOffset;
+            for (auto &kv : opened_) {
+                if (kv.second.rank == e.rank && kv.second.kind == HK_FD_HOST && kv.second.remoteBlock == blockBase) {
+                    o.mappedBase = kv.second.mappedBase;
+                    o.mappedSize = kv.second.mappedSize;
+                    break;
+                }
+            }
+            if (o.mappedBase == 0) {
+                int fd = FdChannel::Fetch(e.fdName, e.fdToken);
+                MF_CHECK_RET(fd >= 0, BM_ERROR, "user segment: cannot fetch the host block of rank " << e.rank);
+                void *p = ::mmap(nullptr, e.windowSize, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+                int err = errno;
+                ::close(fd);
+                MF_CHECK_RET(p != MAP_FAILED, BM_ERROR, "user segment: mapping the host block failed: " << strerror(err));
+                if (opt_.devId >= 0 && cu::Available()) {
+                    cudaSetDevice(opt_.devId);
+                    if (cudaHostRegister(p, e.windowSize, cudaHostRegisterPortable | cudaHostRegisterMapped) != cudaSuccess) {
+                        (void)cudaGetLastError();
+                    }
+                }
+                o.mappedBase = (uint64_t)p;
+                o.mappedSize = e.windowSize;
+            }
+            o.remoteBlock = blockBase;
+            o.local = o.mappedBase + e.fileOffset;
         } else {
             MF_ERROR("user segment: rank " << e.rank << " registered memory that cannot be mapped here (plain host memory)");
             return BM_NOT_SUPPORTED;
@@ -936,6 +1001,18 @@ private:
             if (d != nullptr) {
                 d->MemUnmap((CUdeviceptr)o.mappedBase, o.mappedSize);
                 d->MemAddressFree((CUdeviceptr)o.mappedBase, o.mappedSize);
+            }
+        } else if (o.kind == HK_FD_HOST) {
+            int users = 0;
+            for (auto &kv : opened_) {
+                users += kv.second.kind == HK_FD_HOST && kv.second.mappedBase == o.mappedBase;
+            }
+            if (users <= 1) {
+                if (cu::Available()) {
+                    cudaHostUnregister((void *)o.mappedBase);
+                    (void)cudaGetLastError();
+                }
+                ::munmap((void *)o.mappedBase, o.mappedSize);
             }
         }
     }

@@ -26,7 +26,7 @@ namespace mf {
 namespace hybm {
 
 enum SegmentType : uint32_t { SEG_DEVICE_VMM = 1, SEG_HOST_SHM = 2, SEG_USER_MEM = 3 };
-enum HandleKind : uint32_t { HK_NONE = 0, HK_FD_CHANNEL = 1, HK_CUDA_IPC = 2, HK_FD_VMM_RETAINED = 3 };
+enum HandleKind : uint32_t { HK_NONE = 0, HK_FD_CHANNEL = 1, HK_CUDA_IPC = 2, HK_FD_VMM_RETAINED = 3, HK_FD_HOST = 4 };
 
 constexpr uint32_t SLICE_EXPORT_MAGIC = 0x4D465345u;   // "MFSE"
 constexpr uint32_t ENTITY_EXPORT_MAGIC = 0x4D464545u;  // "MFEE"
@@ -97,6 +97,10 @@ public:
     virtual int Mmap() = 0;
     virtual int RemoveImported(const std::vector<uint32_t> &ranks) = 0;
     virtual int Unmap() = 0;
+    // User-memory segments only: declares [addr, addr+size) as host memory backed by the shareable file `fd` (duplicated),
+    // so that later registrations inside it can be exported to peers.
+    virtual int AdoptHostBlock(uint64_t /*addr*/, uint64_t /*size*/, int /*fd*/) { return BM_NOT_SUPPORTED; }
+    virtual int DropHostBlock(uint64_t /*addr*/) { return BM_NOT_SUPPORTED; }
     virtual uint32_t MemTypeBit() const = 0;
     // True if GPU kernels on the local device can dereference addresses of this segment.
     virtual bool DeviceAccessible() const = 0;

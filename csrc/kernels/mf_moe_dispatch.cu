@@ -59,7 +59,9 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     const int nblk = H / 128;
     extern __shared__ unsigned char smem[];
     int *sendBase = reinterpret_cast<int *>(smem);                              // [E]
-    unsigned char *stage = smem + (size_t)kMaxExperts * sizeof(int);            // per warp: H bytes fp8 + nblk floats
+    int *totals = sendBase + kMaxExperts;                                       // [E] pairs per expert over all sources
+    int *starts = totals + kMaxExperts;                                         // [E] first row of the expert on its owner
+    unsigned char *stage = smem + (size_t)3 * kMaxExperts * sizeof(int);        // per warp: H bytes fp8 + nblk floats
     const size_t stagePerWarp = (size_t)H + (size_t)nblk * 4;
     __shared__ int abortFlag;
 
@@ -89,37 +91,42 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     const bool dead = ReadAbort(a.status, &abortFlag) != 0;
 
     if (!dead) {
-        // ---- (b) where my pairs land: sendBase[e] = start of expert e on its owner + pairs of lower ranks for e
+        // ---- (b) where my pairs land: sendBase[e] = start of expert e on its owner + pairs of lower ranks for e.
+        // Column sums of the count matrix first (one expert per thread, R loads each), then short prefix walks in shared memory.
         for (int e = threadIdx.x; e < E; e += kThreads) {
-            const int d = e / EL;
-            int start = 0;
-            for (int e2 = d * EL; e2 < e; e2++) {
-                int tot = 0;
-                for (int s = 0; s < R; s++) {
-                    tot += ((volatile int *)a.cnt)[s * E + e2];
-                }
-                start += (tot + 127) & ~127;
+            int tot = 0, before = 0;
+            for (int s = 0; s < R; s++) {
+                const int c = ((volatile int *)a.cnt)[s * E + e];
+                tot += c;
+                before += s < me ? c : 0;
             }
-            int before = 0;
-            for (int s = 0; s < me; s++) {
-                before += ((volatile int *)a.cnt)[s * E + e];
-            }
-            sendBase[e] = start + before;
+            totals[e] = tot;
+            sendBase[e] = before;
         }
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            int off = 0;
-            for (int el = 0; el < EL; el++) {
-                int tot = 0;
-                for (int s = 0; s < R; s++) {
-                    tot += ((volatile int *)a.cnt)[s * E + me * EL + el];
-                }
-                a.expertOffset[el] = off;
-                a.expertCount[el] = tot;
-                off += (tot + 127) & ~127;
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += kThreads) {
+            int start = 0;
+            for (int e2 = (e / EL) * EL; e2 < e; e2++) {
+                start += (totals[e2] + 127) & ~127;
             }
-            a.expertOffset[EL] = off;
-            if (off > a.cap) {
-                FailD(a.status, MF_DEV_ERR_BOUNDS);
+            starts[e] = start;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += kThreads) {
+            sendBase[e] += starts[e];
+        }
+        if (blockIdx.x == 0) {
+            for (int el = threadIdx.x; el < EL; el += kThreads) {
+                a.expertOffset[el] = starts[me * EL + el];
+                a.expertCount[el] = totals[me * EL + el];
+            }
+            if (threadIdx.x == 0) {
+                const int last = me * EL + EL - 1;
+                const int off = starts[last] + ((totals[last] + 127) & ~127);
+                a.expertOffset[EL] = off;
+                if (off > a.cap) {
+                    FailD(a.status, MF_DEV_ERR_BOUNDS);
+                }
             }
         }
         __syncthreads();
@@ -328,7 +335,7 @@ extern "C" int mf_k_moe_dispatch(const mf_moe_dispatch_args_t *argsDev, int nEmu
     if (timeoutNs == 0) {
         timeoutNs = 2000000000ull;
     }
-    const size_t smem = (size_t)kMaxExperts * sizeof(int) + (size_t)kWarps * ((size_t)H + (size_t)(H / 128) * 4);
+    const size_t smem = (size_t)3 * kMaxExperts * sizeof(int) + (size_t)kWarps * ((size_t)H + (size_t)(H / 128) * 4);
     static size_t attrSmem = 0;
     if (smem > attrSmem) {
         if (cudaFuncSetAttribute(mf_moe_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

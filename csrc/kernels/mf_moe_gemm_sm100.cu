@@ -34,7 +34,7 @@ constexpr int kThreads = 320;
 constexpr int kAccBufs = 4;                      // TMEM accumulator buffers (128 columns each)
 constexpr int kEpiThreads = 256;                 // warps 2-9
 constexpr int kTileBytes = BM * BK;  // fp8: 16 KiB per operand tile
-constexpr int kMaxGroups = 64;
+constexpr int kMaxGroups = 256;
 constexpr uint32_t kTmemCols = 512;
 
 struct SharedStorage {
@@ -100,10 +100,16 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
     volatile int *abortFlag = &s.abortFlag;
 
     auto decode = [&](int tile, int &g, int &mt, int &nt) {
-        g = 0;
-        while (g + 1 < p.G && s.tilePrefix[g + 1] <= tile) {
-            g++;
+        int lo = 0, hi = p.G;  // last group whose first tile is <= tile (empty groups share a prefix value: take the last)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s.tilePrefix[mid] <= tile) {
+                lo = mid;
+            } else {
+                hi = mid;
+            }
         }
+        g = lo;
         const int local = tile - s.tilePrefix[g];
         mt = local / NT;
         nt = local % NT;
