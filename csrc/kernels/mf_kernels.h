@@ -121,6 +121,38 @@ int mf_k_moe_dispatch(const mf_moe_dispatch_args_t *argsDev, int nEmulatedRanks,
 int mf_k_moe_combine(const mf_moe_combine_args_t *argsDev, int nEmulatedRanks, int rankCount, int H, int K, int EL, uint32_t channel,
                      uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 
+// ------------------------------------------------------------------------------------------------ weight reshard (K6)
+
+// One destination sub-block: rows [r0, r0+nrows) x columns [c0, c0+ncols) of a row-major parameter with colsFull columns
+// that starts at element srcFlatOff of the flat training vector. All of srcFlatOff, colsFull, c0 and ncols must be
+// multiples of 8 elements. quant = 1 casts to e4m3 with one fp32 scale per 128x128 tile (nrows, ncols multiples of 128).
+typedef struct {
+    uint64_t srcFlatOff;
+    uint64_t dstOff;    // BYTE offset of the sub-block in the destination buffer (row-major, ncols columns)
+    uint64_t scaleOff;  // first scale of the sub-block in the scale buffer (floats), row-major over tiles
+    uint32_t colsFull;
+    uint32_t r0, c0;
+    uint32_t nrows, ncols;
+    uint32_t tileStart;  // prefix sum of ceil(nrows/128) * ceil(ncols/128) over the table
+    uint32_t quant;
+    uint32_t pad;
+} mf_reshard_desc_t;
+
+typedef struct {
+    const void *meta;
+    const void *srcShard;  // heap: this rank's shard of the flat bf16 vector (same offset on every rank)
+    void *dst;             // local destination buffer
+    float *dstScale;       // local scale buffer (may be NULL if nothing is quantised)
+    const mf_reshard_desc_t *descs;  // device table
+    int *status;
+    uint64_t shardElems;   // elements per shard (multiple of 8)
+    uint32_t ndesc;
+    uint32_t totalTiles;
+} mf_reshard_args_t;
+
+int mf_k_reshard(const mf_reshard_args_t *argsDev, int nEmulatedRanks, int rankCount, uint32_t channel, uint64_t epoch, uint64_t timeoutNs,
+                 int ctas, mf_stream_t stream);
+
 // bf16 [rows, K] → e4m3 [rows, K] + fp32 scales [rows, K/128] (scale = amax/448 per 128 elements). rowLimit (device int,
 // may be NULL) caps the number of rows actually processed.
 int mf_k_quant_rows_fp8(const void *x, void *q, float *scale, int rows, int K, const int *rowLimit, mf_stream_t stream);

@@ -93,6 +93,31 @@ void BindOps(py::module_ &m)
                                 (mf_stream_t)stream);
     }, py::arg("args_dev"), py::arg("n_emulated"), py::arg("rank_count"), py::arg("H"), py::arg("K"), py::arg("EL"), py::arg("channel"), py::arg("epoch"),
             py::arg("timeout_ns") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
+    ops.attr("RESHARD_DESC_BYTES") = (int)sizeof(mf_reshard_desc_t);
+    ops.attr("RESHARD_ARGS_BYTES") = (int)sizeof(mf_reshard_args_t);
+    ops.def("pack_reshard_desc", [](uint64_t srcFlatOff, uint64_t dstOff, uint64_t scaleOff, uint32_t colsFull, uint32_t r0, uint32_t c0, uint32_t nrows,
+                                    uint32_t ncols, uint32_t tileStart, uint32_t quant) {
+        mf_reshard_desc_t d{srcFlatOff, dstOff, scaleOff, colsFull, r0, c0, nrows, ncols, tileStart, quant, 0};
+        return py::bytes((const char *)&d, sizeof(d));
+    });
+    ops.def("pack_reshard_args", [](uint64_t meta, uint64_t srcShard, uint64_t dst, uint64_t dstScale, uint64_t descs, uint64_t status, uint64_t shardElems,
+                                    uint32_t ndesc, uint32_t totalTiles) {
+        mf_reshard_args_t a{};
+        a.meta = (const void *)meta;
+        a.srcShard = (const void *)srcShard;
+        a.dst = (void *)dst;
+        a.dstScale = (float *)dstScale;
+        a.descs = (const mf_reshard_desc_t *)descs;
+        a.status = (int *)status;
+        a.shardElems = shardElems;
+        a.ndesc = ndesc;
+        a.totalTiles = totalTiles;
+        return py::bytes((const char *)&a, sizeof(a));
+    });
+    ops.def("reshard", [](uint64_t argsDev, int nEmulated, int rankCount, uint32_t channel, uint64_t epoch, uint64_t timeoutNs, int ctas, uint64_t stream) {
+        return mf_k_reshard((const mf_reshard_args_t *)argsDev, nEmulated, rankCount, channel, epoch, timeoutNs, ctas, (mf_stream_t)stream);
+    }, py::arg("args_dev"), py::arg("n_emulated"), py::arg("rank_count"), py::arg("channel"), py::arg("epoch"), py::arg("timeout_ns") = 0,
+            py::arg("ctas") = 0, py::arg("stream") = 0);
     ops.def("allreduce_rmsnorm", [](uint64_t argsDev, int nEmulated, int rankCount, int T, int H, float eps, int algo, uint32_t channel, uint64_t epoch,
                                     uint64_t timeoutNs, int ctas, uint64_t stream) {
         return mf_k_allreduce_rmsnorm((const mf_allreduce_args_t *)argsDev, nEmulated, rankCount, T, H, eps, algo, channel, epoch, timeoutNs, ctas,
