@@ -288,13 +288,12 @@ __global__ void mf_quant_rows_fp8_kernel(const __nv_bfloat16 *__restrict__ x, un
         for (int o = 8; o > 0; o >>= 1) {
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         }
-        const float sc = fmaxf(amax, 1e-10f) / 448.f;
-        const float inv = 1.f / sc;
+        const float sc = fmaxf(amax, 1e-10f) * (1.f / 448.f);
         uint2 packed;
         unsigned short *ps = reinterpret_cast<unsigned short *>(&packed);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            ps[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+            ps[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] / sc, f[2 * i + 1] / sc), __NV_SATFINITE, __NV_E4M3);
         }
         *reinterpret_cast<uint2 *>(q + off) = packed;
         if ((lane & 15) == 0) {

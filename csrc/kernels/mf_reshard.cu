@@ -104,8 +104,7 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                     tmax = fmaxf(tmax, warpMax[w]);
                 }
                 __syncthreads();
-                const float sc = fmaxf(tmax, 1e-10f) / 448.f;
-                const float inv = 1.f / sc;
+                const float sc = fmaxf(tmax, 1e-10f) * (1.f / 448.f);
                 unsigned char *dst = reinterpret_cast<unsigned char *>(a.dst) + d.dstOff;
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
@@ -118,7 +117,7 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             float2 f = __bfloat1622float2(h[q]);
-                            ps[q] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+                            ps[q] = __nv_cvt_float2_to_fp8x2(make_float2(f.x / sc, f.y / sc), __NV_SATFINITE, __NV_E4M3);
                         }
                         *reinterpret_cast<uint2 *>(dst + (size_t)r * d.ncols + c) = pk;
                     }
