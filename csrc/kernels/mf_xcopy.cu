@@ -321,3 +321,98 @@ extern "C" unsigned long long mf_k_checksum_host(const void *buf, size_t n)
     }
     return acc;
 }
+
+// ---------------------------------------------------------------------------------------------- batch copy without any allocation
+// See mf_xcopy_noalloc.h. The descriptor table, the chunk map and the completion counter of this variant live in the array
+// below instead of in memory obtained from cudaMalloc. Every GPU that loads the library carries the array until exit.
+#include "mf_xcopy_noalloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+constexpr size_t kNoAllocHeader = 256;  // completion counter, padded so that the table stays 256-byte aligned
+constexpr size_t kNoAllocBytes =
+    kNoAllocHeader + (size_t)MF_NOALLOC_MAX_COPIES * sizeof(mf_copy_desc_t) + (size_t)MF_NOALLOC_MAX_CHUNKS * sizeof(uint32_t);
+
+static __device__ __align__(256) unsigned char g_noAllocScratch[kNoAllocBytes];
+
+// Host-side mirror of what is sent to the device. Static storage: the entry point must not touch the heap either.
+mf_copy_desc_t g_noAllocDescs[MF_NOALLOC_MAX_COPIES];
+uint32_t g_noAllocMap[MF_NOALLOC_MAX_CHUNKS];
+std::mutex g_noAllocMu;
+void *g_noAllocDevPtr[64] = {nullptr};  // device address of g_noAllocScratch, per device ordinal
+
+}  // namespace
+
+extern "C" int mf_batch_xcopy_noalloc(const uint64_t *srcs, const uint64_t *dsts, const uint64_t *sizes, uint32_t count, void *stream)
+{
+    if (count == 0) {
+        return MF_K_OK;
+    }
+    if (srcs == nullptr || dsts == nullptr || sizes == nullptr) {
+        fprintf(stderr, "mf_batch_xcopy_noalloc: null array\n");
+        return MF_K_INVALID;
+    }
+    if (count > MF_NOALLOC_MAX_COPIES) {
+        fprintf(stderr, "mf_batch_xcopy_noalloc: %u copies exceed the fixed limit of %d per call\n", count, (int)MF_NOALLOC_MAX_COPIES);
+        return MF_K_TOO_LARGE;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return MF_K_LAUNCH_FAILED;
+    }
+    std::lock_guard<std::mutex> g(g_noAllocMu);
+    // In host code the array's name is only a handle for the runtime, not an address a kernel can use: ask the runtime
+    // for the device address once per device, with that device current.
+    if (g_noAllocDevPtr[dev] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noAllocScratch);
+        if (e != cudaSuccess || p == nullptr) {
+            fprintf(stderr, "mf_batch_xcopy_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            (void)cudaGetLastError();
+            return MF_K_LAUNCH_FAILED;
+        }
+        g_noAllocDevPtr[dev] = p;
+    }
+    unsigned char *base = static_cast<unsigned char *>(g_noAllocDevPtr[dev]);
+    uint64_t chunks = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        if (sizes[i] == 0 || sizes[i] >= (1ull << 32) || srcs[i] == 0 || dsts[i] == 0) {
+            fprintf(stderr, "mf_batch_xcopy_noalloc: copy %u has a null address or a size outside 1 .. 4 GiB-1\n", i);
+            return MF_K_INVALID;
+        }
+        const uint64_t n = (sizes[i] + MF_BATCH_CHUNK_BYTES - 1) / MF_BATCH_CHUNK_BYTES;
+        if (chunks + n > MF_NOALLOC_MAX_CHUNKS) {
+            fprintf(stderr, "mf_batch_xcopy_noalloc: the batch needs more than %d chunks of %d bytes (about %d MiB in total)\n",
+                    (int)MF_NOALLOC_MAX_CHUNKS, (int)MF_BATCH_CHUNK_BYTES, (int)((uint64_t)MF_NOALLOC_MAX_CHUNKS * MF_BATCH_CHUNK_BYTES >> 20));
+            return MF_K_TOO_LARGE;
+        }
+        g_noAllocDescs[i] = mf_copy_desc_t{srcs[i], dsts[i], (uint32_t)sizes[i], (uint32_t)chunks};
+        for (uint64_t c = 0; c < n; c++) {
+            g_noAllocMap[chunks + c] = i;
+        }
+        chunks += n;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t descBytes = (size_t)count * sizeof(mf_copy_desc_t);
+    // The array keeps whatever the previous call left in it: the counter has to start at zero, the table and the map are
+    // overwritten for exactly the part this call uses.
+    if (cudaMemsetAsync(base, 0, kNoAllocHeader, s) != cudaSuccess ||
+        cudaMemcpyAsync(base + kNoAllocHeader, g_noAllocDescs, descBytes, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+        cudaMemcpyAsync(base + kNoAllocHeader + descBytes, g_noAllocMap, (size_t)chunks * sizeof(uint32_t), cudaMemcpyHostToDevice, s) != cudaSuccess) {
+        fprintf(stderr, "mf_batch_xcopy_noalloc: staging the copy table failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+        return MF_K_LAUNCH_FAILED;
+    }
+    const int sms = SmCount();
+    if (sms <= 0) {
+        return MF_K_LAUNCH_FAILED;
+    }
+    const unsigned maxCtas = (unsigned)sms * 2;
+    const unsigned grid = chunks < maxCtas ? (unsigned)chunks : maxCtas;
+    mf_batch_xcopy_table_kernel<<<grid, kThreads, 0, s>>>(reinterpret_cast<const mf_copy_desc_t *>(base + kNoAllocHeader), count, (uint32_t)chunks,
+                                                         reinterpret_cast<uint32_t *>(base), nullptr, 0);
+    return LaunchResult();
+}
