@@ -20,6 +20,35 @@ static const char *kExitKey = "EXIT";
 static const char *kNumbersKey = "NUMBERS";
 static constexpr uint64_t kVerOne = 1ull << 30;
 
+static const char *kMembersKey = "MEMBERS";
+
+static std::string EncodeMembers(const std::bitset<GROUP_RANK_MAX> &m)
+{
+    std::string out;
+    for (uint32_t i = 0; i < GROUP_RANK_MAX; i++) {
+        if (m.test(i)) {
+            out += std::to_string(i) + ",";
+        }
+    }
+    return out;
+}
+
+static void DecodeMembers(const std::string &s, std::bitset<GROUP_RANK_MAX> *m)
+{
+    size_t pos = 0;
+    while (pos < s.size()) {
+        size_t comma = s.find(',', pos);
+        if (comma == std::string::npos) {
+            break;
+        }
+        uint32_t r = (uint32_t)std::strtoul(s.substr(pos, comma - pos).c_str(), nullptr, 10);
+        if (r < GROUP_RANK_MAX) {
+            m->set(r);
+        }
+        pos = comma + 1;
+    }
+}
+
 static int MapStoreCode(int rc)
 {
     if (rc == ST_OK) {
@@ -381,6 +410,8 @@ void GroupEngine::HandleEvent(const std::string &value)
                 MF_ERROR("group: join callback for rank " << rank << " failed rc=" << rc);
             }
         }
+        int64_t acks = 0;
+        store_->Add("EVACK_" + nonce, 1, &acks);  // the joiner keeps the event up until every member has seen it
     } else if (kind == 'L') {
         bool member;
         {
@@ -442,6 +473,8 @@ void GroupEngine::HandleRankDown(uint32_t rank)
         if (store_->Cas(key, "", "1", &prev) == ST_OK && prev.empty()) {
             int64_t nv = 0;
             store_->Add(kSizeKey, (int64_t)kVerOne - 1, &nv);
+            std::lock_guard<std::mutex> g(memberMu_);
+            store_->Set(kMembersKey, EncodeMembers(members_));
         }
     }
 }
@@ -455,7 +488,8 @@ int GroupEngine::GroupJoin()
         return GR_OK;
     }
     StartListenEvent();
-    const std::string mine = "J" + std::to_string(opt_.rank) + ":" + std::to_string(NowNs());
+    const std::string joinNonce = std::to_string(NowNs());
+    const std::string mine = "J" + std::to_string(opt_.rank) + ":" + joinNonce;
     uint64_t deadline = NowMs() + opt_.timeoutMs;
     while (true) {
         std::string prev;
@@ -481,8 +515,12 @@ int GroupEngine::GroupJoin()
     uint32_t ver = 0, size = 0;
     UnpackVerSize((uint64_t)packed, &ver, &size);
     {
+        std::string stored;
         std::lock_guard<std::mutex> g(memberMu_);
         members_.reset();
+        if (store_->Get(kMembersKey, &stored, 0) == ST_OK) {
+            DecodeMembers(stored, &members_);  // who is in already (the event key serialises writers of this list)
+        }
         members_.set(opt_.rank);
         size_.store(size + 1);
         version_.store(ver + 1);
@@ -492,7 +530,21 @@ int GroupEngine::GroupJoin()
     int cbRc = opt_.joinCb ? opt_.joinCb(opt_.rank) : 0;
     int64_t nv = 0;
     if (cbRc == 0) {
+        // Every existing member must have seen the event before it is retired, or a quick join could go unnoticed.
+        uint64_t until = NowMs() + opt_.timeoutMs;
+        while (size > 0 && NowMs() < until) {
+            std::string acks;
+            if (store_->Get("EVACK_" + joinNonce, &acks, 0) == ST_OK && std::strtoul(acks.c_str(), nullptr, 10) >= size) {
+                break;
+            }
+            usleep(1000);
+        }
+        {
+            std::lock_guard<std::mutex> g(memberMu_);
+            store_->Set(kMembersKey, EncodeMembers(members_));
+        }
         store_->Add(kSizeKey, (int64_t)(kVerOne | 1), &nv);
+        store_->Remove("EVACK_" + joinNonce, true);
         store_->Remove(kEventKey, true);
         return GR_OK;
     }
@@ -551,14 +603,16 @@ int GroupEngine::GroupLeave()
         usleep(2000);
     }
     int64_t nv = 0;
-    store_->Add(kSizeKey, (int64_t)kVerOne - 1, &nv);
-    store_->Remove("EVACK_" + nonce, true);
-    store_->Remove(kEventKey, true);
     {
         std::lock_guard<std::mutex> g(memberMu_);
+        members_.reset(opt_.rank);
+        store_->Set(kMembersKey, EncodeMembers(members_));
         members_.reset();
         size_.store(0);
     }
+    store_->Add(kSizeKey, (int64_t)kVerOne - 1, &nv);
+    store_->Remove("EVACK_" + nonce, true);
+    store_->Remove(kEventKey, true);
     return GR_OK;
 }
 

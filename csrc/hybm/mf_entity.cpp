@@ -461,12 +461,8 @@ uint32_t MemEntity::ReachTypes(uint32_t rank)
 
 bool MemEntity::AddressInEntity(uint64_t addr, uint64_t len)
 {
-    if (hbm_ && hbm_->InWindow(addr, len)) {
-        return true;
-    }
-    if (dram_ && dram_->InWindow(addr, len)) {
-        return true;
-    }
+    // Window arithmetic is not enough: a rank that left (or died) leaves a hole in the window. Only ranges that are
+    // backed right now — local slices, mapped peers, registered user memory — count.
     AllocatedRange a;
     return VaManager::Instance().FindAllocated(addr, len, &a) && a.entityId == id_;
 }

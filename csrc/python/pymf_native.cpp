@@ -5,11 +5,15 @@
 #include <pybind11/stl.h>
 
 #include <cstring>
+#include <map>
 
 #include "../group/mf_group.h"
 #include "../hybm/mf_cuda.h"
 #include "../hybm/mf_data_op.h"
+#include "../hybm/mf_range_pool.h"
 #include "../hybm/mf_tag_info.h"
+#include "../util/mf_log.h"
+#include "../util/mf_tracer.h"
 #include "../hybm/mf_va_manager.h"
 #include "../kernels/mf_kernels.h"
 #include "../net/mf_rpc.h"
@@ -310,6 +314,29 @@ void BindNative(py::module_ &m)
             return py::none();
         }
         return py::make_tuple(idx, mt);
+    });
+
+    py::class_<hybm::RangePool>(n, "RangePool")
+        .def(py::init<uint64_t, uint64_t, uint64_t>(), py::arg("base"), py::arg("size"), py::arg("align") = 256)
+        .def("allocate", &hybm::RangePool::Allocate)
+        .def("release", &hybm::RangePool::Release)
+        .def("in_use", &hybm::RangePool::InUse)
+        .def("capacity", &hybm::RangePool::Capacity)
+        .def("largest_free", &hybm::RangePool::LargestFree)
+        .def("free_blocks", &hybm::RangePool::FreeBlocks);
+    n.def("trace_point", [](int tp, const std::string &name, int ret, uint64_t busyNs) {
+        // Records one begin/end pair on tracepoint `tp` (test hook for the aggregate tracer).
+        static std::map<int, std::string> names;
+        auto it = names.emplace(tp, name).first;
+        Tracer::Instance().Begin(tp, it->second.c_str());
+        Tracer::Instance().End(tp, NowNs() - busyNs, ret);
+    });
+    n.def("trace_query", [](int tp) -> py::object {
+        uint64_t v[4];
+        if (!Tracer::Instance().Query(tp, v)) {
+            return py::none();
+        }
+        return py::make_tuple(v[0], v[1], v[2], v[3]);
     });
 
     py::class_<hybm::TagInfo, std::shared_ptr<hybm::TagInfo>>(n, "TagInfo")

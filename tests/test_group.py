@@ -1,0 +1,213 @@
+"""Group engine over a loopback store: barrier, allgather (world and keyed subgroups), dynamic join/leave with callbacks,
+rank death, number allocation, exit broadcast. Ranks are threads of this process with one store client each (the engine
+only talks to the store), plus one multi-process churn test. Scenarios follow the reference's group tests
+(test/ut/testcase/smem/smem_bm_test.cpp:209-416 for the fork-based pattern)."""
+import multiprocessing as mp
+import threading
+import time
+
+import pytest
+
+from conftest import free_port
+
+
+class Cluster:
+    def __init__(self, mf, port, n):
+        self.n = mf.native
+        self.server = self.n.StoreServer()
+        assert self.server.start("127.0.0.1", port) == 0
+        self.port = port
+        self.clients = []
+
+    def client(self, rank, world):
+        c = self.n.TcpStore("127.0.0.1", self.port, False, world, rank)
+        assert c.startup(5, 100) == 0
+        self.clients.append(c)
+        return c
+
+    def close(self):
+        for c in self.clients:
+            c.shutdown()
+        self.server.stop()
+
+
+@pytest.fixture
+def cluster(mf, port):
+    c = Cluster(mf, port, 0)
+    yield c
+    c.close()
+
+
+def _run(fns):
+    out = [None] * len(fns)
+
+    def wrap(i):
+        out[i] = fns[i]()
+
+    ts = [threading.Thread(target=wrap, args=(i,)) for i in range(len(fns))]
+    [t.start() for t in ts]
+    [t.join(30) for t in ts]
+    assert not any(t.is_alive() for t in ts), "a rank is stuck"
+    return out
+
+
+def test_static_barrier_and_allgather(mf, cluster):
+    W = 4
+    engines = [mf.native.GroupEngine(cluster.client(r, W), W, r, 10000) for r in range(W)]
+    for _ in range(5):  # more than two rounds: old keys get garbage-collected on the way
+        assert _run([e.barrier for e in engines]) == [0] * W
+    res = _run([lambda r=r: engines[r].allgather(bytes([r]) * 3) for r in range(W)])
+    for rc, data in res:
+        assert rc == 0 and data == b"".join(bytes([r]) * 3 for r in range(W))
+    # keys of finished rounds do not pile up in the store
+    assert cluster.server.size() < 16
+
+
+def test_barrier_times_out_when_a_rank_is_missing(mf, cluster):
+    e0 = mf.native.GroupEngine(cluster.client(0, 2), 2, 0, 300)
+    t0 = time.time()
+    assert e0.barrier() == -2004  # timeout, not a hang
+    assert time.time() - t0 < 5
+
+
+def test_subgroups(mf, cluster):
+    W = 4
+    engines = [mf.native.GroupEngine(cluster.client(r, W), W, r, 10000) for r in range(W)]
+    # two disjoint pairs under different keys, concurrently
+    fns = [lambda r=r: engines[r].subgroup_allgather(f"pair{r // 2}", 2, r % 2, bytes([10 + r])) for r in range(W)]
+    res = _run(fns)
+    assert res[0] == (0, bytes([10, 11])) and res[1] == (0, bytes([10, 11]))
+    assert res[2] == (0, bytes([12, 13])) and res[3] == (0, bytes([12, 13]))
+    assert _run([lambda r=r: engines[r].subgroup_barrier("all", W, r) for r in range(W)]) == [0] * W
+    assert engines[0].subgroup_barrier("", 2, 0) != 0 and engines[0].subgroup_barrier("k", 2, 5) != 0
+
+
+def test_alloc_numbers_are_unique_and_reusable(mf, cluster):
+    W = 3
+    engines = [mf.native.GroupEngine(cluster.client(r, W), W, r, 10000) for r in range(W)]
+    got = _run([lambda e=e: [e.alloc_number(8)[1] for _ in range(2)] for e in engines])
+    flat = sorted(x for g in got for x in g)
+    assert flat == list(range(6))
+    assert engines[0].release_number(3) == 0
+    assert engines[1].alloc_number(8) == (0, 3)
+    assert engines[2].alloc_number(6)[0] != 0 or True  # 6,7 still free under limit 8; limit 6 is exhausted
+    assert engines[2].alloc_number(6)[0] != 0
+    assert engines[0].alloc_number(0)[0] != 0 and engines[0].alloc_number(2000)[0] != 0
+
+
+def test_exit_broadcast(mf, cluster):
+    W = 2
+    engines = [mf.native.GroupEngine(cluster.client(r, W), W, r, 10000) for r in range(W)]
+    seen = []
+    assert engines[1].register_exit(lambda s: seen.append(s)) == 0
+    assert engines[0].broadcast_exit(7) == 0
+    deadline = time.time() + 3
+    while not seen and time.time() < deadline:
+        time.sleep(0.01)
+    assert seen == [7]
+
+
+def test_dynamic_join_leave_callbacks(mf, cluster):
+    W = 3
+    log = {r: [] for r in range(W)}
+    engines = {}
+
+    def make(r):
+        def on_join(rank, r=r):
+            log[r].append(("J", rank))
+            rc, data = engines[r].allgather(bytes([r]))  # the callbacks of all members line up
+            return 0 if rc == 0 else 1
+
+        def on_leave(rank, r=r):
+            log[r].append(("L", rank))
+            return 0
+
+        engines[r] = mf.native.GroupEngine(cluster.client(r, W), W, r, 10000, True, on_join, on_leave)
+        engines[r].start_listen()
+
+    for r in range(W):
+        make(r)
+    assert not engines[0].joined() and engines[0].barrier() == -2003  # not started
+    assert engines[0].join() == 0
+    assert engines[0].rank_size() == 1 and engines[0].members() == [0]
+    assert engines[1].join() == 0
+    assert engines[2].join() == 0
+    time.sleep(0.2)
+    for r in range(W):
+        assert engines[r].rank_size() == 3 and engines[r].members() == [0, 1, 2], (r, engines[r].members())
+    assert log[0] == [("J", 0), ("J", 1), ("J", 2)]
+    assert log[1] == [("J", 1), ("J", 2)] and log[2] == [("J", 2)]
+    assert _run([engines[r].barrier for r in range(W)]) == [0] * W
+    v = engines[0].version()
+    assert engines[1].leave() == 0
+    time.sleep(0.3)
+    assert engines[0].members() == [0, 2] and engines[2].members() == [0, 2]
+    assert ("L", 1) in log[0] and ("L", 1) in log[2]
+    assert engines[0].version() > v
+    assert _run([engines[0].barrier, engines[2].barrier]) == [0, 0]
+    # the shared (version,size) counter follows: 3 joins + 1 leave = version 4, size 2
+    rc, packed = cluster.clients[0].add("DSIZE", 0)
+    assert rc == 0 and packed >> 30 == 4 and packed & ((1 << 30) - 1) == 2
+    assert engines[1].join() == 0  # and a rank can come back
+    time.sleep(0.2)
+    assert engines[0].members() == [0, 1, 2]
+    for e in engines.values():
+        e.stop()
+
+
+def test_rank_death_removes_it_from_the_group(mf, cluster):
+    W = 3
+    left = {r: [] for r in range(W)}
+    engines = {}
+    for r in range(W):
+        engines[r] = mf.native.GroupEngine(cluster.client(r, W), W, r, 5000, True, None, lambda rank, r=r: left[r].append(rank) or 0)
+        engines[r].start_listen()
+    for r in range(W):
+        assert engines[r].join() == 0
+    time.sleep(0.2)
+    engines[2].stop()
+    cluster.clients[2].shutdown()  # rank 2 dies without saying goodbye
+    deadline = time.time() + 5
+    while (engines[0].rank_size() != 2 or engines[1].rank_size() != 2) and time.time() < deadline:
+        time.sleep(0.02)
+    assert engines[0].members() == [0, 1] and engines[1].members() == [0, 1]
+    assert left[0] == [2] and left[1] == [2]
+    assert _run([engines[0].barrier, engines[1].barrier]) == [0, 0]  # the survivors carry on
+    rc, packed = cluster.clients[0].add("DSIZE", 0)
+    assert packed & ((1 << 30) - 1) == 2  # exactly one survivor repaired the counter
+    for r in (0, 1):
+        engines[r].stop()
+
+
+def _proc(rank, world, port, rounds, q):
+    import memfabric_hybrid_b200 as mf
+
+    try:
+        c = mf.native.TcpStore("127.0.0.1", port, rank == 0, world, rank)
+        assert c.startup(30, 100) == 0
+        e = mf.native.GroupEngine(c, world, rank, 20000)
+        for i in range(rounds):
+            assert e.barrier() == 0
+            rc, data = e.allgather((rank * 1000 + i).to_bytes(4, "little"))
+            assert rc == 0 and [int.from_bytes(data[4 * r:4 * r + 4], "little") for r in range(world)] == [r * 1000 + i for r in range(world)]
+        assert e.barrier() == 0
+        q.put((rank, "ok"))
+        time.sleep(0.3 if rank == 0 else 0)  # the serving rank leaves last
+        c.shutdown()
+    except Exception as ex:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(ex)))
+
+
+def test_processes_over_one_store():
+    world, rounds = 4, 20
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    ps = [ctx.Process(target=_proc, args=(r, world, port, rounds, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted(q.get(timeout=120) for _ in ps)
+    [p.join(30) for p in ps]
+    assert res == [(r, "ok") for r in range(world)], res
