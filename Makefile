@@ -60,10 +60,10 @@ $(TESTBIN): $(TEST_SRCS) $(CORE)
 	$(CXX) $(CXXFLAGS) -o $@ $(TEST_SRCS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' $(LDFLAGS)
 
 ASAN_FLAGS := -fsanitize=address,undefined -fno-omit-frame-pointer -O1
-asan:
+asan: $(CUDA_OBJS)
 	@mkdir -p $(BUILD)/asan
-	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -DMF_NO_CUDA_KERNELS -o $(BUILD)/asan/mf_native_tests_asan \
-	    $(TEST_SRCS) $(HOST_SRCS) csrc/kernels/mf_kernels_stub.cpp $(LDFLAGS)
+	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -o $(BUILD)/asan/mf_native_tests_asan \
+	    $(TEST_SRCS) $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
 
 clean:
 	rm -rf $(BUILD) $(CORE) $(PYMOD) $(TESTBIN)

@@ -87,6 +87,7 @@ def main():
         cases = {
             "d2d": lambda: h.copy_data_on_stream(me, peer + top, n, T.G2G, sh, 0),
             "d2d_pull": lambda: h.copy_data_on_stream(peer, me + top, n, T.G2G, sh, 0),
+            "d2d_ldst_kernel": lambda: mf.native.xcopy(peer + top, me, n, -1, sh),
             "d2d_copy_engine": lambda: mf.native.copy_engine(peer + top, me, n, sh),
             "cudaMemcpy_local": lambda: plain_dst[:n].copy_(plain_src[:n], non_blocking=True),
         }

@@ -565,7 +565,7 @@ extern "C" void *mf_bm_ptr_by_mem_type(mf_bm_t handle, mf_bm_mem_type memType, u
     if (e == nullptr) {
         return nullptr;
     }
-    uint32_t mt = memType == MF_MEM_TYPE_DEVICE ? hybm::MEM_TYPE_DEVICE : (memType == MF_MEM_TYPE_HOST ? hybm::MEM_TYPE_HOST : 0);
+    uint32_t mt = memType == MF_MEM_TYPE_DEVICE ? (uint32_t)hybm::MEM_TYPE_DEVICE : (memType == MF_MEM_TYPE_HOST ? (uint32_t)hybm::MEM_TYPE_HOST : 0u);
     if (mt == 0 || peerRankId >= e->Entity()->Opt().rankCount) {
         MF_ERROR("bm ptr: invalid memory type " << (int)memType << " or rank " << peerRankId);
         return nullptr;

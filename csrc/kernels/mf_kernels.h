@@ -133,7 +133,7 @@ typedef struct {
     uint32_t colsFull;
     uint32_t r0, c0;
     uint32_t nrows, ncols;
-    uint32_t tileStart;  // prefix sum of ceil(nrows/128) * ceil(ncols/128) over the table
+    uint32_t tileStart;  // prefix sum of ceil(nrows/128) * ceil(ncols/256) over the table (tiles are 128 rows x 256 columns)
     uint32_t quant;
     uint32_t pad;
 } mf_reshard_desc_t;

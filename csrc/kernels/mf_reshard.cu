@@ -22,17 +22,19 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kTile = 128;
-constexpr int kVecPerThread = (kTile * kTile / 8) / kThreads;  // 8
+constexpr int kThreads = 512;
+constexpr int kTile = 128;           // quantisation block edge and tile height
+constexpr int kTileCols = 256;       // tile width: a warp reads 512 contiguous bytes of a row (two quantisation blocks)
+constexpr int kVecPerRow = kTileCols / 8;
+constexpr int kVecPerThread = (kTile * kTileCols / 8) / kThreads;  // 8
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
     const mf_reshard_args_t a = args[blockIdx.y];
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
-    __shared__ float warpMax[kThreads / 32];
+    __shared__ float warpMax[2][kThreads / 32];  // per quantisation block of the tile, per warp
     __shared__ int abortFlag;
 
     if (blockIdx.x == 0) {
@@ -62,17 +64,17 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                 }
             }
             const mf_reshard_desc_t d = a.descs[lo];
-            const uint32_t tilesPerRow = (d.ncols + kTile - 1) / kTile;
+            const uint32_t tilesPerRow = (d.ncols + kTileCols - 1) / kTileCols;
             const uint32_t local = tile - d.tileStart;
             const uint32_t tr = local / tilesPerRow, tc = local % tilesPerRow;
-            const uint32_t rowBase = tr * kTile, colBase = tc * kTile;
+            const uint32_t rowBase = tr * kTile, colBase = tc * kTileCols;
 
             uint4 v[kVecPerThread];
             float amax = 0.f;
 #pragma unroll
             for (int i = 0; i < kVecPerThread; i++) {
-                const int idx = i * kThreads + (int)threadIdx.x;  // vector index inside the tile: 16 vectors per row
-                const uint32_t r = rowBase + idx / 16, c = colBase + (idx % 16) * 8;
+                const int idx = i * kThreads + (int)threadIdx.x;  // vector index inside the tile: 32 vectors (one warp) per row
+                const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
                 v[i] = make_uint4(0u, 0u, 0u, 0u);
                 if (r < d.nrows && c < d.ncols) {
                     const uint64_t flat = d.srcFlatOff + (uint64_t)(d.r0 + r) * d.colsFull + d.c0 + c;
@@ -90,18 +92,20 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                         amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
                     }
                 }
+                // Lanes 0-15 of every warp hold columns of the tile's left quantisation block, lanes 16-31 of the right one.
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
+                for (int o = 8; o > 0; o >>= 1) {
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                 }
-                if ((threadIdx.x & 31) == 0) {
-                    warpMax[threadIdx.x >> 5] = amax;
+                const int half = (threadIdx.x & 31) >> 4;
+                if ((threadIdx.x & 15) == 0) {
+                    warpMax[half][threadIdx.x >> 5] = amax;
                 }
                 __syncthreads();
                 float tmax = 0.f;
 #pragma unroll
                 for (int w = 0; w < kThreads / 32; w++) {
-                    tmax = fmaxf(tmax, warpMax[w]);
+                    tmax = fmaxf(tmax, warpMax[half][w]);
                 }
                 __syncthreads();
                 const float sc = fmaxf(tmax, 1e-10f) * (1.f / 448.f);
@@ -109,7 +113,7 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
                     const int idx = i * kThreads + (int)threadIdx.x;
-                    const uint32_t r = rowBase + idx / 16, c = colBase + (idx % 16) * 8;
+                    const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
                     if (r < d.nrows && c < d.ncols) {
                         const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v[i]);
                         uint2 pk;
@@ -122,15 +126,15 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                         *reinterpret_cast<uint2 *>(dst + (size_t)r * d.ncols + c) = pk;
                     }
                 }
-                if (threadIdx.x == 0) {
-                    a.dstScale[d.scaleOff + (size_t)tr * tilesPerRow + tc] = sc;
+                if ((threadIdx.x == 0 || threadIdx.x == 16) && colBase + half * kTile < d.ncols) {
+                    a.dstScale[d.scaleOff + (size_t)tr * (d.ncols / kTile) + tc * 2 + half] = sc;
                 }
             } else {
                 char *dst = reinterpret_cast<char *>(a.dst) + d.dstOff;
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
                     const int idx = i * kThreads + (int)threadIdx.x;
-                    const uint32_t r = rowBase + idx / 16, c = colBase + (idx % 16) * 8;
+                    const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
                     if (r < d.nrows && c < d.ncols) {
                         mf_st16(dst + ((size_t)r * d.ncols + c) * 2, v[i]);
                     }

@@ -14,6 +14,8 @@
 // 512-thread CTAs at two per SM (128 KiB in flight per SM — enough to cover HBM3e and NVLink latency), persistent grid.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "mf_copy_device.cuh"
 #include "mf_kernels.h"
 
@@ -36,6 +38,104 @@ mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict
             end = n;
         }
         mf::dev::CopySpan<kUnroll>(dst + begin, src + begin, end - begin, threadIdx.x, kThreads);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- bulk-copy (TMA) variant
+// For large copies whose two addresses are congruent modulo 16: each CTA streams 32 KiB tiles global → shared → global with
+// the bulk asynchronous copy engine of the SM (cp.async.bulk, no tensor map, no multicast), six tiles deep. One thread issues
+// loads, one thread issues stores; mbarriers hand tiles over. The SM's load/store units and register file stay out of the
+// data path, so the copy runs at what the memory system and NVLink deliver. Waits are bounded like everywhere else.
+constexpr int kTmaStages = 6;
+constexpr uint32_t kTmaTile = 32 * 1024;
+constexpr int kTmaStoresInFlight = 3;
+
+__device__ __forceinline__ uint32_t SmemU32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool MbarWaitParity(uint64_t *bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < (1u << 26); i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(SmemU32(bar)), "r"(parity)
+            : "memory");
+        if (ok) {
+            return true;
+        }
+    }
+    return false;  // about a minute of polling: the caller stops issuing work
+}
+
+__global__ void __launch_bounds__(128, 1)
+mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n)
+{
+    extern __shared__ unsigned char tmaSmemRaw[];
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(tmaSmemRaw) + 127) & ~(uintptr_t)127);
+    __shared__ uint64_t full[kTmaStages], empty[kTmaStages];
+    // Unaligned head (up to the first 16-byte boundary of dst) and tail bytes go through ordinary loads/stores.
+    const size_t head = n < 16 ? n : ((16 - ((uintptr_t)dst & 15)) & 15);
+    const size_t body = (n - head) & ~(size_t)15;
+    const size_t tail = n - head - body;
+    if (blockIdx.x == 0 && threadIdx.x >= 64) {
+        const unsigned t = threadIdx.x - 64;
+        if (t < head) {
+            dst[t] = src[t];
+        }
+        if (t < tail) {
+            dst[head + body + t] = src[head + body + t];
+        }
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kTmaStages; i++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(SmemU32(&full[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(SmemU32(&empty[i])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const size_t ntiles = (body + kTmaTile - 1) / kTmaTile;
+    const unsigned char *s0 = src + head;
+    unsigned char *d0 = dst + head;
+    if (threadIdx.x == 0) {
+        uint32_t it = 0;
+        for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
+            const uint32_t st = it % kTmaStages, ph = (it / kTmaStages) & 1;
+            if (!MbarWaitParity(&empty[st], ph ^ 1)) {
+                break;
+            }
+            const size_t off = t * kTmaTile;
+            const uint32_t bytes = (uint32_t)(body - off < kTmaTile ? body - off : kTmaTile);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemU32(&full[st])), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             SmemU32(tiles + (size_t)st * kTmaTile)),
+                         "l"(s0 + off), "r"(bytes), "r"(SmemU32(&full[st]))
+                         : "memory");
+        }
+    } else if (threadIdx.x == 32) {
+        uint32_t it = 0;
+        for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
+            const uint32_t st = it % kTmaStages, ph = (it / kTmaStages) & 1;
+            if (!MbarWaitParity(&full[st], ph)) {
+                break;
+            }
+            const size_t off = t * kTmaTile;
+            const uint32_t bytes = (uint32_t)(body - off < kTmaTile ? body - off : kTmaTile);
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(d0 + off), "r"(SmemU32(tiles + (size_t)st * kTmaTile)),
+                         "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            // All but the newest kTmaStoresInFlight stores have finished reading shared memory: hand that tile back.
+            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kTmaStoresInFlight) : "memory");
+            if (it >= (uint32_t)kTmaStoresInFlight) {
+                const uint32_t done = (it - kTmaStoresInFlight) % kTmaStages;
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemU32(&empty[done])) : "memory");
+            }
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store has landed before the CTA retires
     }
 }
 
@@ -212,6 +312,28 @@ extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_str
     const int sms = SmCount();
     if (sms <= 0) {
         return MF_K_LAUNCH_FAILED;
+    }
+    static const bool useTma = []() {
+        const char *e = getenv("MF_XCOPY_TMA");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    if (useTma && ctas >= 0 && n >= (4u << 20) && ((((uintptr_t)dst) ^ ((uintptr_t)src)) & 15) == 0) {
+        static bool attr = false;
+        const size_t smem = (size_t)kTmaStages * kTmaTile + 128;
+        if (!attr) {
+            if (cudaFuncSetAttribute(mf_xcopy_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return MF_K_LAUNCH_FAILED;
+            }
+            attr = true;
+        }
+        size_t tiles = (n + kTmaTile - 1) / kTmaTile;
+        size_t grid = ctas > 0 ? (size_t)ctas : (tiles < (size_t)sms ? tiles : (size_t)sms);
+        mf_xcopy_tma_kernel<<<(unsigned)grid, 128, smem, (cudaStream_t)stream>>>((unsigned char *)dst, (const unsigned char *)src, n);
+        return LaunchResult();
+    }
+    if (ctas < 0) {
+        ctas = -ctas == 1 ? 0 : -ctas;  // negative: force the load/store kernel (with |ctas| CTAs, -1 = automatic)
     }
     const size_t maxCtas = (size_t)sms * 2;
     // Tile = what one CTA moves per loop trip. Large copies use 64 KiB (8 × 16 B per thread); mid-size copies shrink the

@@ -62,7 +62,7 @@ class ReshardPlan:
             dst = (dst + 255) // 256 * 256
             if q:
                 sc += (nr // 128) * (nc // 128)
-            tiles += ((nr + 127) // 128) * ((nc + 127) // 128)
+            tiles += ((nr + 127) // 128) * ((nc + 255) // 256)  # kernel tiles: 128 rows x 256 columns
         self.dst_bytes, self.scale_floats, self.total_tiles = dst, sc, tiles
 
     def table_bytes(self) -> bytes:
