@@ -1,0 +1,116 @@
+#!/usr/bin/env python
+"""Host-DRAM pool on CPU-only ranks: two processes on one host joined through the TCP config store, each contributing a
+64 MiB DRAM segment to one GVA range. xcopy LH→GH and GH→LH of seeded uint8 buffers, sizes 4 KiB – 32 MiB, plus one batch copy
+of 64 discrete 16 KiB blocks at random aligned offsets; every transfer verified by byte compare. Baseline (oracle and timed):
+memcpy through a plain POSIX shared-memory mapping of the same size.
+
+    python benchmarks/cpu_pool_bench.py [--out gpurun_out/cpu_pool_bench.json]     (no GPU needed)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import mmap
+import multiprocessing as mp
+import os
+import socket
+import sys
+import time
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+POOL = 64 << 20
+
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def worker(rank, port, bar, q):
+    import memfabric_hybrid_b200 as mf
+
+    cfg = mf.bm.BmConfig()
+    cfg.rank_id = rank
+    assert mf.bm.initialize(f"tcp://127.0.0.1:{port}", 2, -1, cfg) == 0, mf.get_last_err_msg()
+    b = mf.bm.create(0, POOL, 0, mf.bm.BmDataOpType.HOST_RDMA)
+    assert b.join() == 0
+    bar.wait(60)
+    T, H = mf.bm.BmCopyType, mf.bm.BmMemType.HOST
+    peer = 1 - rank
+    rows = []
+    shm = mmap.mmap(-1, POOL)  # baseline target: an anonymous shared mapping of the same size
+    shm_np = np.frombuffer(shm, dtype=np.uint8)
+    for lg in range(12, 26):
+        n = 1 << lg
+        data = np.random.default_rng(lg * 10 + rank).integers(0, 256, n, dtype=np.uint8)
+        out = np.empty(n, dtype=np.uint8)
+        iters = max(3, min(200, (64 << 20) // n))
+        bar.wait(60)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            b.copy_data(data.ctypes.data, b.peer_rank_ptr(H, peer), n, T.H2GH, 0)
+        put = (time.perf_counter() - t0) / iters
+        bar.wait(60)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            b.copy_data(b.peer_rank_ptr(H, rank), out.ctypes.data, n, T.GH2H, 0)
+        get = (time.perf_counter() - t0) / iters
+        ok = bool((out == np.random.default_rng(lg * 10 + peer).integers(0, 256, n, dtype=np.uint8)).all())
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            shm_np[:n] = data
+        base = (time.perf_counter() - t0) / iters
+        rows.append({"bytes": n, "lh2gh_GBps": round(n / put / 1e9, 2), "gh2lh_GBps": round(n / get / 1e9, 2), "shm_memcpy_GBps": round(n / base / 1e9, 2),
+                     "lh2gh_us": round(put * 1e6, 1), "bytes_ok": ok})
+        bar.wait(60)
+    rng = np.random.default_rng(99 + rank)
+    offs = [int(s) * (16 << 10) for s in rng.choice(POOL // (16 << 10), size=64, replace=False)]
+    blocks = np.random.default_rng(7 + rank).integers(0, 256, 64 * (16 << 10), dtype=np.uint8)
+    srcs = [blocks.ctypes.data + i * (16 << 10) for i in range(64)]
+    dsts = [b.peer_rank_ptr(H, peer) + o for o in offs]
+    t0 = time.perf_counter()
+    for _ in range(50):
+        assert b.copy_data_batch(srcs, dsts, [16 << 10] * 64, 64, T.H2GH, 0) == 0
+    batch_us = (time.perf_counter() - t0) / 50 * 1e6
+    bar.wait(60)
+    mine = mf.native.host_read(b.peer_rank_ptr(H, rank), POOL)
+    poffs = [int(s) * (16 << 10) for s in np.random.default_rng(99 + peer).choice(POOL // (16 << 10), size=64, replace=False)]
+    pblocks = np.random.default_rng(7 + peer).integers(0, 256, 64 * (16 << 10), dtype=np.uint8).tobytes()
+    batch_ok = all(mine[o:o + (16 << 10)] == pblocks[i * (16 << 10):(i + 1) * (16 << 10)] for i, o in enumerate(poffs))
+    bar.wait(60)
+    q.put((rank, rows, {"batch64x16KiB_us": round(batch_us, 1), "batch_GBps": round(64 * (16 << 10) / batch_us / 1e3, 2), "batch_ok": batch_ok}))
+    time.sleep(0.3 if rank == 0 else 0)
+    b.destroy()
+    mf.bm.uninitialize()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default="gpurun_out/cpu_pool_bench.json")
+    args = ap.parse_args()
+    ctx = mp.get_context("spawn")
+    q, bar, port = ctx.Queue(), ctx.Barrier(2), free_port()
+    ps = [ctx.Process(target=worker, args=(r, port, bar, q)) for r in range(2)]
+    [p.start() for p in ps]
+    res = sorted(q.get(timeout=600) for _ in ps)
+    [p.join(30) for p in ps]
+    rows0, rows1 = res[0][1], res[1][1]
+    merged = []
+    for a, b in zip(rows0, rows1):  # the slower rank counts
+        merged.append({k: (min(a[k], b[k]) if k.endswith("GBps") else (max(a[k], b[k]) if k.endswith("_us") else (a[k] and b[k] if k == "bytes_ok" else a[k]))) for k in a})
+        print(json.dumps(merged[-1]))
+    batch = {k: (max(res[0][2][k], res[1][2][k]) if k.endswith("_us") else (min(res[0][2][k], res[1][2][k]) if k.endswith("GBps") else res[0][2][k] and res[1][2][k]))
+             for k in res[0][2]}
+    print(json.dumps(batch))
+    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+    with open(args.out, "w") as f:
+        json.dump({"rows": merged, "batch": batch}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
