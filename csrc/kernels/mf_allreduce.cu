@@ -242,24 +242,69 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
     if (!dead) {
         const int64_t heapOffX = (const char *)a.x - (const char *)mf_shm_ptr(m, me, 0);
         const int64_t heapOffRes = (char *)a.residualOut - (char *)mf_shm_ptr(m, me, 0);
+        const char *rank0x = (const char *)a.x - (uint64_t)me * m->symmetricSize;
         for (int row = rowLo + blockIdx.x; row < rowHi; row += gridDim.x) {
             const size_t rowOff = (size_t)row * H * 2;
+            // All loads of the row first (VPT x R peer vectors + the residual), then the arithmetic, then all stores:
+            // the loads of one vector never wait behind the stores of the previous one.
+            constexpr int KC = VPT < 2 ? VPT : 2;  // vectors per thread handled together: 2 x 8 peers x 16 B = 64 registers
+            const bool preload = NVLS || R <= 8;
 #pragma unroll
-            for (int k = 0; k < VPT; k++) {
-                const int vec = (int)threadIdx.x + k * kThreads;
+            for (int k0 = 0; k0 < VPT; k0 += KC) {
+            uint4 in[KC][8];
+            uint4 resv[KC];
+#pragma unroll
+            for (int kk = 0; kk < KC; kk++) {
+                const int k = kk, vec = (int)threadIdx.x + (k0 + kk) * kThreads;
+                if (vec < vecsPerRow) {
+                    const size_t off = rowOff + (size_t)vec * 16;
+                    if (NVLS) {
+                        in[k][0] = mf_multimem_ld_reduce_add_bf16x8((const char *)m->multicastBase + heapOffX + off);
+                    } else if (preload) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; j++) {
+                            if (j < R) {
+                                in[k][j] = mf_ld16(rank0x + (uint64_t)j * m->symmetricSize + off);
+                            }
+                        }
+                    }
+                    if (a.residual != nullptr) {
+                        resv[k] = mf_ld16((const char *)a.residual + off);
+                    }
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < KC; kk++) {
+                const int k = kk, vec = (int)threadIdx.x + (k0 + kk) * kThreads;
                 if (vec >= vecsPerRow) {
                     continue;
                 }
                 const size_t off = rowOff + (size_t)vec * 16;
                 float acc[8];
                 if (NVLS) {
-                    Unpack(mf_multimem_ld_reduce_add_bf16x8((const char *)m->multicastBase + heapOffX + off), acc);
+                    Unpack(in[k][0], acc);
+                } else if (preload) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        acc[i] = 0.f;
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; j++) {
+                        if (j < R) {
+                            float f[8];
+                            Unpack(in[k][j], f);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                acc[i] += f[i];
+                            }
+                        }
+                    }
                 } else {
                     ReduceVec(m, (const char *)a.x, off, acc);
                 }
                 if (a.residual != nullptr) {
                     float res[8];
-                    Unpack(mf_ld16((const char *)a.residual + off), res);
+                    Unpack(resv[k], res);
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         acc[i] += res[i];
@@ -273,6 +318,7 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
                         mf_st16((char *)mf_shm_ptr(m, (me + r) % R, (uint64_t)heapOffRes + off), packed);
                     }
                 }
+            }
             }
         }
     }

@@ -134,8 +134,10 @@ class FusedMoE(_MoEBase):
         T = x.shape[0]
         self._pack(x, idx, w, T)
         s = stream or torch.cuda.current_stream()
+        # One warp per token: small batches get a small grid (its grid-wide barriers are cheaper), large ones every SM.
+        ctas = max(1, min(1 << 16, (T + 7) // 8))
         rc = _ops.moe_dispatch(self._dargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.n_experts, CH_DISPATCH,
-                               self.heap.next_epoch(CH_DISPATCH), self.timeout_ns, 0, s.cuda_stream)
+                               self.heap.next_epoch(CH_DISPATCH), self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"moe_dispatch launch failed ({rc})")
         self.launches += 1
@@ -147,8 +149,9 @@ class FusedMoE(_MoEBase):
         import torch
 
         s = stream or torch.cuda.current_stream()
+        ctas = max(1, min(1 << 16, (T * self.topk + 7) // 8))  # one warp per returned row
         rc = _ops.moe_combine(self._cargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.el, CH_COMBINE, self.heap.next_epoch(CH_COMBINE),
-                              self.timeout_ns, 0, s.cuda_stream)
+                              self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"moe_combine launch failed ({rc})")
         self.launches += 1

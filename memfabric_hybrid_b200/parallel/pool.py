@@ -62,7 +62,9 @@ def open_pool(rank: int, world: int, device: int, hbm_bytes: int, dram_bytes: in
     if rc != 0:
         raise RuntimeError(f"bm.initialize failed ({rc}): {get_last_err_msg()}")
     op = bm.BmDataOpType.SDMA if device >= 0 else bm.BmDataOpType.HOST_RDMA
-    handle = bm.create(pool_id, dram_bytes, hbm_bytes if device >= 0 else 0, op, 0, dram_bytes, hbm_bytes)
+    # DRAM slices of GPU ranks are placed on the GPU's own NUMA node (flag bits 0-6 = 0x7F): host legs then stay local.
+    flags = 0x7F if device >= 0 and dram_bytes > 0 else 0
+    handle = bm.create(pool_id, dram_bytes, hbm_bytes if device >= 0 else 0, op, flags, dram_bytes, hbm_bytes)
     rc = handle.join()
     if rc != 0:
         raise RuntimeError(f"bm.join failed ({rc}): {get_last_err_msg()}")
