@@ -211,7 +211,8 @@ mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args
 
 // ------------------------------------------------------------------------------------------------ two-shot / NVLS
 
-template <bool NVLS, int VPT>
+// RC: compile-time upper bound of the rank count (2, 4 or 8; 0 = any) so that the peer vectors of a trip live in registers.
+template <bool NVLS, int VPT, int RC>
 __global__ void __launch_bounds__(kThreads, 1)
 mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epoch,
                                     uint64_t timeoutNs)
@@ -242,83 +243,80 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
     if (!dead) {
         const int64_t heapOffX = (const char *)a.x - (const char *)mf_shm_ptr(m, me, 0);
         const int64_t heapOffRes = (char *)a.residualOut - (char *)mf_shm_ptr(m, me, 0);
+        // Phase 1 needs no row structure (the norm happens in phase 2), so it is a flat sweep over the 16-byte vectors of my
+        // row block with up to 16 peer vectors in flight per thread: U consecutive tiles of blockDim vectors per trip.
         const char *rank0x = (const char *)a.x - (uint64_t)me * m->symmetricSize;
-        for (int row = rowLo + blockIdx.x; row < rowHi; row += gridDim.x) {
-            const size_t rowOff = (size_t)row * H * 2;
-            // All loads of the row first (VPT x R peer vectors + the residual), then the arithmetic, then all stores:
-            // the loads of one vector never wait behind the stores of the previous one.
-            constexpr int KC = VPT < 2 ? VPT : 2;  // vectors per thread handled together: 2 x 8 peers x 16 B = 64 registers
-            const bool preload = NVLS || R <= 8;
+        const size_t firstVec = (size_t)rowLo * vecsPerRow, nVec = (size_t)(rowHi - rowLo) * vecsPerRow;
+        constexpr int U = NVLS ? 8 : (RC == 2 ? 8 : (RC == 4 ? 4 : (RC == 8 ? 2 : 1)));
+        constexpr int RCC = RC == 0 ? 1 : RC;
+        const size_t trip = (size_t)U * kThreads;
+        for (size_t base = (size_t)blockIdx.x * trip; base < nVec; base += (size_t)gridDim.x * trip) {
+            uint4 in[U][RCC];
+            uint4 resv[U];
 #pragma unroll
-            for (int k0 = 0; k0 < VPT; k0 += KC) {
-            uint4 in[KC][8];
-            uint4 resv[KC];
-#pragma unroll
-            for (int kk = 0; kk < KC; kk++) {
-                const int k = kk, vec = (int)threadIdx.x + (k0 + kk) * kThreads;
-                if (vec < vecsPerRow) {
-                    const size_t off = rowOff + (size_t)vec * 16;
+            for (int u = 0; u < U; u++) {
+                const size_t i = base + (size_t)u * kThreads + threadIdx.x;
+                if (i < nVec) {
+                    const size_t off = (firstVec + i) * 16;
                     if (NVLS) {
-                        in[k][0] = mf_multimem_ld_reduce_add_bf16x8((const char *)m->multicastBase + heapOffX + off);
-                    } else if (preload) {
+                        in[u][0] = mf_multimem_ld_reduce_add_bf16x8((const char *)m->multicastBase + heapOffX + off);
+                    } else if (RC != 0) {
 #pragma unroll
-                        for (uint32_t j = 0; j < 8; j++) {
+                        for (uint32_t j = 0; j < (uint32_t)RCC; j++) {
                             if (j < R) {
-                                in[k][j] = mf_ld16(rank0x + (uint64_t)j * m->symmetricSize + off);
+                                in[u][j] = mf_ld16(rank0x + (uint64_t)j * m->symmetricSize + off);
                             }
                         }
                     }
                     if (a.residual != nullptr) {
-                        resv[k] = mf_ld16((const char *)a.residual + off);
+                        resv[u] = mf_ld16((const char *)a.residual + off);
                     }
                 }
             }
 #pragma unroll
-            for (int kk = 0; kk < KC; kk++) {
-                const int k = kk, vec = (int)threadIdx.x + (k0 + kk) * kThreads;
-                if (vec >= vecsPerRow) {
-                    continue;
-                }
-                const size_t off = rowOff + (size_t)vec * 16;
-                float acc[8];
-                if (NVLS) {
-                    Unpack(in[k][0], acc);
-                } else if (preload) {
+            for (int u = 0; u < U; u++) {
+                const size_t i = base + (size_t)u * kThreads + threadIdx.x;
+                if (i < nVec) {
+                    const size_t off = (firstVec + i) * 16;
+                    float acc[8];
+                    if (NVLS) {
+                        Unpack(in[u][0], acc);
+                    } else if (RC != 0) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        acc[i] = 0.f;
-                    }
+                        for (int q = 0; q < 8; q++) {
+                            acc[q] = 0.f;
+                        }
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; j++) {
-                        if (j < R) {
-                            float f[8];
-                            Unpack(in[k][j], f);
+                        for (uint32_t j = 0; j < (uint32_t)RCC; j++) {
+                            if (j < R) {
+                                float f[8];
+                                Unpack(in[u][j], f);
 #pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                acc[i] += f[i];
+                                for (int q = 0; q < 8; q++) {
+                                    acc[q] += f[q];
+                                }
                             }
                         }
+                    } else {
+                        ReduceVec(m, (const char *)a.x, off, acc);
                     }
-                } else {
-                    ReduceVec(m, (const char *)a.x, off, acc);
-                }
-                if (a.residual != nullptr) {
-                    float res[8];
-                    Unpack(resv[k], res);
+                    if (a.residual != nullptr) {
+                        float res[8];
+                        Unpack(resv[u], res);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        acc[i] += res[i];
+                        for (int q = 0; q < 8; q++) {
+                            acc[q] += res[q];
+                        }
+                    }
+                    const uint4 packed = Pack(acc);
+                    if (NVLS) {
+                        mf_multimem_st16((char *)m->multicastBase + heapOffRes + off, packed);
+                    } else {
+                        for (uint32_t r = 0; r < R; r++) {
+                            mf_st16((char *)mf_shm_ptr(m, (me + r) % R, (uint64_t)heapOffRes + off), packed);
+                        }
                     }
                 }
-                const uint4 packed = Pack(acc);
-                if (NVLS) {
-                    mf_multimem_st16((char *)m->multicastBase + heapOffRes + off, packed);
-                } else {
-                    for (uint32_t r = 0; r < R; r++) {
-                        mf_st16((char *)mf_shm_ptr(m, (me + r) % R, (uint64_t)heapOffRes + off), packed);
-                    }
-                }
-            }
             }
         }
     }
@@ -355,15 +353,24 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
 }
 
 template <int VPT>
-const void *PickKernel(int algo)
+const void *PickKernel(int algo, int rankCount)
 {
     if (algo == MF_AR_ONESHOT) {
         return (const void *)mf_allreduce_rmsnorm_oneshot_kernel<VPT>;
     }
     if (algo == MF_AR_NVLS) {
-        return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<true, VPT>;
+        return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<true, VPT, 0>;
     }
-    return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT>;
+    if (rankCount <= 2) {
+        return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT, 2>;
+    }
+    if (rankCount <= 4) {
+        return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT, 4>;
+    }
+    if (rankCount <= 8) {
+        return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT, 8>;
+    }
+    return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT, 0>;
 }
 
 int CoopCapacity(const void *kernel)
@@ -396,7 +403,9 @@ extern "C" int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nE
     void *kargs[] = {(void *)&argsDev, (void *)&T, (void *)&H, (void *)&eps, (void *)&channel, (void *)&epoch, (void *)&timeoutNs};
     // Vectors per thread per row are a compile-time constant so that a row lives in registers.
     const int vecsPerRow = H / 8;
-    const void *kernel = vecsPerRow <= kThreads ? PickKernel<1>(algo) : vecsPerRow <= 2 * kThreads ? PickKernel<2>(algo) : PickKernel<4>(algo);
+    const void *kernel = vecsPerRow <= kThreads       ? PickKernel<1>(algo, rankCount)
+                         : vecsPerRow <= 2 * kThreads ? PickKernel<2>(algo, rankCount)
+                                                      : PickKernel<4>(algo, rankCount);
     int capacity = CoopCapacity(kernel);
     if (capacity <= 0) {
         return MF_K_LAUNCH_FAILED;

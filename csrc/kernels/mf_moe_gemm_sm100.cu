@@ -21,6 +21,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "mf_kernels.h"
 #include "mf_sm100_ptx.cuh"
 
@@ -336,6 +338,10 @@ bool MakeMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t K)
 
 }  // namespace
 
+int mf_moe_grouped_gemm_2sm_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const float *aScale, const float *bScale, void *out,
+                                   const int *groupOffset, const int *groupCount, int G, int N, int K, int mode, int *status, int ctas,
+                                   cudaStream_t stream);
+
 extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, const float *bScale, void *out, const int *groupOffset,
                                      const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas, mf_stream_t stream)
 {
@@ -349,6 +355,19 @@ extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const v
     CUtensorMap mapA, mapB;
     if (!MakeMap(&mapA, a, (uint64_t)rowsTotal, (uint64_t)K) || !MakeMap(&mapB, b, (uint64_t)G * N, (uint64_t)K)) {
         return MF_K_LAUNCH_FAILED;
+    }
+    // The two-SM kernel (256-wide tiles over CTA pairs, mf_moe_gemm2_sm100.cu) is opt-in: ctas == -2 or MF_GEMM_2SM=1. Measured
+    // on B200 it is slower than this one-SM kernel (917 vs 1244 TFLOP/s on the prefill shape): both are paced by the per-K-block
+    // promotion of partial sums out of TMEM, not by operand traffic, and the wider tile makes that step longer per thread.
+    static const bool prefer2sm = []() {
+        const char *e = getenv("MF_GEMM_2SM");
+        return e != nullptr && e[0] == '1';
+    }();
+    if ((ctas == -2 || (prefer2sm && ctas >= 0 && rowsTotal >= 192 * G)) && N % 256 == 0) {
+        return mf_moe_grouped_gemm_2sm_launch(mapA, mapB, aScale, bScale, out, groupOffset, groupCount, G, N, K, mode, status, 0, (cudaStream_t)stream);
+    }
+    if (ctas < 0) {
+        ctas = 0;
     }
     GemmParams p;
     p.aScale = aScale;

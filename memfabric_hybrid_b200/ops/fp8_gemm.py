@@ -72,11 +72,13 @@ def interleave_gate_up(w_gate, w_up):
     return torch.cat([g, u], dim=-2).reshape(*lead, 2 * I, K).contiguous()
 
 
-def grouped_gemm(a_q, a_scale, b_q, b_scale, group_offset, group_count, mode: str = "bf16", out=None, status=None, ctas: int = 0, stream=None):
+def grouped_gemm(a_q, a_scale, b_q, b_scale, group_offset, group_count, mode: str = "bf16", out=None, status=None, ctas: int = 0, stream=None,
+                 two_sm: bool = False):
     """out[rows of group g] = dequant(a)[rows] @ dequant(b[g]).T  (bf16), optionally with the SwiGLU epilogue.
 
     a_q [R, K] e4m3, a_scale [R, K/128], b_q [G, N, K] e4m3, b_scale [G, N/128, K/128], group_offset int32 [G+1] (starts are
-    multiples of 128), group_count int32 [G] — both on the device."""
+    multiples of 128), group_count int32 [G] — both on the device. two_sm=True runs the CTA-pair (cta_group::2) variant, which
+    needs N % 256 == 0."""
     import torch
 
     R, K = a_q.shape
@@ -87,7 +89,8 @@ def grouped_gemm(a_q, a_scale, b_q, b_scale, group_offset, group_count, mode: st
     out = out if out is not None else torch.empty(R, n_out, dtype=torch.bfloat16, device=a_q.device)
     s = stream or torch.cuda.current_stream()
     rc = _ops.moe_grouped_gemm(a_q.data_ptr(), a_scale.data_ptr(), b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(), group_offset.data_ptr(),
-                               group_count.data_ptr(), G, R, N, K, epi, status.data_ptr() if status is not None else 0, ctas, s.cuda_stream)
+                               group_count.data_ptr(), G, R, N, K, epi, status.data_ptr() if status is not None else 0, -2 if two_sm else ctas,
+                               s.cuda_stream)
     if rc != 0:
         raise RuntimeError(f"moe_grouped_gemm launch failed ({rc})")
     return out

@@ -34,7 +34,9 @@ def test_quant_rows_matches_torch():
 
 
 @pytest.mark.parametrize("counts,N,K", [([128], 128, 128), ([128], 128, 256), ([128], 256, 512), ([1], 128, 128), ([200, 0, 37, 128], 256, 1024),
-                                        ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048)])
+                                        ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048),
+                                        # large row counts take the two-SM (cta_group::2) kernel: 256-wide tiles over CTA pairs
+                                        ([512], 256, 256), ([256], 256, 128), ([700, 256, 1], 512, 1024), ([1000, 130, 257, 640], 768, 2048)])
 def test_grouped_gemm_matches_reference(counts, N, K):
     import torch
 
@@ -49,7 +51,8 @@ def test_grouped_gemm_matches_reference(counts, N, K):
     w_q, w_s = F.quant_weight_torch(w)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=dev)
-    F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, out=out, status=status)
+    two_sm = N % 256 == 0 and rows >= 192 * len(counts)  # the CTA-pair kernel is exercised on the large cases
+    F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, out=out, status=status, two_sm=two_sm)
     torch.cuda.synchronize()
     assert int(status) == 0
     ref = F.grouped_gemm_reference(a_q, a_s, w_q, w_s, offs, cnts)
@@ -64,13 +67,14 @@ def test_grouped_gemm_matches_reference(counts, N, K):
         assert bool(torch.isnan(pad.float()).all()) or pad.numel() == 0
 
 
-def test_grouped_gemm_swiglu_epilogue():
+@pytest.mark.parametrize("big_counts", [None, [600, 257, 300]])
+def test_grouped_gemm_swiglu_epilogue(big_counts):
     import torch
 
     from memfabric_hybrid_b200.ops import fp8_gemm as F
 
     dev = "cuda"
-    counts, I, K = [70, 130, 3], 256, 512
+    counts, I, K = big_counts or [70, 130, 3], 256, 512
     offs, cnts, rows = _groups(counts, dev)
     g = torch.Generator(device=dev).manual_seed(9)
     a = torch.randn(rows, K, generator=g, device=dev)
@@ -79,7 +83,7 @@ def test_grouped_gemm_swiglu_epilogue():
     w = F.interleave_gate_up(wg, wu)
     a_q, a_s = F.quant_act_torch(a)
     w_q, w_s = F.quant_weight_torch(w)
-    out = F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu")
+    out = F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu", two_sm=big_counts is not None)
     torch.cuda.synchronize()
     ref = F.grouped_gemm_reference(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu")
     # cross-check the interleaved layout against the textbook formula on the dequantised, de-interleaved weights
