@@ -247,7 +247,7 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
         // row block with up to 16 peer vectors in flight per thread: U consecutive tiles of blockDim vectors per trip.
         const char *rank0x = (const char *)a.x - (uint64_t)me * m->symmetricSize;
         const size_t firstVec = (size_t)rowLo * vecsPerRow, nVec = (size_t)(rowHi - rowLo) * vecsPerRow;
-        constexpr int U = NVLS ? 8 : (RC == 2 ? 8 : (RC == 4 ? 4 : (RC == 8 ? 2 : 1)));
+        constexpr int U = NVLS ? 2 : (RC == 2 ? 8 : (RC == 4 ? 4 : (RC == 8 ? 2 : 1)));  // in-switch reductions: two in flight measured best
         constexpr int RCC = RC == 0 ? 1 : RC;
         const size_t trip = (size_t)U * kThreads;
         for (size_t base = (size_t)blockIdx.x * trip; base < nVec; base += (size_t)gridDim.x * trip) {
