@@ -53,7 +53,11 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
     // rank 0's copy of the shard buffer: rank r's is r * symmetricSize further
     const char *shard0 = reinterpret_cast<const char *>(a.srcShard) - (uint64_t)m->rankId * m->symmetricSize;
     if (!dead) {
-        for (uint32_t tile = blockIdx.x; tile < a.totalTiles; tile += gridDim.x) {
+        // Blocked distribution: every CTA walks a contiguous run of tiles (same rows, neighbouring columns, then the next rows),
+        // so its reads stay inside a few pages of one owner at a time instead of hopping across all peers' shards.
+        const uint32_t perCta = (a.totalTiles + gridDim.x - 1) / gridDim.x;
+        const uint32_t tileEnd = min(a.totalTiles, (blockIdx.x + 1) * perCta);
+        for (uint32_t tile = blockIdx.x * perCta; tile < tileEnd; tile++) {
             uint32_t lo = 0, hi = a.ndesc;
             while (hi - lo > 1) {
                 const uint32_t mid = (lo + hi) >> 1;
