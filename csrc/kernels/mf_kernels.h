@@ -68,6 +68,8 @@ int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRank
 // ------------------------------------------------------------------------------------------------ MoE expert FFN (K5b)
 
 enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1 };
+// Pipeline-study switches OR-ed into `mode` (results are meaningless, only the timing is of interest).
+enum { MF_GEMM_DEBUG_NO_PROMOTION = 16, MF_GEMM_DEBUG_NO_LOADS = 32 };
 
 // Grouped block-scaled FP8 GEMM on tcgen05 tensor cores. Group g owns rows [groupOffset[g], groupOffset[g] + groupCount[g])
 // of A (group starts must be multiples of 128 rows; rows between count and the next start are ignored) and weights

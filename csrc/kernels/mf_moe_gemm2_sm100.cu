@@ -129,7 +129,7 @@ mf_moe_grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmapA, const 
         }
         for (int i = 0; i < kAccBufs; i++) {
             MbarInit(&s.tmemFull[i], 1);
-            MbarInit(&s.tmemEmpty[i], 2 * kEpiThreads);  // both CTAs' epilogue threads arrive on the leader's copy
+            MbarInit(&s.tmemEmpty[i], 2 * kEpiThreads / 32);  // one arrival per epilogue warp of both CTAs, on the leader's copy
         }
         s.abortFlag = 0;
         int acc = 0;
@@ -182,6 +182,12 @@ mf_moe_grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                     const uint32_t st = it % kStages, ph = (it / kStages) & 1;
                     if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
                         break;
+                    }
+                    if (p.mode & MF_GEMM_DEBUG_NO_LOADS) {
+                        if (cta == 0) {
+                            MbarArrive(&s.full[st]);
+                        }
+                        continue;
                     }
                     if (cta == 0) {
                         MbarExpectTx(&s.full[st], 4 * kTileBytes);  // A and B halves of both CTAs
@@ -249,6 +255,14 @@ mf_moe_grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                     break;
                 }
                 TcFenceAfter();
+                if (p.mode & MF_GEMM_DEBUG_NO_PROMOTION) {
+                    TcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) {
+                        RemoteArrive(leaderEmpty0 + buf * (uint32_t)sizeof(uint64_t));
+                    }
+                    continue;
+                }
                 const uint32_t taddr = tmemBase + ((uint32_t)(quad * 32) << 16) + buf * BN + half * HC;
 #pragma unroll
                 for (int c = 0; c < HC / 32; c++) {
@@ -257,7 +271,10 @@ mf_moe_grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                     TmemLdWait();
                     if (c == HC / 32 - 1) {
                         TcFenceBefore();
-                        RemoteArrive(leaderEmpty0 + buf * (uint32_t)sizeof(uint64_t));  // my part of the buffer is in registers
+                        __syncwarp();
+                        if (lane == 0) {
+                            RemoteArrive(leaderEmpty0 + buf * (uint32_t)sizeof(uint64_t));  // the warp's part of the buffer is in registers
+                        }
                     }
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
@@ -269,7 +286,7 @@ mf_moe_grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                 break;
             }
             if (valid) {
-                if (p.mode == MF_GEMM_EPI_SWIGLU) {
+                if ((p.mode & 15) == MF_GEMM_EPI_SWIGLU) {
                     // Each 64-column chunk holds 32 gate projections followed by the 32 matching up projections.
                     __nv_bfloat16 *o = p.out + (size_t)row * p.outStride + nt * (BN / 2) + half * (HC / 2);
 #pragma unroll
@@ -332,7 +349,7 @@ int mf_moe_grouped_gemm_2sm_launch(const CUtensorMap &mapA, const CUtensorMap &m
     p.N = N;
     p.K = K;
     p.mode = mode;
-    p.outStride = mode == MF_GEMM_EPI_SWIGLU ? N / 2 : N;
+    p.outStride = (mode & 15) == MF_GEMM_EPI_SWIGLU ? N / 2 : N;
     static bool attrSet = false;
     const size_t smem = sizeof(SharedStorage2) + 1024;
     if (!attrSet) {

@@ -78,7 +78,7 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
         }
         for (int i = 0; i < kAccBufs; i++) {
             MbarInit(&s.tmemFull[i], 1);
-            MbarInit(&s.tmemEmpty[i], kEpiThreads);
+            MbarInit(&s.tmemEmpty[i], kEpiThreads / 32);  // one arrival per epilogue warp
         }
         s.abortFlag = 0;
         int acc = 0;
@@ -130,6 +130,10 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
                     const uint32_t st = it % kStages, ph = (it / kStages) & 1;
                     if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
                         break;
+                    }
+                    if (p.mode & MF_GEMM_DEBUG_NO_LOADS) {
+                        MbarArrive(&s.full[st]);  // pipeline study: tensor core and promotion without operand traffic
+                        continue;
                     }
                     MbarExpectTx(&s.full[st], 2 * kTileBytes);
                     TmaLoad2D(s.a[st], &tmapA, &s.full[st], kb * BK, rowA);
@@ -195,13 +199,24 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
                     break;
                 }
                 TcFenceAfter();
+                if (p.mode & MF_GEMM_DEBUG_NO_PROMOTION) {
+                    TcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) {
+                        MbarArrive(&s.tmemEmpty[buf]);  // pipeline study: loads and MMAs without the per-K-block TMEM read-out
+                    }
+                    continue;
+                }
                 const uint32_t taddr = tmemBase + ((uint32_t)(quad * 32) << 16) + buf * BN + half * HC;
                 float v[HC];
                 TmemLd32Issue(taddr, v);
                 TmemLd32Issue(taddr + 32, v + 32);
                 TmemLdWait();
                 TcFenceBefore();
-                MbarArrive(&s.tmemEmpty[buf]);  // the values are in registers: the buffer can take the next partial product
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&s.tmemEmpty[buf]);  // the warp's values are in registers: one arrival per warp keeps the barrier cheap
+                }
 #pragma unroll
                 for (int i = 0; i < HC; i++) {
                     acc[i] = fmaf(v[i], scale, acc[i]);
@@ -211,7 +226,7 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
                 break;
             }
             if (valid) {
-                if (p.mode == MF_GEMM_EPI_SWIGLU) {
+                if ((p.mode & 15) == MF_GEMM_EPI_SWIGLU) {
                     // Each 64-column half of the tile holds 32 gate projections followed by the 32 matching up projections.
                     __nv_bfloat16 *o = p.out + (size_t)row * p.outStride + nt * (BN / 2) + half * (HC / 2);
 #pragma unroll
@@ -380,7 +395,7 @@ extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const v
     p.N = N;
     p.K = K;
     p.mode = mode;
-    p.outStride = mode == MF_GEMM_EPI_SWIGLU ? N / 2 : N;
+    p.outStride = (mode & 15) == MF_GEMM_EPI_SWIGLU ? N / 2 : N;
     static bool attrSet = false;
     const size_t smem = sizeof(SharedStorage) + 1024;
     if (!attrSet) {
