@@ -59,8 +59,8 @@ def main():
     for e in range(EL):
         wg = torch.randn(I, H, generator=g, device=dev) * H ** -0.5
         wu = torch.randn(I, H, generator=g, device=dev) * H ** -0.5
-        w13_q[e], w13_s[e] = F.quant_weight_torch(F.interleave_gate_up(wg, wu))
-        w2_q[e], w2_s[e] = F.quant_weight_torch(torch.randn(H, I, generator=g, device=dev) * I ** -0.5)
+        w13_q[e], w13_s[e] = F.quant_weight_mx_torch(F.interleave_gate_up(wg, wu))
+        w2_q[e], w2_s[e] = F.quant_weight_mx_torch(torch.randn(H, I, generator=g, device=dev) * I ** -0.5)
     del wg, wu
 
     cap = capacity_rows(Tmax, K, world, EL, args.capacity_factor)

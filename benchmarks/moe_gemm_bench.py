@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--out", default="gpurun_out/moe_gemm_bench.json")
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--tile-n", type=int, default=0, help="0 = let the launcher choose, 128 or 256")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     dev = "cuda"
@@ -46,18 +47,25 @@ def main():
         offs_t = torch.tensor(offs, dtype=torch.int32, device=dev)
         cnts_t = torch.tensor(counts, dtype=torch.int32, device=dev)
         a = torch.randn(cur, K, generator=g, device=dev)
-        a_q, a_s = F.quant_act_torch(a)
+        a_q, a_s = F.quant_act_mx_torch(a)
         del a
         w_q = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device=dev)
         w_s = torch.empty(G, N // 128, K // 128, dtype=torch.float32, device=dev)
         for e in range(G):  # random-init expert by expert to bound the fp32 temporaries
-            q, s_ = F.quant_weight_torch(torch.randn(N, K, generator=g, device=dev) * 0.02)
+            q, s_ = F.quant_weight_mx_torch(torch.randn(N, K, generator=g, device=dev) * 0.02)
             w_q[e], w_s[e] = q, s_
         out = torch.empty(cur, N // 2 if mode == "swiglu" else N, dtype=torch.bfloat16, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
 
+        out_q = torch.empty(cur, N // 2, dtype=torch.float8_e4m3fn, device=dev) if mode == "swiglu" else None
+        out_sf = torch.empty(cur, N // 64, dtype=torch.uint8, device=dev) if mode == "swiglu" else None
+
         def run():
-            F.grouped_gemm(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode=mode, out=out, status=status)
+            # the layer's configuration: SwiGLU + 1x32 quantisation fused into the first GEMM, bf16 out of the second
+            if mode == "swiglu":
+                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="swiglu_fp8", out=out_q, out_sf=out_sf, status=status, tile_n=args.tile_n)
+            else:
+                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="bf16", out=out, status=status, tile_n=args.tile_n)
 
         for _ in range(3):
             run()
@@ -74,7 +82,7 @@ def main():
         ms = sorted(times)[len(times) // 2]
         flops = 2.0 * sum(counts) * N * K
         # baseline: cuBLAS bf16, one matmul per expert on dequantised operands (what a library implementation does)
-        a_bf = F.dequant_act(a_q, a_s).to(torch.bfloat16)
+        a_bf = F.dequant_act_mx(a_q, a_s).to(torch.bfloat16)
         w_bf = torch.empty(G, N, K, dtype=torch.bfloat16, device=dev)
         for e in range(G):
             w_bf[e] = F.dequant_weight(w_q[e], w_s[e]).to(torch.bfloat16)
@@ -101,14 +109,16 @@ def main():
             bt.append(a_ev.elapsed_time(b_ev))
         bms = sorted(bt)[len(bt) // 2]
         # correctness on one expert
-        ref = F.grouped_gemm_reference(a_q[:offs[1]], a_s[:offs[1]], w_q[:1], w_s[:1], offs_t[:2], cnts_t[:1], mode=mode)
-        err = float((out[:counts[0]].float() - ref[:counts[0]]).abs().max() / (ref[:counts[0]].abs().max() + 1e-9))
+        ref = F.grouped_gemm_mx_reference(a_q[:offs[1]], a_s[:offs[1]], w_q[:1], w_s[:1], offs_t[:2], cnts_t[:1], mode=mode)
+        got = F.dequant_act_mx(out_q[:counts[0]], out_sf[:counts[0]]) if mode == "swiglu" else out[:counts[0]].float()
+        err = float((got - ref[:counts[0]]).abs().max() / (ref[:counts[0]].abs().max() + 1e-9))
         weight_bytes = G * N * K
         row = {"case": name, "G": G, "rows_per_expert": per, "N": N, "K": K, "mode": mode, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
                "weight_GBps": round(weight_bytes / ms / 1e6, 1), "cublas_bf16_ms": round(bms, 4), "speedup": round(bms / ms, 2),
                "rel_err": round(err, 5), "status": int(status)}
         rows_out.append(row)
         print(json.dumps(row), flush=True)
+        row["tile_n"] = args.tile_n
         del a_bf, w_bf, w_q, w_s, a_q, a_s, out
         torch.cuda.empty_cache()
     os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)

@@ -59,17 +59,18 @@ def case_gemm():
     G, per, N, K = 8, 512, 4096, 7168
     g = torch.Generator(device="cuda").manual_seed(1)
     rows = G * per
-    a_q, a_s = F.quant_act_torch(torch.randn(rows, K, generator=g, device="cuda"))
+    a_q, a_s = F.quant_act_mx_torch(torch.randn(rows, K, generator=g, device="cuda"))
     w_q = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device="cuda")
     w_s = torch.empty(G, N // 128, K // 128, dtype=torch.float32, device="cuda")
     for e in range(G):
-        w_q[e], w_s[e] = F.quant_weight_torch(torch.randn(N, K, generator=g, device="cuda") * 0.02)
+        w_q[e], w_s[e] = F.quant_weight_mx_torch(torch.randn(N, K, generator=g, device="cuda") * 0.02)
     offs = torch.arange(0, rows + 1, per, dtype=torch.int32, device="cuda")
     cnts = torch.full((G,), per, dtype=torch.int32, device="cuda")
-    out = torch.empty(rows, N // 2, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(rows, N // 2, dtype=torch.float8_e4m3fn, device="cuda")
+    out_sf = torch.empty(rows, N // 64, dtype=torch.uint8, device="cuda")
     torch.cuda.synchronize()
     for _ in range(3):
-        F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu", out=out)
+        F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu_fp8", out=out, out_sf=out_sf)
     torch.cuda.synchronize()
 
 
@@ -101,13 +102,13 @@ def case_dispatch():
     weights = []
     for _ in range(world):
         el = E // world
-        w13 = F.quant_weight_torch(torch.randn(el, 2 * I, H, generator=g, device="cuda") * 0.01)
-        w2 = F.quant_weight_torch(torch.randn(el, H, I, generator=g, device="cuda") * 0.02)
+        w13 = F.quant_weight_mx_torch(torch.randn(el, 2 * I, H, generator=g, device="cuda") * 0.01)
+        w2 = F.quant_weight_mx_torch(torch.randn(el, H, I, generator=g, device="cuda") * 0.02)
         weights.append((w13[0], w13[1], w2[0], w2[1]))
     xs = [torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
     routed = [route(torch.randn(T, E, generator=g, device="cuda"), K) for _ in range(world)]
     cap = T * K * 2 + (E // world) * 128
-    heap = EmulatedHeap(world, world * E * 4 + cap * (H + H // 128 * 4 + 16) + T * K * H * 2 + (4 << 20))
+    heap = EmulatedHeap(world, world * E * 4 + cap * (H + H // 128 * 4 + 16 + 56) + T * K * H * 2 + (4 << 20))
     layer = EmulatedMoE(heap, T, H, E, K, I, weights, capacity_factor=2.0)
     for _ in range(2):
         outs, status = layer(xs, [r[0] for r in routed], [r[1] for r in routed])

@@ -99,7 +99,7 @@ __device__ __forceinline__ void ReduceVec(const MfDeviceMeta *m, const char *xLo
 #pragma unroll
         for (uint32_t j = 0; j < 8; j++) {
             if (j < n) {
-                v[j] = mf_ld16(rank0 + (uint64_t)(r0 + j) * m->symmetricSize);
+                v[j] = mf_ld16_coherent(rank0 + (uint64_t)(r0 + j) * m->symmetricSize);
             }
         }
 #pragma unroll
@@ -264,7 +264,7 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
 #pragma unroll
                         for (uint32_t j = 0; j < (uint32_t)RCC; j++) {
                             if (j < R) {
-                                in[u][j] = mf_ld16(rank0x + (uint64_t)j * m->symmetricSize + off);
+                                in[u][j] = mf_ld16_coherent(rank0x + (uint64_t)j * m->symmetricSize + off);
                             }
                         }
                     }

@@ -7,7 +7,8 @@
 #ifdef __CUDACC__
 #include <vector_types.h>
 #else
-struct int4;  // only pointers to it cross this interface in host code
+struct int4;  // only pointers to them cross this interface in host code
+struct int2;
 #endif
 
 #ifdef __cplusplus
@@ -67,9 +68,7 @@ int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRank
 
 // ------------------------------------------------------------------------------------------------ MoE expert FFN (K5b)
 
-enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1 };
-// Pipeline-study switches OR-ed into `mode` (results are meaningless, only the timing is of interest).
-enum { MF_GEMM_DEBUG_NO_PROMOTION = 16, MF_GEMM_DEBUG_NO_LOADS = 32 };
+enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1, MF_GEMM_EPI_SWIGLU_FP8 = 2 };
 
 // Grouped block-scaled FP8 GEMM on tcgen05 tensor cores. Group g owns rows [groupOffset[g], groupOffset[g] + groupCount[g])
 // of A (group starts must be multiples of 128 rows; rows between count and the next start are ignored) and weights
@@ -79,6 +78,17 @@ enum { MF_GEMM_DEBUG_NO_PROMOTION = 16, MF_GEMM_DEBUG_NO_LOADS = 32 };
 // groupOffset/groupCount live on the device (the routing result never visits the host). status: device int or NULL.
 int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, const float *bScale, void *out, const int *groupOffset,
                           const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas, mf_stream_t stream);
+
+// The same GEMM with the block scaling done by the tensor core (tcgen05.mma.kind::mxf8f6f4.block_scale): all scales are
+// powers of two. aSf: [rowsTotal, K/128] 32-bit words, byte j of a word = UE8M0 exponent (value 2^(byte-127)) of K-elements
+// [128*kb + 32*j, +32) of that row (a 1x128 scale is the same byte four times); bScale: [G, N/128, K/128] fp32 whose
+// mantissa bits are ignored (only the exponent is used). Epilogues: MF_GEMM_EPI_BF16 (out bf16 [rowsTotal, N]),
+// MF_GEMM_EPI_SWIGLU (out bf16 [rowsTotal, N/2]) and MF_GEMM_EPI_SWIGLU_FP8: out e4m3 [rowsTotal, N/2] plus outSf
+// [rowsTotal, N/64] UE8M0 bytes, one per 32 outputs, i.e. exactly the a / aSf operands of a following GEMM with K = N/2.
+// tileN: 0 = pick from the sizes, 128 or 256 (256 needs N % 256 == 0). a, b, out and aSf must be 16-byte aligned.
+int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
+                             const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
+                             int *status, int ctas, mf_stream_t stream);
 
 // ------------------------------------------------------------------------------------------------ MoE dispatch / combine (K5a, K5c)
 
@@ -90,8 +100,9 @@ typedef struct {
     const float *topkW;   // [T, K] renormalised routing weights
     int *cnt;             // heap: [R][E] pair counts, row s written by rank s on every rank
     void *recvX;          // heap: [cap][H] e4m3
-    float *recvScale;     // heap: [cap][H/128]
-    int4 *recvMeta;       // heap: [cap] {source rank, token, k, weight bits}
+    uint32_t *recvSf;     // heap: [cap][H/128] scale words: the UE8M0 exponent byte of the 1x128 block, four times
+    int4 *recvMeta;       // heap: [cap] {source rank, token, k | siblings << 8 | MF_MOE_META_FOLLOWER, weight bits}
+    int2 *recvSib;        // heap: [cap][MF_MOE_MAX_SIBLINGS] {row, weight bits} of a leader's sibling rows
     int *localCnt;        // [E] scratch, zero before the first call (the kernel leaves it zero)
     int *cursor;          // [E] scratch, zero before the first call (the kernel leaves it zero)
     int *expertOffset;    // out: [E/R + 1] first row of each local expert (multiples of 128); last = rows in use
@@ -102,17 +113,23 @@ typedef struct {
     int cap;
 } mf_moe_dispatch_args_t;
 
+// A token with several experts on one owner: the pair with the lowest k is the leader, the others are followers.
+enum { MF_MOE_MAX_SIBLINGS = 7, MF_MOE_META_FOLLOWER = 1 << 30 };
+
 typedef struct {
     const void *meta;
     const void *y;            // [cap][H] bf16 expert outputs (local)
     const int4 *recvMeta;     // as filled by dispatch (local side of the heap buffer)
+    const int2 *recvSib;      // as filled by dispatch
     const int *expertOffset;  // as filled by dispatch
     const int *expertCount;
-    void *retY;               // heap: [Tmax * K][H] bf16 landing zone at the source rank
-    const float *topkW;       // [T, K]
+    void *retY;               // heap: [retRows][H] bf16 landing zone at the source rank, row = token * K + k
+    const int *topkIdx;       // [T, K] as given to dispatch
     void *out;                // [T, H] bf16
     int *status;
     int T;
+    int cap;                  // rows of the receive buffer (and of y)
+    int retRows;              // rows of every rank's landing zone (max tokens * K)
     int reserved;
 } mf_moe_combine_args_t;
 

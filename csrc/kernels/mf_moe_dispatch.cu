@@ -3,13 +3,20 @@
 // dispatch  (a) histogram of this rank's (token, k) pairs per global expert, pushed to every rank; (b) after a cross-rank
 //           barrier every rank knows the full count matrix and derives, without any further message, the row of the
 //           destination rank's receive buffer where each of its pairs lands (experts contiguous, starts aligned to the
-//           128-row GEMM tile, sources in rank order); (c) each token is quantised ONCE to e4m3 with 1x128 scales in
-//           shared memory and its bytes, scales and routing record are stored straight into the receive buffers of the
-//           owners of its top-k experts over NVLink; (d) a closing barrier tells the owners that everything has landed.
-//           The owner-side tables (expert_offset / expert_count) that the grouped GEMM consumes are written on the way.
-// combine   each expert owner pushes its output rows back to the source rank's landing zone [token][k][hidden]; after a
-//           barrier the source reduces over k in fp32 with the renormalised routing weights (fixed k order: deterministic)
-//           and writes bf16.
+//           128-row GEMM tile, sources in rank order); (c) each token is quantised ONCE to e4m3 with 1x128 power-of-two
+//           scales (UE8M0 exponent bytes, the format the block-scaled tensor-core GEMM consumes) in shared memory and its
+//           bytes, scale words and routing record are stored straight into the receive buffers of the owners of its top-k
+//           experts over NVLink; (d) a closing barrier tells the owners that everything has landed.
+//           The owner-side tables (expert_offset / expert_count) that the grouped GEMM consumes are written on the way,
+//           clamped to the capacity of the receive buffer: on overflow the call reports MF_DEV_ERR_BOUNDS and what was
+//           published never points past the buffer.
+//           A token whose top-k holds several experts of the same owner tells that owner, in the record of the first of
+//           them (the "leader"), where its sibling rows are.
+// combine   each expert owner reduces the sibling rows of a token with their routing weights (fp32) and pushes ONE row
+//           per (token, owner) back to the source rank's landing zone [token][k of the leader][hidden]; after a barrier the
+//           source adds the partial sums of the owners in fixed k order (fp32, deterministic) and writes bf16. A top-8
+//           token over 8 ranks reaches 5.25 distinct owners on average, so a third of the return traffic never leaves
+//           the owner.
 // The reference library names MoE dispatch/combine only as a use case of its symmetric heap (README.md:53 of the reference);
 // the flag/barrier discipline follows its sample kernel (example/shm/AllReduce/shm_all_reduce.cpp:69-112) with bounded waits.
 // Like the all-reduce, both kernels take an array of per-rank argument blocks so that tests can run all ranks of a fake
@@ -35,6 +42,14 @@ __device__ __forceinline__ void FailD(int *status, int code)
     if (threadIdx.x == 0 && status != nullptr) {
         atomicCAS(status, 0, code);
     }
+}
+
+// UE8M0 byte (biased exponent) of the smallest power of two >= t, clamped to [1, 253] so that its reciprocal is a normal float.
+__device__ __forceinline__ uint32_t Ue8m0Ceil(float t)
+{
+    const uint32_t bits = __float_as_uint(t);
+    const uint32_t e = ((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) != 0u ? 1u : 0u);
+    return e < 1u ? 1u : (e > 253u ? 253u : e);
 }
 
 __device__ __forceinline__ int ReadAbort(int *status, int *smemFlag)
@@ -116,14 +131,17 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
             sendBase[e] += starts[e];
         }
         if (blockIdx.x == 0) {
+            // What the GEMM and combine consume never points past the receive buffer: an expert that starts beyond the
+            // capacity is published empty, one that straddles it is cut. The senders skip the same rows.
             for (int el = threadIdx.x; el < EL; el += kThreads) {
-                a.expertOffset[el] = starts[me * EL + el];
-                a.expertCount[el] = totals[me * EL + el];
+                const int off = min(starts[me * EL + el], a.cap);
+                a.expertOffset[el] = off;
+                a.expertCount[el] = min(totals[me * EL + el], a.cap - off);
             }
             if (threadIdx.x == 0) {
                 const int last = me * EL + EL - 1;
                 const int off = starts[last] + ((totals[last] + 127) & ~127);
-                a.expertOffset[EL] = off;
+                a.expertOffset[EL] = min(off, a.cap);
                 if (off > a.cap) {
                     FailD(a.status, MF_DEV_ERR_BOUNDS);
                 }
@@ -133,7 +151,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
 
         // ---- (c) quantise each token once, store it to the owners of its experts
         unsigned char *myStage = stage + (size_t)warp * stagePerWarp;
-        float *myScale = reinterpret_cast<float *>(myStage + H);
+        uint32_t *myScale = reinterpret_cast<uint32_t *>(myStage + H);
         const int warpsTotal = gridDim.x * kWarps;
         for (int t = blockIdx.x * kWarps + warp; t < a.T; t += warpsTotal) {
             const __nv_bfloat16 *row = reinterpret_cast<const __nv_bfloat16 *>(a.x) + (size_t)t * H;
@@ -161,52 +179,84 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
                 for (int o = 8; o > 0; o >>= 1) {
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                 }
-                const float sc = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+                // Scale = smallest power of two >= amax / 448, as a biased exponent byte; multiplying by its reciprocal is exact.
+                const uint32_t eb = Ue8m0Ceil(amax * (1.f / 448.f));
+                const float inv = __uint_as_float((254u - eb) << 23);
                 uint2 packed;
                 unsigned short *ps = reinterpret_cast<unsigned short *>(&packed);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    ps[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] / sc, f[2 * i + 1] / sc), __NV_SATFINITE, __NV_E4M3);
+                    ps[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
                 }
                 if (active) {
                     *reinterpret_cast<uint2 *>(myStage + off) = packed;
                     if ((lane & 15) == 0) {
-                        myScale[blk] = sc;
+                        myScale[blk] = eb * 0x01010101u;  // the same exponent for the four 32-element steps of the block
                     }
                 }
             }
             __syncwarp();
+            // Lane k owns pair (t, k): its row on the owner, and whether it leads the pairs of this token on that owner.
+            int myE = -1, mySlot = -1, myOwner = -1;
+            float myW = 0.f;
+            if (lane < K) {
+                myE = a.topkIdx[t * K + lane];
+                myW = a.topkW[t * K + lane];
+                if (myE >= 0 && myE < E) {
+                    mySlot = sendBase[myE] + atomicAdd(&a.cursor[myE], 1);
+                    myOwner = myE / EL;
+                    if (mySlot >= a.cap) {
+                        if (a.status != nullptr) {
+                            atomicCAS(a.status, 0, MF_DEV_ERR_BOUNDS);
+                        }
+                        mySlot = -1;  // the owner's buffer is full: this pair is dropped and the call reports the overflow
+                    }
+                }
+                if (a.sendSlot != nullptr) {
+                    a.sendSlot[t * K + lane] = mySlot;
+                }
+            }
+            // Pairs of one (token, owner) form groups of up to 1 + MF_MOE_MAX_SIBLINGS in k order; the first of a group leads it.
+            int before = 0, nsib = 0;
+            int2 sib[MF_MOE_MAX_SIBLINGS];
+            for (int j = 0; j < K; j++) {
+                const int oj = __shfl_sync(0xffffffffu, myOwner, j);
+                const int sj = __shfl_sync(0xffffffffu, mySlot, j);
+                const float wj = __shfl_sync(0xffffffffu, myW, j);
+                if (mySlot >= 0 && sj >= 0 && oj == myOwner && j != lane) {
+                    if (j < lane) {
+                        before++;
+                    } else if (nsib < MF_MOE_MAX_SIBLINGS) {
+                        sib[nsib++] = make_int2(sj, __float_as_int(wj));
+                    }
+                }
+            }
+            const bool leader = mySlot >= 0 && before % (MF_MOE_MAX_SIBLINGS + 1) == 0;
             for (int k = 0; k < K; k++) {
-                const int e = a.topkIdx[t * K + k];
-                if (e < 0 || e >= E) {
+                const int slot = __shfl_sync(0xffffffffu, mySlot, k);
+                if (slot < 0) {
                     continue;
                 }
-                int slot = 0;
-                if (lane == 0) {
-                    slot = sendBase[e] + atomicAdd(&a.cursor[e], 1);
-                    if (a.sendSlot != nullptr) {
-                        a.sendSlot[t * K + k] = slot;
-                    }
-                }
-                slot = __shfl_sync(0xffffffffu, slot, 0);
-                if (slot >= a.cap) {
-                    if (lane == 0 && a.status != nullptr) {
-                        atomicCAS(a.status, 0, MF_DEV_ERR_BOUNDS);
-                    }
-                    continue;
-                }
-                const uint32_t d = (uint32_t)(e / EL);
+                const uint32_t d = (uint32_t)__shfl_sync(0xffffffffu, myOwner, k);
                 unsigned char *dx = reinterpret_cast<unsigned char *>(mf_shm_peer(m, a.recvX, d)) + (size_t)slot * H;
-                float *ds = mf_shm_peer(m, a.recvScale, d) + (size_t)slot * nblk;
+                uint32_t *ds = mf_shm_peer(m, a.recvSf, d) + (size_t)slot * nblk;
                 for (int v = lane; v < H / 16; v += 32) {
                     mf_st16(dx + (size_t)v * 16, *reinterpret_cast<const uint4 *>(myStage + (size_t)v * 16));
                 }
                 for (int v = lane; v < nblk; v += 32) {
                     ds[v] = myScale[v];
                 }
-                if (lane == 0) {
-                    int4 meta = make_int4(me, t, k, __float_as_int(a.topkW[t * K + k]));
-                    mf_shm_peer(m, a.recvMeta, d)[slot] = meta;
+            }
+            if (mySlot >= 0) {
+                const uint32_t d = (uint32_t)myOwner;
+                // Followers of a (token, owner) group are marked; the leader carries the number of siblings and their rows.
+                const int kField = lane | (leader ? (nsib << 8) : MF_MOE_META_FOLLOWER);
+                mf_shm_peer(m, a.recvMeta, d)[mySlot] = make_int4(me, t, kField, __float_as_int(myW));
+                if (leader) {
+                    int2 *sd = mf_shm_peer(m, a.recvSib, d) + (size_t)mySlot * MF_MOE_MAX_SIBLINGS;
+                    for (int i = 0; i < nsib; i++) {
+                        sd[i] = sib[i];
+                    }
                 }
             }
             __syncwarp();
@@ -248,11 +298,16 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
         }
     }
     __syncthreads();
-    const int rows = offs[EL];
+    const int rows = min(offs[EL], a.cap);
     const int vecs = H / 8;
+    const uint32_t R = m->rankCount;
+    // A call whose dispatch failed (overflow, timeout) moves no data; it still walks through the barriers so that the
+    // peers' waits complete.
+    const bool dead = ReadAbort(a.status, &abortFlag) != 0;
 
-    // ---- push: each valid output row goes to its source rank's landing zone [token][k][:]
-    for (int r = blockIdx.x * kWarps + warp; r < rows; r += warpsTotal) {
+    // ---- push: one row per (token, owner): the leader's output plus its siblings', weighted, to the source rank's
+    //      landing zone [token][k of the leader][:]
+    for (int r = blockIdx.x * kWarps + warp; r < rows && !dead; r += warpsTotal) {
         int el = 0;
         while (el + 1 < EL && offs[el + 1] <= r) {
             el++;
@@ -262,13 +317,45 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
         }
         const int4 meta = a.recvMeta[r];
         const uint32_t src = (uint32_t)meta.x;
-        if (src >= m->rankCount) {
+        const int k = meta.z & 0xff, nsib = (meta.z >> 8) & 0xff;
+        if ((meta.z & MF_MOE_META_FOLLOWER) != 0 || src >= R || meta.y < 0 || k >= K || (long long)meta.y * K + k >= a.retRows ||
+            nsib > MF_MOE_MAX_SIBLINGS) {
             continue;
         }
-        const char *y = reinterpret_cast<const char *>(a.y) + (size_t)r * H * 2;
-        char *dst = reinterpret_cast<char *>(mf_shm_peer(m, a.retY, src)) + ((size_t)meta.y * K + meta.z) * H * 2;
+        const int2 *sd = a.recvSib + (size_t)r * MF_MOE_MAX_SIBLINGS;
+        int rowOf[MF_MOE_MAX_SIBLINGS + 1];
+        float wOf[MF_MOE_MAX_SIBLINGS + 1];
+        rowOf[0] = r;
+        wOf[0] = __int_as_float(meta.w);
+        int n = 1;
+        for (int i = 0; i < nsib; i++) {
+            const int2 e = sd[i];
+            if (e.x >= 0 && e.x < rows) {
+                rowOf[n] = e.x;
+                wOf[n] = __int_as_float(e.y);
+                n++;
+            }
+        }
+        char *dst = reinterpret_cast<char *>(mf_shm_peer(m, a.retY, src)) + ((size_t)meta.y * K + k) * H * 2;
         for (int v = lane; v < vecs; v += 32) {
-            mf_st16(dst + (size_t)v * 16, mf_ld16(y + (size_t)v * 16));
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int i = 0; i < n; i++) {
+                const uint4 raw = mf_ld16(reinterpret_cast<const char *>(a.y) + (size_t)rowOf[i] * H * 2 + (size_t)v * 16);
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float2 f = __bfloat1622float2(h[q]);
+                    acc[2 * q] = fmaf(wOf[i], f.x, acc[2 * q]);
+                    acc[2 * q + 1] = fmaf(wOf[i], f.y, acc[2 * q + 1]);
+                }
+            }
+            uint4 pk;
+            __nv_bfloat162 *hp = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                hp[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+            }
+            mf_st16(dst + (size_t)v * 16, pk);
         }
     }
     __threadfence_system();
@@ -283,21 +370,41 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
     if (ReadAbort(a.status, &abortFlag) != 0) {
         return;
     }
-    // ---- reduce over k with the routing weights (fp32, fixed order)
+    // ---- add the owners' partial sums (fp32, fixed order): pair k carries one iff no earlier pair of the token has the same owner
+    const int ELg = EL;
     for (int t = blockIdx.x * kWarps + warp; t < a.T; t += warpsTotal) {
         const char *base = reinterpret_cast<const char *>(a.retY) + (size_t)t * K * H * 2;
         char *o = reinterpret_cast<char *>(a.out) + (size_t)t * H * 2;
+        uint32_t leaders = 0;
+        for (int k = 0; k < K; k++) {
+            const int e = a.topkIdx[t * K + k];
+            if (e < 0 || e >= ELg * (int)R) {
+                continue;
+            }
+            int before = 0;
+            for (int j = 0; j < k; j++) {
+                const int ej = a.topkIdx[t * K + j];
+                if (ej >= 0 && ej < ELg * (int)R && ej / ELg == e / ELg) {
+                    before++;
+                }
+            }
+            if (before % (MF_MOE_MAX_SIBLINGS + 1) == 0) {
+                leaders |= 1u << k;
+            }
+        }
         for (int v = lane; v < vecs; v += 32) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int k = 0; k < K; k++) {
-                const float w = a.topkW[t * K + k];
+                if ((leaders >> k & 1u) == 0) {
+                    continue;
+                }
                 const uint4 raw = mf_ld16_coherent(base + (size_t)k * H * 2 + (size_t)v * 16);
                 const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     float2 f = __bfloat1622float2(h[i]);
-                    acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+                    acc[2 * i] += f.x;
+                    acc[2 * i + 1] += f.y;
                 }
             }
             uint4 pk;

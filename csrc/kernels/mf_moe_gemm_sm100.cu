@@ -58,7 +58,7 @@ struct GemmParams {
     const int *groupOffset;
     const int *groupCount;
     int *status;
-    int G, N, K, mode, outStride;
+    int G, N, K, mode, outStride, rowsTotal;
 };
 
 __device__ __forceinline__ float Silu(float x) { return x / (1.f + __expf(-x)); }
@@ -131,10 +131,6 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
                     if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
                         break;
                     }
-                    if (p.mode & MF_GEMM_DEBUG_NO_LOADS) {
-                        MbarArrive(&s.full[st]);  // pipeline study: tensor core and promotion without operand traffic
-                        continue;
-                    }
                     MbarExpectTx(&s.full[st], 2 * kTileBytes);
                     TmaLoad2D(s.a[st], &tmapA, &s.full[st], kb * BK, rowA);
                     TmaLoad2D(s.b[st], &tmapB, &s.full[st], kb * BK, rowB);
@@ -178,7 +174,8 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
             int g, mt, nt;
             decode(tile, g, mt, nt);
             const int row = p.groupOffset[g] + mt * BM + rowInTile;
-            const bool valid = mt * BM + rowInTile < p.groupCount[g];
+            // Rows past the end of A (group tables that overrun the buffer) are never read or written.
+            const bool valid = mt * BM + rowInTile < p.groupCount[g] && row < p.rowsTotal;
             const float *sa = p.aScale + (size_t)row * KB;
             const float *sb = p.bScale + ((size_t)g * NT + nt) * KB;
             float acc[HC];
@@ -199,14 +196,6 @@ mf_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __gr
                     break;
                 }
                 TcFenceAfter();
-                if (p.mode & MF_GEMM_DEBUG_NO_PROMOTION) {
-                    TcFenceBefore();
-                    __syncwarp();
-                    if (lane == 0) {
-                        MbarArrive(&s.tmemEmpty[buf]);  // pipeline study: loads and MMAs without the per-K-block TMEM read-out
-                    }
-                    continue;
-                }
                 const uint32_t taddr = tmemBase + ((uint32_t)(quad * 32) << 16) + buf * BN + half * HC;
                 float v[HC];
                 TmemLd32Issue(taddr, v);
@@ -285,12 +274,15 @@ __global__ void mf_quant_rows_fp8_kernel(const __nv_bfloat16 *__restrict__ x, un
         if (row >= limit) {
             continue;
         }
+        // With an odd number of blocks per row the upper half-warp has no block in the last pair; it walks through the same
+        // instructions on a zero vector so that the full-mask shuffles below stay convergent.
         const int blk = (int)(pr % pairsPerRow) * 2 + (lane >> 4);
-        if (blk >= blocksPerRow) {
-            continue;
+        const bool active = blk < blocksPerRow;
+        const size_t off = (size_t)row * K + (size_t)(active ? blk : 0) * 128 + (lane & 15) * 8;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (active) {
+            raw = *reinterpret_cast<const uint4 *>(x + off);
         }
-        const size_t off = (size_t)row * K + (size_t)blk * 128 + (lane & 15) * 8;
-        const uint4 raw = *reinterpret_cast<const uint4 *>(x + off);
         const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
         float f[8];
         float amax = 0.f;
@@ -312,9 +304,11 @@ __global__ void mf_quant_rows_fp8_kernel(const __nv_bfloat16 *__restrict__ x, un
         for (int i = 0; i < 4; i++) {
             ps[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] / sc, f[2 * i + 1] / sc), __NV_SATFINITE, __NV_E4M3);
         }
-        *reinterpret_cast<uint2 *>(q + off) = packed;
-        if ((lane & 15) == 0) {
-            scale[(size_t)row * blocksPerRow + blk] = sc;
+        if (active) {
+            *reinterpret_cast<uint2 *>(q + off) = packed;
+            if ((lane & 15) == 0) {
+                scale[(size_t)row * blocksPerRow + blk] = sc;
+            }
         }
     }
 }
@@ -353,10 +347,6 @@ bool MakeMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t K)
 
 }  // namespace
 
-int mf_moe_grouped_gemm_2sm_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const float *aScale, const float *bScale, void *out,
-                                   const int *groupOffset, const int *groupCount, int G, int N, int K, int mode, int *status, int ctas,
-                                   cudaStream_t stream);
-
 extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, const float *bScale, void *out, const int *groupOffset,
                                      const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas, mf_stream_t stream)
 {
@@ -370,16 +360,6 @@ extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const v
     CUtensorMap mapA, mapB;
     if (!MakeMap(&mapA, a, (uint64_t)rowsTotal, (uint64_t)K) || !MakeMap(&mapB, b, (uint64_t)G * N, (uint64_t)K)) {
         return MF_K_LAUNCH_FAILED;
-    }
-    // The two-SM kernel (256-wide tiles over CTA pairs, mf_moe_gemm2_sm100.cu) is opt-in: ctas == -2 or MF_GEMM_2SM=1. Measured
-    // on B200 it is slower than this one-SM kernel (917 vs 1244 TFLOP/s on the prefill shape): both are paced by the per-K-block
-    // promotion of partial sums out of TMEM, not by operand traffic, and the wider tile makes that step longer per thread.
-    static const bool prefer2sm = []() {
-        const char *e = getenv("MF_GEMM_2SM");
-        return e != nullptr && e[0] == '1';
-    }();
-    if ((ctas == -2 || (prefer2sm && ctas >= 0 && rowsTotal >= 192 * G)) && N % 256 == 0) {
-        return mf_moe_grouped_gemm_2sm_launch(mapA, mapB, aScale, bScale, out, groupOffset, groupCount, G, N, K, mode, status, 0, (cudaStream_t)stream);
     }
     if (ctas < 0) {
         ctas = 0;
@@ -396,6 +376,7 @@ extern "C" int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const v
     p.K = K;
     p.mode = mode;
     p.outStride = (mode & 15) == MF_GEMM_EPI_SWIGLU ? N / 2 : N;
+    p.rowsTotal = rowsTotal;
     static bool attrSet = false;
     const size_t smem = sizeof(SharedStorage) + 1024;
     if (!attrSet) {

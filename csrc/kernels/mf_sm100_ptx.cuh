@@ -169,6 +169,49 @@ __device__ __forceinline__ void MmaF8(uint32_t tmemD, uint64_t aDesc, uint64_t b
         "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// ---------------------------------------------------------------------------------------------- block-scaled MMA (kind::mxf8f6f4)
+// Scale factors are UE8M0 bytes (value = 2^(byte - 127)), one per operand row and 32 K-elements. The tensor core reads them
+// from TMEM: row r of a 128-row operand tile sits in lane r % 32 (replicated in all four 32-lane quadrants), 32-bit column
+// r / 32 of the scale-factor area, and byte j of that column belongs to the j-th 32-element K step of a 128-element K block
+// (selected per instruction through the a_sf_id / b_sf_id fields of the descriptor).
+
+// Shared-memory descriptor of one scale-factor atom for tcgen05.cp: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t SmemDescSfAtom(uint32_t smemByteAddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smemByteAddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// Copies one 512-byte scale-factor atom (32 rows x 16 bytes) from shared memory into four TMEM columns starting at `taddr`,
+// replicated into the four lane quadrants. Issued by ONE thread; ordered with the tcgen05.mma that the same thread issues next.
+__device__ __forceinline__ void TmemCpSfAtom(uint32_t taddr, uint64_t smemDesc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smemDesc) : "memory");
+}
+// Generic-proxy writes to shared memory (ordinary stores) become visible to the async proxy (tcgen05.cp, TMA) after this fence.
+__device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Instruction descriptor for kind::mxf8f6f4.block_scale, E4M3 x E4M3 (A/B format 0 at [7,10) and [10,13)), both operands K-major,
+// UE8M0 scale factors (bit 23), N >> 3 at [17,23), M >> 4 at [24,29), byte selectors of the scale-factor columns: B at [4,6), A at
+// [29,31). The accumulator is always fp32.
+__host__ __device__ constexpr uint32_t InstrDescMxF8(uint32_t m, uint32_t n, uint32_t sfId)
+{
+    return (sfId << 4) | (1u << 23) | ((n >> 3) << 17) | ((m >> 4) << 24) | (sfId << 29);
+}
+// D[tmem] (+)= (A * sfa) x (B * sfb)^T for one 32-element K step, issued by ONE thread. sfaTmem / sfbTmem: TMEM addresses of the
+// scale-factor columns (the byte selector travels in the descriptor).
+__device__ __forceinline__ void MmaMxF8(uint32_t tmemD, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t sfaTmem, uint32_t sfbTmem,
+                                        uint32_t accumulate)
+{
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(tmemD),
+        "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(sfaTmem), "r"(sfbTmem)
+        : "memory");
+}
 // Makes `bar` complete once all tcgen05.mma issued so far by this thread have finished (implies fence::before_thread_sync).
 __device__ __forceinline__ void MmaCommit(uint64_t *bar)
 {

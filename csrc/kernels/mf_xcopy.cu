@@ -23,10 +23,18 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kUnroll = 8;
+constexpr size_t kPdlMaxBytes = 32 * 1024;
 
 __global__ void __launch_bounds__(kThreads, 2)
 mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n, size_t tileBytes)
 {
+    // Programmatic dependent launch: when the host sets the stream-serialisation attribute (small copies only), the next
+    // kernel of the stream may be scheduled while this one runs, and this kernel may have been scheduled while its
+    // predecessor ran; the wait returns once the predecessor has completed and its writes are visible, so stream order
+    // is kept and only the launch latency between back-to-back small copies is hidden. Without the attribute both
+    // instructions do nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Tile 0 is stretched by `lead` bytes so that every later tile starts on a 16-byte boundary of dst.
     const size_t lead = (16 - ((uintptr_t)dst & 15)) & 15;
     const size_t body = n > lead ? n - lead : 0;
@@ -317,6 +325,10 @@ extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_str
         const char *e = getenv("MF_XCOPY_TMA");
         return !(e != nullptr && e[0] == '0');
     }();
+    static const bool usePdl = []() {
+        const char *e = getenv("MF_XCOPY_PDL");
+        return !(e != nullptr && e[0] == '0');
+    }();
     if (useTma && ctas >= 0 && n >= (4u << 20) && ((((uintptr_t)dst) ^ ((uintptr_t)src)) & 15) == 0) {
         static bool attr = false;
         const size_t smem = (size_t)kTmaStages * kTmaTile + 128;
@@ -344,8 +356,23 @@ extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_str
     }
     size_t ntiles = (n + tile - 1) / tile;
     size_t grid = ctas > 0 ? (size_t)ctas : (ntiles < maxCtas ? ntiles : maxCtas);
-    mf_xcopy_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>((unsigned char *)dst, (const unsigned char *)src, n, tile);
-    return LaunchResult();
+    // Back-to-back small copies are bound by the launch-to-launch gap, not by bytes: up to kPdlMaxBytes the kernel is
+    // launched with programmatic stream serialisation (measured on two B200s over NVLink: 4.1 us -> 2.5-2.9 us per 4-16 KiB
+    // copy, against 3.1-3.6 us for the copy engine; from 64 KiB on the overlap no longer pays).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (usePdl && n <= kPdlMaxBytes) ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, mf_xcopy_kernel, (unsigned char *)dst, (const unsigned char *)src, n, tile) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return MF_K_LAUNCH_FAILED;
+    }
+    return MF_K_OK;
 }
 
 extern "C" int mf_k_batch_xcopy(const mf_copy_desc_t *descs, const mf_copy_desc_t *descsDev, uint32_t count, uint32_t totalChunks,

@@ -33,6 +33,17 @@ void BindOps(py::module_ &m)
     });
     ops.attr("GEMM_EPI_BF16") = (int)MF_GEMM_EPI_BF16;
     ops.attr("GEMM_EPI_SWIGLU") = (int)MF_GEMM_EPI_SWIGLU;
+    ops.attr("GEMM_EPI_SWIGLU_FP8") = (int)MF_GEMM_EPI_SWIGLU_FP8;
+    ops.attr("MOE_MAX_SIBLINGS") = (int)MF_MOE_MAX_SIBLINGS;
+    ops.def("moe_grouped_gemm_mx", [](uint64_t a, uint64_t aSf, uint64_t b, uint64_t bScale, uint64_t out, uint64_t outSf, uint64_t groupOffset,
+                                      uint64_t groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN, uint64_t status, int ctas,
+                                      uint64_t stream) {
+        return mf_k_moe_grouped_gemm_mx((const void *)a, (const uint32_t *)aSf, (const void *)b, (const float *)bScale, (void *)out, (void *)outSf,
+                                        (const int *)groupOffset, (const int *)groupCount, G, rowsTotal, N, K, mode, tileN, (int *)status, ctas,
+                                        (mf_stream_t)stream);
+    }, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_scale"), py::arg("out"), py::arg("out_sf"), py::arg("group_offset"),
+            py::arg("group_count"), py::arg("G"), py::arg("rows_total"), py::arg("N"), py::arg("K"), py::arg("mode"), py::arg("tile_n") = 0,
+            py::arg("status") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
     ops.def("moe_grouped_gemm", [](uint64_t a, uint64_t aScale, uint64_t b, uint64_t bScale, uint64_t out, uint64_t groupOffset, uint64_t groupCount,
                                    int G, int rowsTotal, int N, int K, int mode, uint64_t status, int ctas, uint64_t stream) {
         return mf_k_moe_grouped_gemm((const void *)a, (const float *)aScale, (const void *)b, (const float *)bScale, (void *)out,
@@ -44,8 +55,8 @@ void BindOps(py::module_ &m)
     }, py::arg("x"), py::arg("q"), py::arg("scale"), py::arg("rows"), py::arg("K"), py::arg("row_limit") = 0, py::arg("stream") = 0);
     ops.attr("MOE_DISPATCH_ARGS_BYTES") = (int)sizeof(mf_moe_dispatch_args_t);
     ops.attr("MOE_COMBINE_ARGS_BYTES") = (int)sizeof(mf_moe_combine_args_t);
-    ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvScale,
-                                         uint64_t recvMeta, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
+    ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvSf,
+                                         uint64_t recvMeta, uint64_t recvSib, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
                                          uint64_t sendSlot, uint64_t status, int T, int cap) {
         mf_moe_dispatch_args_t a{};
         a.meta = (const void *)meta;
@@ -54,8 +65,9 @@ void BindOps(py::module_ &m)
         a.topkW = (const float *)topkW;
         a.cnt = (int *)cnt;
         a.recvX = (void *)recvX;
-        a.recvScale = (float *)recvScale;
+        a.recvSf = (uint32_t *)recvSf;
         a.recvMeta = (int4 *)recvMeta;
+        a.recvSib = (int2 *)recvSib;
         a.localCnt = (int *)localCnt;
         a.cursor = (int *)cursor;
         a.expertOffset = (int *)expertOffset;
@@ -66,19 +78,22 @@ void BindOps(py::module_ &m)
         a.cap = cap;
         return py::bytes((const char *)&a, sizeof(a));
     });
-    ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t expertOffset, uint64_t expertCount, uint64_t retY,
-                                        uint64_t topkW, uint64_t out, uint64_t status, int T) {
+    ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t recvSib, uint64_t expertOffset, uint64_t expertCount,
+                                        uint64_t retY, uint64_t topkIdx, uint64_t out, uint64_t status, int T, int cap, int retRows) {
         mf_moe_combine_args_t a{};
         a.meta = (const void *)meta;
         a.y = (const void *)y;
         a.recvMeta = (const int4 *)recvMeta;
+        a.recvSib = (const int2 *)recvSib;
         a.expertOffset = (const int *)expertOffset;
         a.expertCount = (const int *)expertCount;
         a.retY = (void *)retY;
-        a.topkW = (const float *)topkW;
+        a.topkIdx = (const int *)topkIdx;
         a.out = (void *)out;
         a.status = (int *)status;
         a.T = T;
+        a.cap = cap;
+        a.retRows = retRows;
         return py::bytes((const char *)&a, sizeof(a));
     });
     ops.def("moe_dispatch", [](uint64_t argsDev, int nEmulated, int rankCount, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs,

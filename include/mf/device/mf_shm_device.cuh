@@ -123,7 +123,10 @@ __device__ __forceinline__ bool mf_wait_until_ge(const uint64_t *flag, uint64_t 
     }
 }
 
-/* 16-byte streaming accessors for heap data. */
+/* 16-byte streaming accessors for heap data.
+ * mf_ld16 uses the non-coherent read-only path: legal only for data that nobody writes while the calling kernel runs
+ * (inputs produced by earlier kernels of the stream). Data that another GPU, or another CTA, writes during the kernel and
+ * that becomes visible through a signal or barrier inside the kernel must be read with mf_ld16_coherent. */
 __device__ __forceinline__ uint4 mf_ld16(const void *p)
 {
     uint4 v;
@@ -134,7 +137,7 @@ __device__ __forceinline__ uint4 mf_ld16(const void *p)
 __device__ __forceinline__ uint4 mf_ld16_coherent(const void *p)
 {
     uint4 v;
-    asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ void mf_st16(void *p, const uint4 &v)
@@ -147,7 +150,7 @@ __device__ __forceinline__ void mf_put16(void *remoteDst, const void *localSrc, 
 {
     const uint64_t vecs = n >> 4;
     for (uint64_t i = threadIdx.x; i < vecs; i += blockDim.x) {
-        mf_st16((char *)remoteDst + (i << 4), mf_ld16((const char *)localSrc + (i << 4)));
+        mf_st16((char *)remoteDst + (i << 4), mf_ld16_coherent((const char *)localSrc + (i << 4)));
     }
 }
 __device__ __forceinline__ void mf_get16(void *localDst, const void *remoteSrc, uint64_t n) { mf_put16(localDst, remoteSrc, n); }

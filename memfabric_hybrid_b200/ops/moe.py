@@ -1,11 +1,13 @@
-"""Expert-parallel MoE layer over the symmetric heap: dispatch (fp8 1x128 quantisation fused) → grouped block-scaled FP8
-expert FFN on tcgen05 tensor cores (SwiGLU fused into the first GEMM) → combine (weighted top-k reduction fused).
+"""Expert-parallel MoE layer over the symmetric heap: dispatch (fp8 quantisation with 1x128 power-of-two scales fused) →
+grouped block-scaled FP8 expert FFN on tcgen05 tensor cores (scales applied by the tensor core; SwiGLU and the 1x32
+re-quantisation of the intermediate fused into the first GEMM's epilogue) → combine (owner-side reduction of a token's
+experts that share an owner, then the weighted top-k sum at the source).
 
     layer = FusedMoE(heap, max_tokens, hidden, n_experts, topk, inter, w13_q, w13_s, w2_q, w2_s)
     out = layer(x, topk_idx, topk_w)        # every rank calls; x [T, hidden] bf16, idx int32 [T, topk], w fp32 [T, topk]
 
 `w13` holds this rank's experts' gate/up projections in the interleaved layout of ops.fp8_gemm.interleave_gate_up,
-`w2` the down projections; both e4m3 with 128x128 block scales. `route()` turns router logits into (idx, renormalised w).
+`w2` the down projections; both e4m3 with 128x128 power-of-two block scales (ops.fp8_gemm.quant_weight_mx_torch). `route()` turns router logits into (idx, renormalised w).
 
 ``EmulatedMoE`` drives the same kernels for all ranks of an ``EmulatedHeap`` on one GPU (dispatch and combine each as one
 cooperative launch over all ranks; the per-rank GEMMs in between are ordinary launches) — this is how the multi-rank logic
@@ -54,11 +56,13 @@ class _RankState:
         self.recv_x_off = alloc(cap * hidden, 1024)
         self.recv_s_off = alloc(cap * nblk * 4)
         self.recv_m_off = alloc(cap * 16)
+        self.recv_sib_off = alloc(cap * _ops.MOE_MAX_SIBLINGS * 8)
         self.ret_y_off = alloc(max_tokens * topk * hidden * 2)
         self.cnt = heap.tensor(self.cnt_off, (R, n_experts), torch.int32)
         self.recv_x = heap.tensor(self.recv_x_off, (cap, hidden), torch.uint8).view(torch.float8_e4m3fn)
-        self.recv_s = heap.tensor(self.recv_s_off, (cap, nblk), torch.float32)
+        self.recv_s = heap.tensor(self.recv_s_off, (cap, nblk), torch.int32)  # four UE8M0 bytes per 128-column block
         self.recv_m = heap.tensor(self.recv_m_off, (cap, 4), torch.int32)
+        self.recv_sib = heap.tensor(self.recv_sib_off, (cap, _ops.MOE_MAX_SIBLINGS, 2), torch.int32)
         self.ret_y = heap.tensor(self.ret_y_off, (max_tokens * topk, hidden), torch.bfloat16)
         self.cnt.zero_()
         el = n_experts // R
@@ -68,9 +72,9 @@ class _RankState:
         self.expert_count = torch.zeros(el, dtype=torch.int32, device=device)
         self.send_slot = torch.zeros(max_tokens * topk, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.h1 = torch.empty(cap, inter, dtype=torch.bfloat16, device=device)
+        self.max_rows_ret = max_tokens * topk
         self.h1_q = torch.empty(cap, inter, dtype=torch.float8_e4m3fn, device=device)
-        self.h1_s = torch.empty(cap, inter // 128, dtype=torch.float32, device=device)
+        self.h1_sf = torch.empty(cap, inter // 32, dtype=torch.uint8, device=device)
         self.y = torch.empty(cap, hidden, dtype=torch.bfloat16, device=device)
         self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
 
@@ -84,12 +88,12 @@ class _MoEBase:
         self.launches = 0
 
     def _experts(self, st: _RankState, w13_q, w13_s, w2_q, w2_s, stream=None):
-        """The expert FFN of one rank on what dispatch delivered: GEMM1 (+SwiGLU) → 1x128 quantisation → GEMM2."""
+        """The expert FFN of one rank on what dispatch delivered: GEMM1 (+SwiGLU, + 1x32 quantisation) → GEMM2."""
         rows = st.cap
-        F.grouped_gemm(st.recv_x, st.recv_s, w13_q, w13_s, st.expert_offset, st.expert_count, mode="swiglu", out=st.h1, status=st.status, stream=stream)
-        F.quant_rows_fp8(st.h1, st.h1_q, st.h1_s, row_limit=st.expert_offset[self.el:self.el + 1], stream=stream)
-        F.grouped_gemm(st.h1_q, st.h1_s, w2_q, w2_s, st.expert_offset, st.expert_count, mode="bf16", out=st.y, status=st.status, stream=stream)
-        self.launches += 3
+        F.grouped_gemm_mx(st.recv_x, st.recv_s, w13_q, w13_s, st.expert_offset, st.expert_count, mode="swiglu_fp8", out=st.h1_q, out_sf=st.h1_sf,
+                          status=st.status, stream=stream)
+        F.grouped_gemm_mx(st.h1_q, st.h1_sf, w2_q, w2_s, st.expert_offset, st.expert_count, mode="bf16", out=st.y, status=st.status, stream=stream)
+        self.launches += 2
         return rows
 
 
@@ -120,10 +124,11 @@ class FusedMoE(_MoEBase):
             return
         st, h = self.st, self.heap
         d = _ops.pack_moe_dispatch_args(h.meta_ptr, x.data_ptr(), idx.data_ptr(), w.data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(), st.recv_s.data_ptr(),
-                                        st.recv_m.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(), st.expert_offset.data_ptr(),
+                                        st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(), st.expert_offset.data_ptr(),
                                         st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap)
-        c = _ops.pack_moe_combine_args(h.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.expert_offset.data_ptr(), st.expert_count.data_ptr(),
-                                       st.ret_y.data_ptr(), w.data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T)
+        c = _ops.pack_moe_combine_args(h.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
+                                       st.expert_count.data_ptr(), st.ret_y.data_ptr(), idx.data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T,
+                                       st.cap, st.max_rows_ret)
         self._dargs.copy_(torch.frombuffer(bytearray(d), dtype=torch.uint8))
         self._cargs.copy_(torch.frombuffer(bytearray(c), dtype=torch.uint8))
         self._key = key
@@ -201,10 +206,11 @@ class EmulatedMoE(_MoEBase):
         for r in range(n):
             st, rk = self.states[r], self.eheap.ranks[r]
             d += _ops.pack_moe_dispatch_args(rk.meta_ptr, xs[r].data_ptr(), idxs[r].data_ptr(), ws[r].data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(),
-                                             st.recv_s.data_ptr(), st.recv_m.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(),
+                                             st.recv_s.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(),
                                              st.expert_offset.data_ptr(), st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap)
-            c += _ops.pack_moe_combine_args(rk.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.expert_offset.data_ptr(), st.expert_count.data_ptr(),
-                                            st.ret_y.data_ptr(), ws[r].data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T)
+            c += _ops.pack_moe_combine_args(rk.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
+                                            st.expert_count.data_ptr(), st.ret_y.data_ptr(), idxs[r].data_ptr(), st.out.data_ptr(), st.status.data_ptr(),
+                                            T, st.cap, st.max_rows_ret)
         dargs = torch.frombuffer(bytearray(d), dtype=torch.uint8).cuda()
         cargs = torch.frombuffer(bytearray(c), dtype=torch.uint8).cuda()
         s = torch.cuda.current_stream().cuda_stream
@@ -225,8 +231,8 @@ class EmulatedMoE(_MoEBase):
 
 
 def moe_reference(xs, idxs, ws, weights, n_experts: int, inter: int):
-    """fp32 PyTorch oracle of the whole layer with the same quantisation points: tokens → e4m3 (1x128), FFN1 + SwiGLU in fp32
-    on dequantised operands, bf16 rounding, → e4m3 (1x128), FFN2 in fp32, bf16 rounding, weighted sum over k in fp32.
+    """fp32 PyTorch oracle of the whole layer with the same quantisation points: tokens → e4m3 (1x128 power-of-two scales), FFN1 +
+    SwiGLU in fp32 on dequantised operands → e4m3 (1x32 power-of-two scales), FFN2 in fp32, bf16 rounding, weighted sum over k in fp32.
     xs/idxs/ws: per-rank inputs; weights: per-rank (w13_q, w13_s, w2_q, w2_s). Returns per-rank outputs (fp32)."""
     import torch
 
@@ -238,8 +244,8 @@ def moe_reference(xs, idxs, ws, weights, n_experts: int, inter: int):
     for r in range(R):
         x = xs[r]
         T, H = x.shape
-        xq, xsc = F.quant_act_torch(x)
-        xd = F.dequant_act(xq, xsc)
+        xq, xsf = F.quant_act_mx_torch(x)
+        xd = F.dequant_act_mx(xq, xsf)
         out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
         for k in range(idxs[r].shape[1]):
             e_all = idxs[r][:, k].long()
@@ -249,9 +255,9 @@ def moe_reference(xs, idxs, ws, weights, n_experts: int, inter: int):
                 owner, le = e // el, e % el
                 h = xd[sel] @ w13[owner][le].T
                 h = h.view(len(sel), -1, 2, 32)
-                h = (torch.nn.functional.silu(h[:, :, 0]) * h[:, :, 1]).reshape(len(sel), inter).to(torch.bfloat16)
-                hq, hs = F.quant_act_torch(h)
-                y = (F.dequant_act(hq, hs) @ w2[owner][le].T).to(torch.bfloat16).float()
+                h = (torch.nn.functional.silu(h[:, :, 0]) * h[:, :, 1]).reshape(len(sel), inter)
+                hq, hsf = F.quant_act_mx_torch(h, block=32)
+                y = (F.dequant_act_mx(hq, hsf) @ w2[owner][le].T).to(torch.bfloat16).float()
                 yk[sel] = y
             out += ws[r][:, k:k + 1].float() * yk
         outs.append(out)

@@ -35,7 +35,6 @@ def test_quant_rows_matches_torch():
 
 @pytest.mark.parametrize("counts,N,K", [([128], 128, 128), ([128], 128, 256), ([128], 256, 512), ([1], 128, 128), ([200, 0, 37, 128], 256, 1024),
                                         ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048),
-                                        # large row counts take the two-SM (cta_group::2) kernel: 256-wide tiles over CTA pairs
                                         ([512], 256, 256), ([256], 256, 128), ([700, 256, 1], 512, 1024), ([1000, 130, 257, 640], 768, 2048)])
 def test_grouped_gemm_matches_reference(counts, N, K):
     import torch
@@ -51,8 +50,7 @@ def test_grouped_gemm_matches_reference(counts, N, K):
     w_q, w_s = F.quant_weight_torch(w)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=dev)
-    two_sm = N % 256 == 0 and rows >= 192 * len(counts)  # the CTA-pair kernel is exercised on the large cases
-    F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, out=out, status=status, two_sm=two_sm)
+    F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, out=out, status=status)
     torch.cuda.synchronize()
     assert int(status) == 0
     ref = F.grouped_gemm_reference(a_q, a_s, w_q, w_s, offs, cnts)
@@ -83,7 +81,7 @@ def test_grouped_gemm_swiglu_epilogue(big_counts):
     w = F.interleave_gate_up(wg, wu)
     a_q, a_s = F.quant_act_torch(a)
     w_q, w_s = F.quant_weight_torch(w)
-    out = F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu", two_sm=big_counts is not None)
+    out = F.grouped_gemm(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu")
     torch.cuda.synchronize()
     ref = F.grouped_gemm_reference(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu")
     # cross-check the interleaved layout against the textbook formula on the dequantised, de-interleaved weights
@@ -98,3 +96,81 @@ def test_grouped_gemm_swiglu_epilogue(big_counts):
         torch.testing.assert_close(ref[o[gi]:o[gi] + c[gi]], textbook, rtol=1e-4, atol=1e-4)
         got = out[o[gi]:o[gi] + c[gi]].float()
         torch.testing.assert_close(got, textbook, rtol=2e-2, atol=2e-2 * float(textbook.abs().max() + 1e-6))
+
+
+# ---------------------------------------------------------------------------------------------- block-scaled tensor-core path (UE8M0 scales)
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("counts,N,K", [([128], 256, 128), ([128], 256, 512), ([1], 256, 384), ([200, 0, 37, 128], 256, 1024),
+                                        ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048), ([700, 256, 1], 512, 1024),
+                                        ([1000, 130, 257, 640], 768, 2048)])
+def test_grouped_gemm_mx_matches_reference(counts, N, K, tile_n):
+    import torch
+
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+
+    dev = "cuda"
+    offs, cnts, rows = _groups(counts, dev)
+    g = torch.Generator(device=dev).manual_seed(sum(counts) + N + K)
+    # rows of very different magnitude, so that a misplaced scale factor (wrong row, wrong K block) cannot hide
+    a = torch.randn(rows, K, generator=g, device=dev) * torch.exp2(torch.randint(-6, 7, (rows, 1), generator=g, device=dev).float())
+    a = a * torch.exp2(torch.randint(-3, 4, (1, K // 128), generator=g, device=dev).float()).repeat_interleave(128, dim=1)
+    w = torch.randn(len(counts), N, K, generator=g, device=dev) * 0.05
+    w = w * torch.exp2(torch.randint(-4, 5, (len(counts), N // 128, 1, K // 128, 1), generator=g, device=dev).float()).expand(
+        -1, -1, 128, -1, 128).reshape(len(counts), N, K)
+    a_q, a_sf = F.quant_act_mx_torch(a)
+    w_q, w_s = F.quant_weight_mx_torch(w)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=dev)
+    F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, out=out, status=status, tile_n=tile_n)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    ref = F.grouped_gemm_mx_reference(a_q, a_sf, w_q, w_s, offs, cnts)
+    o, c = offs.tolist(), cnts.tolist()
+    for gi in range(len(counts)):
+        got = out[o[gi]:o[gi] + c[gi]].float()
+        exp = ref[o[gi]:o[gi] + c[gi]]
+        if c[gi] > 0:
+            # per row: rows differ by orders of magnitude
+            tol = 2e-2 * exp.abs().amax(dim=1, keepdim=True) + 1e-6
+            assert bool(((got - exp).abs() <= tol).all()), f"group {gi}: {float(((got - exp).abs() / tol).max())}"
+        pad = out[o[gi] + c[gi]:o[gi + 1]]
+        assert bool(torch.isnan(pad.float()).all()) or pad.numel() == 0  # padding rows are never written
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("counts", [[70, 130, 3], [600, 257, 300]])
+def test_grouped_gemm_mx_swiglu_and_fused_quant(counts, tile_n):
+    import torch
+
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+
+    dev = "cuda"
+    I, K = 256, 512
+    offs, cnts, rows = _groups(counts, dev)
+    g = torch.Generator(device=dev).manual_seed(9)
+    a = torch.randn(rows, K, generator=g, device=dev)
+    wg = torch.randn(len(counts), I, K, generator=g, device=dev) * 0.05
+    wu = torch.randn(len(counts), I, K, generator=g, device=dev) * 0.05
+    a_q, a_sf = F.quant_act_mx_torch(a)
+    w_q, w_s = F.quant_weight_mx_torch(F.interleave_gate_up(wg, wu))
+    out = F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, mode="swiglu", tile_n=tile_n)
+    hq, hsf = F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, mode="swiglu_fp8", tile_n=tile_n)
+    torch.cuda.synchronize()
+    ref = F.grouped_gemm_mx_reference(a_q, a_sf, w_q, w_s, offs, cnts, mode="swiglu")
+    ref_q, ref_sf = F.grouped_gemm_mx_reference(a_q, a_sf, w_q, w_s, offs, cnts, mode="swiglu_fp8")
+    o, c = offs.tolist(), cnts.tolist()
+    for gi in range(len(counts)):
+        sl = slice(o[gi], o[gi] + c[gi])
+        exp = ref[sl]
+        torch.testing.assert_close(out[sl].float(), exp, rtol=2e-2, atol=2e-2 * float(exp.abs().max() + 1e-6))
+        # fused quantisation: scale bytes agree except where fp32 summation order moves an amax across a power of two, and the
+        # dequantised values agree to an e4m3 step
+        same = (hsf[sl] == ref_sf[sl]).float().mean()
+        assert float(same) > 0.99, float(same)
+        assert int((hsf[sl].int() - ref_sf[sl].int()).abs().max()) <= 1
+        got = F.dequant_act_mx(hq[sl], hsf[sl])
+        err = (got - ref_q[sl]).abs()
+        assert float(err.max()) <= 0.13 * float(exp.abs().max()) + 1e-6
+        assert float(err.mean()) <= 5e-3 * float(exp.abs().max())

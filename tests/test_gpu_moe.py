@@ -22,8 +22,8 @@ def _weights(world, n_experts, hidden, inter, seed, device="cuda"):
         wg = torch.randn(el, inter, hidden, generator=g, device=device) * (hidden ** -0.5)
         wu = torch.randn(el, inter, hidden, generator=g, device=device) * (hidden ** -0.5)
         w2 = torch.randn(el, hidden, inter, generator=g, device=device) * (inter ** -0.5)
-        w13_q, w13_s = F.quant_weight_torch(F.interleave_gate_up(wg, wu))
-        w2_q, w2_s = F.quant_weight_torch(w2)
+        w13_q, w13_s = F.quant_weight_mx_torch(F.interleave_gate_up(wg, wu))
+        w2_q, w2_s = F.quant_weight_mx_torch(w2)
         out.append((w13_q, w13_s, w2_q, w2_s))
     return out
 
@@ -67,7 +67,7 @@ def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter)
     weights = _weights(world, n_experts, hidden, inter, 3)
     xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 5)
     cap_rows = T * topk * world + (n_experts // world) * 128
-    heap_bytes = world * n_experts * 4 + cap_rows * (hidden + hidden // 128 * 4 + 16) + T * topk * hidden * 2 + (1 << 20)
+    heap_bytes = world * n_experts * 4 + cap_rows * (hidden + hidden // 128 * 4 + 16 + 56) + T * topk * hidden * 2 + (1 << 20)
     heap = EmulatedHeap(world, heap_bytes)
     layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world))
     outs, status = layer(xs, idxs, ws)
@@ -100,6 +100,53 @@ def test_skewed_routing_all_tokens_to_one_expert():
     outs, status = layer(xs, idxs, ws)
     assert status == [0] * world
     assert layer.states[1].expert_count.tolist() == [0, 2 * T]
+    _check(outs, moe_reference(xs, idxs, ws, weights, n_experts, inter))
+
+
+def test_receive_buffer_overflow_is_reported_and_contained():
+    """Routing skew beyond the capacity of the receive buffer: the call reports MF_DEV_ERR_BOUNDS, the published tables stay
+    inside the buffer, nothing past it is written, and the layer works again on the next, balanced call."""
+    import torch
+
+    from memfabric_hybrid_b200.ops.moe import EmulatedMoE, moe_reference
+    from memfabric_hybrid_b200.parallel.heap import EmulatedHeap
+
+    world, T, hidden, n_experts, topk, inter = 2, 500, 512, 4, 1, 128
+    weights = _weights(world, n_experts, hidden, inter, 31)
+    xs, bal_idx, bal_w = _inputs(world, T, hidden, n_experts, topk, 32)
+    heap = EmulatedHeap(world, 16 << 20)
+    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=1.0)
+    cap = layer.states[0].cap
+    assert cap < 2 * T  # the skewed call below cannot fit
+    idxs = [torch.full((T, 1), 3, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ws = [torch.ones(T, 1, dtype=torch.float32, device="cuda") for _ in range(world)]
+    outs, status = layer(xs, idxs, ws)
+    assert outs is None and any(s == 2 for s in status), status  # MF_DEV_ERR_BOUNDS
+    for st in layer.states:
+        offs, cnts = st.expert_offset.tolist(), st.expert_count.tolist()
+        assert offs[-1] <= cap and all(o + c <= cap for o, c in zip(offs, cnts)), (offs, cnts, cap)
+    assert float((torch.ones(4, device="cuda") + 1).sum()) == 8.0  # the context is alive
+    for st in layer.states:
+        st.status.zero_()
+    outs, status = layer(xs, bal_idx, bal_w)
+    assert status == [0] * world
+    _check(outs, moe_reference(xs, bal_idx, bal_w, weights, n_experts, inter))
+
+
+def test_tokens_with_several_experts_on_one_owner():
+    """top-k larger than the rank count forces every token to have sibling experts on one owner (owner-side reduction)."""
+    import torch
+
+    from memfabric_hybrid_b200.ops.moe import EmulatedMoE, moe_reference
+    from memfabric_hybrid_b200.parallel.heap import EmulatedHeap
+
+    world, T, hidden, n_experts, topk, inter = 2, 40, 512, 24, 12, 128
+    weights = _weights(world, n_experts, hidden, inter, 41)
+    xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 42)
+    heap = EmulatedHeap(world, 32 << 20)
+    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world))
+    outs, status = layer(xs, idxs, ws)
+    assert status == [0] * world
     _check(outs, moe_reference(xs, idxs, ws, weights, n_experts, inter))
 
 
@@ -152,7 +199,7 @@ def _real_rank(rank, world, port, q):
 def test_real_ranks_one_per_gpu():
     import torch
 
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")
