@@ -4,7 +4,7 @@
 of 64 discrete 16 KiB blocks at random aligned offsets; every transfer verified by byte compare. Baseline (oracle and timed):
 memcpy through a plain POSIX shared-memory mapping of the same size.
 
-    python benchmarks/cpu_pool_bench.py [--out gpurun_out/cpu_pool_bench.json]     (no GPU needed)
+    python benchmarks/cpu_pool_bench.py [--out FILE.json]     (no GPU needed)
 """
 from __future__ import annotations
 
@@ -91,7 +91,7 @@ def worker(rank, port, bar, q):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/cpu_pool_bench.json")
+    ap.add_argument("--out", default="")
     args = ap.parse_args()
     ctx = mp.get_context("spawn")
     q, bar, port = ctx.Queue(), ctx.Barrier(2), free_port()
@@ -107,9 +107,10 @@ def main():
     batch = {k: (max(res[0][2][k], res[1][2][k]) if k.endswith("_us") else (min(res[0][2][k], res[1][2][k]) if k.endswith("GBps") else res[0][2][k] and res[1][2][k]))
              for k in res[0][2]}
     print(json.dumps(batch))
-    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
-    with open(args.out, "w") as f:
-        json.dump({"rows": merged, "batch": batch}, f, indent=1)
+    if args.out:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        with open(args.out, "w") as f:
+            json.dump({"rows": merged, "batch": batch}, f, indent=1)
 
 
 if __name__ == "__main__":

@@ -5,7 +5,7 @@ batch of 1 / 8 / 32 requests. Directions: GD→GD (to the next rank's pooled HBM
 (reload). Reported per direction and batch size: p50 / p99 of the blocking call's wall latency (what a serving engine
 sees), the device time of the same work enqueued on a stream, and GB/s (1e9), all as the max over ranks.
 
-    python benchmarks/kv_blocks.py [--pool-gib 8] [--dram-gib 4] [--iters 50] [--out gpurun_out/kv_blocks.json]
+    python benchmarks/kv_blocks.py [--pool-gib 64] [--dram-gib-total 256] [--iters 50] [--out kv_blocks.json]
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/kv_blocks.py
 
 Baseline columns: the same blocks moved with one cudaMemcpyAsync per block (what a copy-engine implementation does).
@@ -42,82 +42,29 @@ def make_requests(nreq: int, span: int, seed: int):
     return offs, sizes
 
 
-def percentile(xs, p):
-    xs = sorted(xs)
-    return xs[min(len(xs) - 1, int(round(p / 100.0 * (len(xs) - 1))))]
-
-
-def measure(handle, srcs, dsts, sizes, copy_type, stream, iters, maxr, native=None):
-    import torch
-
-    n = len(sizes)
-    total = int(sum(sizes))
-    # blocking latency through the public API
-    for _ in range(3):
-        assert handle.copy_data_batch(srcs, dsts, sizes, n, copy_type, 0) == 0
-    lat = []
-    for _ in range(iters):
-        t0 = time.perf_counter()
-        rc = handle.copy_data_batch(srcs, dsts, sizes, n, copy_type, 0)
-        lat.append((time.perf_counter() - t0) * 1e6)
-        assert rc == 0
-    # device time of the enqueued work
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    a.record(stream)
-    for _ in range(iters):
-        handle.copy_data_batch_on_stream(srcs, dsts, sizes, copy_type, stream.cuda_stream, 0)
-    b.record(stream)
-    torch.cuda.synchronize()
-    dev_us = a.elapsed_time(b) * 1e3 / iters
-    out = {
-        "p50_us": round(maxr(percentile(lat, 50)), 1),
-        "p99_us": round(maxr(percentile(lat, 99)), 1),
-        "device_us": round(maxr(dev_us), 1),
-    }
-    out["GBps_p50"] = round(total / (out["p50_us"] * 1e-6) / 1e9, 1)
-    out["GBps_device"] = round(total / (out["device_us"] * 1e-6) / 1e9, 1)
-    if native is not None:
-        # per-block cudaMemcpyAsync on the same stream, then one synchronize: the copy-engine way
-        for _ in range(2):
-            for s, d, z in zip(srcs, dsts, sizes):
-                native.copy_engine(d, s, z, stream.cuda_stream)
-            stream.synchronize()
-        lat2 = []
-        for _ in range(max(5, iters // 4)):
-            t0 = time.perf_counter()
-            for s, d, z in zip(srcs, dsts, sizes):
-                native.copy_engine(d, s, z, stream.cuda_stream)
-            stream.synchronize()
-            lat2.append((time.perf_counter() - t0) * 1e6)
-        out["per_block_memcpy_p50_us"] = round(maxr(percentile(lat2, 50)), 1)
-    return out
-
-
-def kv_latency_quick(pool, rank, world, stream, iters: int = 30):
-    """Small variant used by bench.py on the pool it already has: GD→GD, batch of 1 and 8 requests."""
-    import torch
-
+def kv_latency_quick(pool, rank, world, stream, iters: int = 30, span: int = 1 << 30, base_off: int = 0, with_host: bool = False):
+    """Short variant used by bench.py on a pool it already has. Blocks live in [base_off, base_off + span) of this rank's HBM
+    window (sources) and in the next `span` bytes (destinations). GD→GD for batches of 1 / 8 / 32 requests; with a DRAM pool
+    also GD→GH and GH→GD."""
     import memfabric_hybrid_b200 as mf
+    from benchmarks.workloads import kv_measure
 
-    def maxr(v):
-        if world == 1:
-            return v
-        import torch.distributed as dist
-
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    span = 1 << 30
     me, peer = pool.hbm(rank), pool.hbm((rank + 1) % world)
+    G2G = mf.bm.BmCopyType.G2G
     res = {}
-    for nreq in (1, 8):
+    for nreq in (1, 8, 32):
         so, sizes = make_requests(nreq, span, 11 + nreq)
         do, _ = make_requests(nreq, span, 29 + nreq)
-        srcs = [int(me + o) for o in so]
-        dsts = [int(peer + span + o) for o in do]
-        res[f"gd2gd_batch{nreq}"] = measure(pool.handle, srcs, dsts, [int(s) for s in sizes], mf.bm.BmCopyType.G2G, stream, iters, maxr)
+        sizes_l = [int(s) for s in sizes]
+        srcs = [int(me + base_off + o) for o in so]
+        dsts = [int(peer + base_off + span + o) for o in do]
+        res[f"gd2gd_batch{nreq}"] = kv_measure(pool.handle, srcs, dsts, sizes_l, G2G, stream, iters, mf.native)
+        if with_host and pool.dram_bytes >= nreq * len(BLOCKS_PER_REQUEST) * 128 * KiB:
+            ho, _ = make_requests(nreq, pool.dram_bytes, 7 + nreq)
+            gh = [int(pool.dram(rank) + o) for o in ho]
+            back = [int(me + base_off + span + o) for o in do]
+            res[f"gd2gh_batch{nreq}"] = kv_measure(pool.handle, srcs, gh, sizes_l, G2G, stream, max(5, iters // 3), mf.native)
+            res[f"gh2gd_batch{nreq}"] = kv_measure(pool.handle, gh, back, sizes_l, G2G, stream, max(5, iters // 3), mf.native)
     return res
 
 
@@ -125,13 +72,15 @@ def main():
     import torch
 
     import memfabric_hybrid_b200 as mf
+    from benchmarks.workloads import kv_measure
     from memfabric_hybrid_b200.parallel.pool import env_rank_world, open_pool
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--pool-gib", type=float, default=8.0, help="pooled HBM per rank (the full-size configuration is 64)")
-    ap.add_argument("--dram-gib", type=float, default=4.0, help="pooled DRAM per rank (the full-size configuration is 256 in total)")
+    ap.add_argument("--pool-gib", type=float, default=64.0, help="pooled HBM per rank (the benchmark configuration: 64 GiB per GPU)")
+    ap.add_argument("--dram-gib-total", type=float, default=256.0,
+                    help="pooled host DRAM over all ranks (the benchmark configuration: 256 GiB); every rank contributes an equal share")
     ap.add_argument("--iters", type=int, default=50)
-    ap.add_argument("--out", default="gpurun_out/kv_blocks.json")
+    ap.add_argument("--out", default="", help="also write the result to this JSON file")
     args = ap.parse_args()
     rank, local, world = env_rank_world()
     torch.cuda.set_device(local)
@@ -152,7 +101,7 @@ def main():
         return float(t.item())
 
     hbm = int(args.pool_gib * (1 << 30))
-    dram = int(args.dram_gib * (1 << 30))
+    dram = int(args.dram_gib_total * (1 << 30)) // world // (2 << 20) * (2 << 20)
     pool = open_pool(rank, world, local, hbm, dram_bytes=dram)
     barrier()
     stream = torch.cuda.current_stream()
@@ -172,10 +121,10 @@ def main():
         gd_dst = [int(peer + half + o) for o in do]
         gh = [int(pool.dram(rank) + o) for o in ho]
         back = [int(me + half + o) for o in do]
-        results[f"gd2gd_batch{nreq}"] = measure(pool.handle, gd_src, gd_dst, sizes_l, G2G, stream, args.iters, maxr, mf.native)
+        results[f"gd2gd_batch{nreq}"] = kv_measure(pool.handle, gd_src, gd_dst, sizes_l, G2G, stream, args.iters, mf.native)
         barrier()
-        results[f"gd2gh_batch{nreq}"] = measure(pool.handle, gd_src, gh, sizes_l, G2G, stream, args.iters, maxr, mf.native)
-        results[f"gh2gd_batch{nreq}"] = measure(pool.handle, gh, back, sizes_l, G2G, stream, args.iters, maxr, mf.native)
+        results[f"gd2gh_batch{nreq}"] = kv_measure(pool.handle, gd_src, gh, sizes_l, G2G, stream, args.iters, mf.native)
+        results[f"gh2gd_batch{nreq}"] = kv_measure(pool.handle, gh, back, sizes_l, G2G, stream, args.iters, mf.native)
         barrier()
         # bit-exactness of offload + reload: the reloaded blocks equal the source blocks
         if world == 1:
@@ -185,10 +134,14 @@ def main():
             results[f"roundtrip_exact_batch{nreq}"] = bool(ok)
         if rank == 0:
             print(json.dumps({k: v for k, v in results.items() if k.endswith(f"batch{nreq}")}), flush=True)
+    summary = {"world": world, "request_bytes": REQUEST_BYTES, "blocks_per_request": len(BLOCKS_PER_REQUEST),
+               "hbm_pool_bytes_per_rank": hbm, "dram_pool_bytes_per_rank": dram, "dram_pool_bytes_total": dram * world, "results": results}
     if rank == 0:
+        print(json.dumps({k: v for k, v in summary.items() if k != "results"}), flush=True)
+    if rank == 0 and args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "w") as f:
-            json.dump({"world": world, "request_bytes": REQUEST_BYTES, "blocks_per_request": len(BLOCKS_PER_REQUEST), "results": results}, f, indent=1)
+            json.dump(summary, f, indent=1)
     barrier()
     pool.close()
     if world > 1:

@@ -3,7 +3,7 @@
 DeepSeek-V3 expert shapes per rank at EP=8: 32 experts, FFN1 [rows, 7168] x [4096, 7168]^T with the SwiGLU epilogue and
 FFN2 [rows, 2048] x [7168, 2048]^T; rows per expert 32 (decode: 128 tokens/rank) and 1024 (prefill: 4096 tokens/rank).
 
-    python benchmarks/moe_gemm_bench.py [--out gpurun_out/moe_gemm_bench.json] [--small]
+    python benchmarks/moe_gemm_bench.py [--out FILE.json] [--small]
 """
 from __future__ import annotations
 
@@ -21,7 +21,7 @@ def main():
     from memfabric_hybrid_b200.ops import fp8_gemm as F
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/moe_gemm_bench.json")
+    ap.add_argument("--out", default="")
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tile-n", type=int, default=0, help="0 = let the launcher choose, 128 or 256")
@@ -121,9 +121,10 @@ def main():
         row["tile_n"] = args.tile_n
         del a_bf, w_bf, w_q, w_s, a_q, a_s, out
         torch.cuda.empty_cache()
-    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
-    with open(args.out, "w") as f:
-        json.dump(rows_out, f, indent=1)
+    if args.out:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        with open(args.out, "w") as f:
+            json.dump(rows_out, f, indent=1)
 
 
 if __name__ == "__main__":

@@ -3,7 +3,7 @@
 (example/trans/perf/transfer_perf.cpp:126-171, results example/trans/perf/README.md:61-70): rank 0 → rank 1, block sizes
 32 KiB … 16 MiB; latency = mean wall-clock of 10 blocking single copies, throughput = 10 batches of 32 blocks.
 
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/transfer_perf.py [--out gpurun_out/transfer_perf.json]
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/transfer_perf.py [--out FILE.json]
 
 The reference's published Atlas A3 numbers (SDMA dev0 → dev1) are printed alongside.
 """
@@ -29,7 +29,7 @@ def main():
     from memfabric_hybrid_b200.parallel.pool import env_rank_world, open_pool
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/transfer_perf.json")
+    ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, local, world = env_rank_world()
     torch.cuda.set_device(local)
@@ -66,9 +66,10 @@ def main():
             rows.append({"block": n, "latency_us": round(lat, 1), "batch32_GBps": round(gbps, 1), "reference_a3_latency_us": REF_LAT_US[i],
                          "reference_a3_GBps": REF_GBPS[i]})
             print(json.dumps(rows[-1]), flush=True)
-        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
-        with open(args.out, "w") as f:
-            json.dump({"world": world, "rows": rows}, f, indent=1)
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "w") as f:
+                json.dump({"world": world, "rows": rows}, f, indent=1)
     if world > 1:
         dist.barrier()
     pool.close()

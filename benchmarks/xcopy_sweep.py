@@ -2,7 +2,7 @@
 """Bandwidth sweep of xcopy over the GVA: D2D (local or rank r → r+1), H2D, D2H, GH→GD, sizes 4 KiB – 2 GiB in powers of two,
 against cudaMemcpyAsync on the same buffers. Device-timed (CUDA events), max over ranks, seeded data, GB = 1e9 B.
 
-    python benchmarks/xcopy_sweep.py [--max-log2 31] [--out gpurun_out/xcopy_sweep.json]
+    python benchmarks/xcopy_sweep.py [--max-log2 31] [--out FILE.json]
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/xcopy_sweep.py
 
 Mirrors the reference's bm_perf_benchmark directions (example/bm/BmBenchmark/band_width_calculator.cpp:423-600).
@@ -26,7 +26,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-log2", type=int, default=12)
     ap.add_argument("--max-log2", type=int, default=30)
-    ap.add_argument("--out", default="gpurun_out/xcopy_sweep.json")
+    ap.add_argument("--out", default="")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--ctas", default="", help="comma list of CTA counts to try with the raw kernel at the largest size")
     args = ap.parse_args()
@@ -129,9 +129,10 @@ def main():
     torch.cuda.synchronize()
     ok = int(out[0]) == 0
     if rank == 0:
-        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
-        with open(args.out, "w") as f:
-            json.dump({"world": world, "rows": rows, "cta_rows": cta_rows, "bit_exact": ok}, f, indent=1)
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "w") as f:
+                json.dump({"world": world, "rows": rows, "cta_rows": cta_rows, "bit_exact": ok}, f, indent=1)
         print("bit_exact", ok)
     barrier()
     pool.close()

@@ -497,10 +497,7 @@ void *g_noAllocDevPtr[64] = {nullptr};  // device address of g_noAllocScratch, p
 
 extern "C" int mf_batch_xcopy_noalloc(const uint64_t *srcs, const uint64_t *dsts, const uint64_t *sizes, uint32_t count, void *stream)
 {
-    if (count == 0) {
-        return MF_K_OK;
-    }
-    if (srcs == nullptr || dsts == nullptr || sizes == nullptr) {
+    if (count != 0 && (srcs == nullptr || dsts == nullptr || sizes == nullptr)) {
         fprintf(stderr, "mf_batch_xcopy_noalloc: null array\n");
         return MF_K_INVALID;
     }
@@ -525,6 +522,18 @@ extern "C" int mf_batch_xcopy_noalloc(const uint64_t *srcs, const uint64_t *dsts
             return MF_K_LAUNCH_FAILED;
         }
         g_noAllocDevPtr[dev] = p;
+    }
+    if (count == 0) {
+        return MF_K_OK;  // warm-up call: the module is loaded and the array's address is known from here on
+    }
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing((cudaStream_t)stream, &capture) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return MF_K_LAUNCH_FAILED;
+    }
+    if (capture != cudaStreamCaptureStatusNone) {
+        fprintf(stderr, "mf_batch_xcopy_noalloc: the stream is being captured; the staged copy table cannot be part of a graph\n");
+        return MF_K_INVALID;
     }
     unsigned char *base = static_cast<unsigned char *>(g_noAllocDevPtr[dev]);
     uint64_t chunks = 0;

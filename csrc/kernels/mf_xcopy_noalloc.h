@@ -18,7 +18,14 @@
 // contents; each call zeroes the counter and rewrites the part of the table it uses, on the caller's stream.
 //
 // First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device current) and keeps it
-// for later calls. Make that first call during start-up, before any stream capture is begun on the device.
+// for later calls; an empty batch (count == 0) does just that, which makes it the warm-up call to issue during start-up,
+// before any stream capture is begun on the device and before the embedder takes the remaining memory.
+//
+// Host-side cost: the table travels from ordinary (pageable) static host arrays with cudaMemcpyAsync. For tables up to
+// roughly 64 KiB (about 2700 copies, or a chunk map of that size) the runtime stages the bytes and returns at once; beyond
+// that it first waits until earlier work on `stream` has drained, so a very long table makes the call block the host.
+// A call made while `stream` is being captured into a graph is refused with MF_K_INVALID: the staged table would be
+// read again, with whatever a later call left there, every time the graph ran.
 //
 // The call never invokes cudaMalloc, cudaFree, or any allocating routine of the runtime, of this library or of torch; host
 // side it uses only static storage. The caller passes inputs and outputs as device-visible addresses (local HBM, peer HBM

@@ -16,6 +16,7 @@
 #include "../util/mf_tracer.h"
 #include "../hybm/mf_va_manager.h"
 #include "../kernels/mf_kernels.h"
+#include "../kernels/mf_xcopy_noalloc.h"
 #include "../net/mf_rpc.h"
 #include "../store/mf_store_client.h"
 #include "pymf_parts.h"
@@ -403,6 +404,14 @@ void BindNative(py::module_ &m)
         }
         return mf_k_batch_xcopy(d.data(), nullptr, (uint32_t)d.size(), chunks, nullptr, nullptr, 0, ctas, (mf_stream_t)stream);
     }, py::arg("srcs"), py::arg("dsts"), py::arg("sizes"), py::arg("ctas") = 0, py::arg("stream") = 0);
+    // Any number of copies up to the limits of the allocation-free entry point; tables longer than the inline limit run
+    // through the table kernel.
+    n.def("batch_xcopy_noalloc", [](std::vector<uint64_t> srcs, std::vector<uint64_t> dsts, std::vector<uint64_t> sizes, uint64_t stream) {
+        if (srcs.size() != dsts.size() || srcs.size() != sizes.size()) {
+            return (int)MF_K_INVALID;
+        }
+        return mf_batch_xcopy_noalloc(srcs.data(), dsts.data(), sizes.data(), (uint32_t)srcs.size(), (void *)stream);
+    }, py::arg("srcs"), py::arg("dsts"), py::arg("sizes"), py::arg("stream") = 0);
     n.def("fill_pattern", [](uint64_t dst, uint64_t nbytes, uint64_t seed, uint64_t stream) {
         return mf_k_fill_pattern((void *)dst, nbytes, seed, (mf_stream_t)stream);
     }, py::arg("dst"), py::arg("nbytes"), py::arg("seed"), py::arg("stream") = 0);

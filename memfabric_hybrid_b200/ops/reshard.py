@@ -75,12 +75,16 @@ class ReshardPlan:
 
 
 class Resharder:
-    def __init__(self, heap, plan: ReshardPlan, timeout_ns: int = 0):
+    def __init__(self, heap, plan: ReshardPlan, timeout_ns: int = 0, shard=None):
+        """`shard` = (offset, tensor) of another Resharder over the same source layout: both then read the same heap buffer
+        (e.g. a bf16 and an fp8 destination of one training shard)."""
         import torch
 
         self.heap, self.plan, self.timeout_ns = heap, plan, timeout_ns
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.shard_off, self.shard = heap.empty((plan.shard_elems,), torch.bfloat16)
+        self.shard_off, self.shard = shard if shard is not None else heap.empty((plan.shard_elems,), torch.bfloat16)
+        if self.shard.numel() != plan.shard_elems:
+            raise ValueError("the shared shard does not match this plan's shard size")
         self.dst = torch.empty(plan.dst_bytes, dtype=torch.uint8, device=dev)
         self.scales = torch.empty(max(plan.scale_floats, 1), dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)

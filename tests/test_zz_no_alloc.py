@@ -45,7 +45,8 @@ def test_matches_regular_batch_copy_twice(mf):
     src = torch.empty(region, dtype=torch.uint8, device="cuda")
     out_new = torch.empty(region, dtype=torch.uint8, device="cuda")
     out_old = torch.empty(region, dtype=torch.uint8, device="cuda")
-    stream = torch.cuda.current_stream().cuda_stream
+    assert fn(None, None, None, 0, None) == 0  # warm-up: resolves the built-in table's address, launches nothing
+    side = torch.cuda.Stream()
     for call, count in enumerate((150, 97)):  # within the regular entry point's inline limit so both paths can run it
         rng = np.random.default_rng(40 + call)
         src.copy_(torch.from_numpy(rng.integers(0, 256, region, dtype=np.uint8)).cuda())
@@ -53,8 +54,14 @@ def test_matches_regular_batch_copy_twice(mf):
         out_old.fill_(0x5A)
         sizes, soffs, doffs = _layout(count, region, rng)
         srcs = [src.data_ptr() + o for o in soffs]
+        # first call on the current stream, second on a stream of its own (ordered after the fills by the synchronize)
+        stream = torch.cuda.current_stream().cuda_stream if call == 0 else side.cuda_stream
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(_arr(srcs), _arr([out_new.data_ptr() + o for o in doffs]), _arr(sizes), count, ctypes.c_void_p(stream))
         assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed the amount of free device memory"
         assert mf.native.batch_xcopy_inline(srcs, [out_old.data_ptr() + o for o in doffs], sizes, 0, stream) == 0
         torch.cuda.synchronize()
         assert torch.equal(out_new, out_old), f"call {call}: the two entry points disagree"
