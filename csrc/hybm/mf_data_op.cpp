@@ -394,6 +394,33 @@ std::shared_ptr<DataOperator> MakeCpuDataOp() { return std::make_shared<CpuDataO
 
 // =============================================================================================== compose
 
+namespace {
+std::atomic<uint64_t> g_served[6];
+std::atomic<uint64_t> g_batchGroupsLast{0};
+
+void NoteServed(uint32_t type, uint64_t elems)
+{
+    const int slot = type == OP_KERNEL_LDST ? 0 : (type == OP_COPY_ENGINE ? 1 : 2);
+    g_served[2 * slot].fetch_add(1, std::memory_order_relaxed);
+    g_served[2 * slot + 1].fetch_add(elems, std::memory_order_relaxed);
+}
+}  // namespace
+
+DataOpStats GetDataOpStats()
+{
+    DataOpStats s;
+    s.kernelCalls = g_served[0].load();
+    s.kernelElems = g_served[1].load();
+    s.copyEngineCalls = g_served[2].load();
+    s.copyEngineElems = g_served[3].load();
+    s.cpuCalls = g_served[4].load();
+    s.cpuElems = g_served[5].load();
+    s.batchGroupsLast = g_batchGroupsLast.load();
+    return s;
+}
+
+void NoteBatchGroups(uint32_t groups) { g_batchGroupsLast.store(groups, std::memory_order_relaxed); }
+
 ComposeDataOp::ComposeDataOp(int device, uint32_t allowedOps, std::shared_ptr<TagInfo> tags)
     : device_(device), allowed_(allowedOps), tags_(std::move(tags))
 {
@@ -470,6 +497,7 @@ int ComposeDataOp::DataCopy(const CopyParams &p, CopyDirection dir, const ExtOpt
     for (auto &e : cands) {
         ret = e->DataCopy(p, dir, opt);
         if (ret == BM_OK) {
+            NoteServed(e->Type(), 1);
             return ret;
         }
         MF_WARN("data op: engine " << e->Name() << " failed (" << ret << ") for " << DirectionName(dir) << ", trying the next one");
@@ -492,6 +520,7 @@ int ComposeDataOp::BatchDataCopy(const BatchCopyParams &p, CopyDirection dir, co
     for (auto &e : cands) {
         ret = e->BatchDataCopy(p, dir, opt);
         if (ret == BM_OK) {
+            NoteServed(e->Type(), p.batchSize);
             return ret;
         }
         MF_WARN("data op: engine " << e->Name() << " failed (" << ret << ") for batch " << DirectionName(dir) << ", trying the next one");

@@ -56,6 +56,14 @@ uint32_t DefaultSyncTimeoutMs();
 
 class TagInfo;
 
+// Process-wide counters of which engine served how many calls and elements (observability, and the seam tests use to check
+// that an address a kernel cannot read never reached the kernel engine).
+struct DataOpStats {
+    uint64_t kernelCalls, kernelElems, copyEngineCalls, copyEngineElems, cpuCalls, cpuElems, batchGroupsLast;
+};
+DataOpStats GetDataOpStats();
+void NoteBatchGroups(uint32_t groups);
+
 class ComposeDataOp : public DataOperator {
 public:
     ComposeDataOp(int device, uint32_t allowedOps, std::shared_ptr<TagInfo> tags);

@@ -589,27 +589,74 @@ int MemEntity::BatchCopyData(const BatchCopyParams &p, CopyDirection dir, void *
                  "batch copy: empty or null parameters");
     MF_CHECK_RET(dataOp_ != nullptr, BM_NOT_SUPPORTED, "batch copy: this entity has no host data operator");
     std::shared_lock<std::shared_mutex> lk(mapMu_);
-    ExtOptions opt;
-    opt.stream = stream;
-    opt.flags = flags;
-    // Direction and visibility are taken from the first element (all elements of a batch share a direction); the bounds
-    // of every element's pool side are checked.
-    int rc = ResolveDirection((uint64_t)p.sources[0], (uint64_t)p.destinations[0], &dir, &opt);
-    if (rc != BM_OK) {
-        return rc;
-    }
-    const bool srcPool = SrcClassOf(dir) >= PC_GLOBAL_HOST, dstPool = DstClassOf(dir) >= PC_GLOBAL_HOST;
+    // Every element is placed on its own: which rank owns each side, what the non-pool side really is (device memory,
+    // pinned host memory a kernel can read, or pageable host memory only the copy engine or the CPU may touch), and whether
+    // its pool side stays inside the pool. Elements are then grouped by (source rank, destination rank, direction,
+    // visibility) and every group goes to the data operator as one sub-batch, so the tag rule of each rank pair applies and
+    // an address a kernel cannot dereference never reaches a kernel.
+    // Reference: hybm_entity_default.cpp:767-800 (grouping), :995-1017 (locating), hybm_compose_data_op.cpp:114-175 (use).
+    struct Group {
+        CopyDirection dir;
+        ExtOptions opt;
+        std::vector<uint32_t> idx;
+    };
+    std::vector<Group> groups;
+    auto sameGroup = [](const Group &g, CopyDirection d, const ExtOptions &o) {
+        return g.dir == d && g.opt.srcRank == o.srcRank && g.opt.dstRank == o.dstRank && g.opt.srcDeviceVisible == o.srcDeviceVisible &&
+               g.opt.dstDeviceVisible == o.dstDeviceVisible;
+    };
+    size_t last = 0;
     for (uint32_t i = 0; i < p.batchSize; i++) {
         MF_CHECK_RET(p.sources[i] != nullptr && p.destinations[i] != nullptr, BM_INVALID_PARAM, "batch copy: null pointer at #" << i);
-        if (srcPool) {
+        ExtOptions opt;
+        opt.stream = stream;
+        opt.flags = flags;
+        CopyDirection d = dir;
+        int rc = ResolveDirection((uint64_t)p.sources[i], (uint64_t)p.destinations[i], &d, &opt);
+        if (rc != BM_OK) {
+            MF_ERROR("batch copy: element #" << i << " cannot be placed");
+            return rc;
+        }
+        if (SrcClassOf(d) >= PC_GLOBAL_HOST) {
             MF_CHECK_RET(AddressInEntity((uint64_t)p.sources[i], p.dataSizes[i]), BM_INVALID_PARAM, "batch copy: source #" << i << " leaves the pool");
         }
-        if (dstPool) {
+        if (DstClassOf(d) >= PC_GLOBAL_HOST) {
             MF_CHECK_RET(AddressInEntity((uint64_t)p.destinations[i], p.dataSizes[i]), BM_INVALID_PARAM,
                          "batch copy: destination #" << i << " leaves the pool");
         }
+        if (groups.empty() || !sameGroup(groups[last], d, opt)) {
+            last = groups.size();
+            for (size_t g = 0; g < groups.size(); g++) {
+                if (sameGroup(groups[g], d, opt)) {
+                    last = g;
+                    break;
+                }
+            }
+            if (last == groups.size()) {
+                groups.push_back(Group{d, opt, {}});
+            }
+        }
+        groups[last].idx.push_back(i);
     }
-    return dataOp_->BatchDataCopy(p, dir, opt);
+    NoteBatchGroups((uint32_t)groups.size());
+    if (groups.size() == 1) {
+        return dataOp_->BatchDataCopy(p, groups[0].dir, groups[0].opt);  // the common case: the caller's arrays as they are
+    }
+    for (const Group &g : groups) {
+        std::vector<void *> srcs(g.idx.size()), dsts(g.idx.size());
+        std::vector<uint64_t> sizes(g.idx.size());
+        for (size_t k = 0; k < g.idx.size(); k++) {
+            srcs[k] = p.sources[g.idx[k]];
+            dsts[k] = p.destinations[g.idx[k]];
+            sizes[k] = p.dataSizes[g.idx[k]];
+        }
+        BatchCopyParams sub{srcs.data(), dsts.data(), sizes.data(), (uint32_t)g.idx.size()};
+        int rc = dataOp_->BatchDataCopy(sub, g.dir, g.opt);
+        if (rc != BM_OK) {
+            return rc;
+        }
+    }
+    return BM_OK;
 }
 
 int MemEntity::Wait()

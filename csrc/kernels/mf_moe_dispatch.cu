@@ -307,7 +307,10 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
 
     // ---- push: one row per (token, owner): the leader's output plus its siblings', weighted, to the source rank's
     //      landing zone [token][k of the leader][:]
-    for (int r = blockIdx.x * kWarps + warp; r < rows && !dead; r += warpsTotal) {
+    // Work unit = (row, chunk of 128 vectors): a leader with many siblings is spread over several warps.
+    const int chunks = (vecs + 127) / 128;
+    for (long long u = (long long)blockIdx.x * kWarps + warp; u < (long long)rows * chunks && !dead; u += warpsTotal) {
+        const int r = (int)(u / chunks), ch = (int)(u % chunks);
         int el = 0;
         while (el + 1 < EL && offs[el + 1] <= r) {
             el++;
@@ -337,7 +340,8 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
             }
         }
         char *dst = reinterpret_cast<char *>(mf_shm_peer(m, a.retY, src)) + ((size_t)meta.y * K + k) * H * 2;
-        for (int v = lane; v < vecs; v += 32) {
+        const int vEnd = min(vecs, (ch + 1) * 128);
+        for (int v = ch * 128 + lane; v < vEnd; v += 32) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int i = 0; i < n; i++) {
                 const uint4 raw = mf_ld16(reinterpret_cast<const char *>(a.y) + (size_t)rowOf[i] * H * 2 + (size_t)v * 16);

@@ -28,7 +28,7 @@ constexpr int kTileCols = 256;       // tile width: a warp reads 512 contiguous 
 constexpr int kVecPerRow = kTileCols / 8;
 constexpr int kVecPerThread = (kTile * kTileCols / 8) / kThreads;  // 8
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
@@ -67,26 +67,42 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                     hi = mid;
                 }
             }
-            const mf_reshard_desc_t d = a.descs[lo];
-            const uint32_t tilesPerRow = (d.ncols + kTileCols - 1) / kTileCols;
+            const mf_reshard_desc_t &d = a.descs[lo];
+            const uint32_t nrows = d.nrows, ncols = d.ncols, colsFull = d.colsFull;
+            const uint32_t tilesPerRow = (ncols + kTileCols - 1) / kTileCols;
             const uint32_t local = tile - d.tileStart;
             const uint32_t tr = local / tilesPerRow, tc = local % tilesPerRow;
             const uint32_t rowBase = tr * kTile, colBase = tc * kTileCols;
-
+            // A warp reads one row segment of 512 bytes per trip: lane l owns columns colBase + 8l .. +7 of rows
+            // rowBase + warp, + 16, + 32, ... (16 warps, 8 trips).
+            const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t c = colBase + lane * 8;
+            const bool colOk = c < ncols;
+            // Which shard holds the tile's first element: ONE 64-bit division per tile. A tile spans far fewer elements than a
+            // shard, so every other element of it lives in that shard or in the next; the loop below walks on in the rare
+            // case of tiny shards.
+            const uint64_t tileFlat = d.srcFlatOff + (uint64_t)(d.r0 + rowBase) * colsFull + d.c0 + colBase;
+            const uint64_t owner0 = tileFlat / a.shardElems;
+            const uint64_t rel0 = tileFlat - owner0 * a.shardElems + (uint64_t)warp * colsFull + lane * 8;
+            const uint64_t relStep = (uint64_t)(kThreads / 32) * colsFull;
+            const char *ownerBase = shard0 + owner0 * m->symmetricSize;
             uint4 v[kVecPerThread];
-            float amax = 0.f;
 #pragma unroll
             for (int i = 0; i < kVecPerThread; i++) {
-                const int idx = i * kThreads + (int)threadIdx.x;  // vector index inside the tile: 32 vectors (one warp) per row
-                const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
+                const uint32_t r = rowBase + warp + i * (kThreads / 32);
                 v[i] = make_uint4(0u, 0u, 0u, 0u);
-                if (r < d.nrows && c < d.ncols) {
-                    const uint64_t flat = d.srcFlatOff + (uint64_t)(d.r0 + r) * d.colsFull + d.c0 + c;
-                    const uint64_t owner = flat / a.shardElems, within = flat - owner * a.shardElems;
-                    v[i] = mf_ld16(shard0 + owner * m->symmetricSize + within * 2);
+                if (colOk && r < nrows) {
+                    uint64_t within = rel0 + (uint64_t)i * relStep;
+                    const char *base = ownerBase;
+                    while (within >= a.shardElems) {
+                        within -= a.shardElems;
+                        base += m->symmetricSize;
+                    }
+                    v[i] = mf_ld16_coherent(base + within * 2);
                 }
             }
             if (d.quant) {
+                float amax = 0.f;
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
                     const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v[i]);
@@ -101,9 +117,9 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                 for (int o = 8; o > 0; o >>= 1) {
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                 }
-                const int half = (threadIdx.x & 31) >> 4;
-                if ((threadIdx.x & 15) == 0) {
-                    warpMax[half][threadIdx.x >> 5] = amax;
+                const int half = lane >> 4;
+                if ((lane & 15) == 0) {
+                    warpMax[half][warp] = amax;
                 }
                 __syncthreads();
                 float tmax = 0.f;
@@ -111,36 +127,35 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
                 for (int w = 0; w < kThreads / 32; w++) {
                     tmax = fmaxf(tmax, warpMax[half][w]);
                 }
-                __syncthreads();
+                __syncthreads();  // warpMax is rewritten by the next tile
                 const float sc = fmaxf(tmax, 1e-10f) * (1.f / 448.f);
-                unsigned char *dst = reinterpret_cast<unsigned char *>(a.dst) + d.dstOff;
+                const float inv = 1.f / sc;
+                unsigned char *dst = reinterpret_cast<unsigned char *>(a.dst) + d.dstOff + c;
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
-                    const int idx = i * kThreads + (int)threadIdx.x;
-                    const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
-                    if (r < d.nrows && c < d.ncols) {
+                    const uint32_t r = rowBase + warp + i * (kThreads / 32);
+                    if (colOk && r < nrows) {
                         const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v[i]);
                         uint2 pk;
                         unsigned short *ps = reinterpret_cast<unsigned short *>(&pk);
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             float2 f = __bfloat1622float2(h[q]);
-                            ps[q] = __nv_cvt_float2_to_fp8x2(make_float2(f.x / sc, f.y / sc), __NV_SATFINITE, __NV_E4M3);
+                            ps[q] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
                         }
-                        *reinterpret_cast<uint2 *>(dst + (size_t)r * d.ncols + c) = pk;
+                        *reinterpret_cast<uint2 *>(dst + (size_t)r * ncols) = pk;
                     }
                 }
-                if ((threadIdx.x == 0 || threadIdx.x == 16) && colBase + half * kTile < d.ncols) {
-                    a.dstScale[d.scaleOff + (size_t)tr * (d.ncols / kTile) + tc * 2 + half] = sc;
+                if ((lane & 15) == 0 && warp == 0 && colBase + half * kTile < ncols) {
+                    a.dstScale[d.scaleOff + (size_t)tr * (ncols / kTile) + tc * 2 + half] = sc;
                 }
             } else {
-                char *dst = reinterpret_cast<char *>(a.dst) + d.dstOff;
+                char *dst = reinterpret_cast<char *>(a.dst) + d.dstOff + (size_t)c * 2;
 #pragma unroll
                 for (int i = 0; i < kVecPerThread; i++) {
-                    const int idx = i * kThreads + (int)threadIdx.x;
-                    const uint32_t r = rowBase + idx / kVecPerRow, c = colBase + (idx % kVecPerRow) * 8;
-                    if (r < d.nrows && c < d.ncols) {
-                        mf_st16(dst + ((size_t)r * d.ncols + c) * 2, v[i]);
+                    const uint32_t r = rowBase + warp + i * (kThreads / 32);
+                    if (colOk && r < nrows) {
+                        mf_st16(dst + (size_t)r * ncols * 2, v[i]);
                     }
                 }
             }

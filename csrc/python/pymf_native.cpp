@@ -386,6 +386,18 @@ void BindNative(py::module_ &m)
         d["runtime"] = c.runtimeVersion;
         return d;
     });
+    n.def("data_op_stats", []() {
+        hybm::DataOpStats st = hybm::GetDataOpStats();
+        py::dict d;
+        d["kernel_calls"] = st.kernelCalls;
+        d["kernel_elems"] = st.kernelElems;
+        d["copy_engine_calls"] = st.copyEngineCalls;
+        d["copy_engine_elems"] = st.copyEngineElems;
+        d["cpu_calls"] = st.cpuCalls;
+        d["cpu_elems"] = st.cpuElems;
+        d["batch_groups_last"] = st.batchGroupsLast;
+        return d;
+    });
     n.def("xcopy", [](uint64_t dst, uint64_t src, uint64_t nbytes, int ctas, uint64_t stream) {
         return mf_k_xcopy((void *)dst, (const void *)src, nbytes, ctas, (mf_stream_t)stream);
     }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("ctas") = 0, py::arg("stream") = 0);

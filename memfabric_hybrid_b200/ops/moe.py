@@ -154,7 +154,7 @@ class FusedMoE(_MoEBase):
         import torch
 
         s = stream or torch.cuda.current_stream()
-        ctas = max(1, min(1 << 16, (T * self.topk + 7) // 8))  # one warp per returned row
+        ctas = max(1, min(1 << 16, (T * self.topk * ((self.hidden // 8 + 127) // 128) + 7) // 8))  # one warp per 2 KiB piece of a returned row
         rc = _ops.moe_combine(self._cargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.el, CH_COMBINE, self.heap.next_epoch(CH_COMBINE),
                               self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:

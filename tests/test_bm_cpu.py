@@ -69,6 +69,26 @@ def _pair_worker(rank, port, bar, q):
         for i, o in enumerate(peer_offs):
             assert mine[o:o + (16 << 10)] == peer_blocks[i * (16 << 10):(i + 1) * (16 << 10)].tobytes(), f"block {i}"
         bar.wait(60)
+        # one batch whose elements land on BOTH ranks' windows: every element is placed on its own and the batch is served as
+        # one group per (source rank, destination rank)
+        mix = _seeded(8 * 4096, 900 + rank)
+        msrcs = [mix.ctypes.data + i * 4096 for i in range(8)]
+        mdsts = [b.peer_rank_ptr(H, (rank + i) % 2) + 48 * MiB + (rank * 8 + i) * 4096 for i in range(8)]
+        assert b.copy_data_batch(msrcs, mdsts, [4096] * 8, 8, T.H2GH, 0) == 0, mf.get_last_err_msg()
+        assert mf.native.data_op_stats()["batch_groups_last"] == 2
+        bar.wait(60)
+        got = mf.native.host_read(b.peer_rank_ptr(H, rank) + 48 * MiB, 16 * 4096)
+        for r in range(2):
+            theirs = _seeded(8 * 4096, 900 + r)
+            for i in range(8):
+                if (r + i) % 2 == rank:
+                    o = (r * 8 + i) * 4096
+                    assert got[o:o + 4096] == theirs[i * 4096:(i + 1) * 4096].tobytes(), (r, i)
+        # an element that leaves the pool fails the whole batch before anything is moved
+        bad = list(mdsts)
+        bad[5] = b.peer_rank_ptr(H, 1) + POOL - 8
+        assert b.copy_data_batch(msrcs, bad, [4096] * 8, 8, T.H2GH, 0) != 0
+        bar.wait(60)
         # GH → GH between the two windows, AUTO direction, and refusals
         assert b.copy_data(b.peer_rank_ptr(H, rank), b.peer_rank_ptr(H, peer) + 32 * MiB, 4096, T.G2G, 0) == 0
         assert b.copy_data(b.peer_rank_ptr(H, rank) + 8, b.peer_rank_ptr(H, rank) + 40 * MiB, 100, T.AUTO, 0) == 0

@@ -122,7 +122,7 @@ def _real_rank(rank, world, port, q):
 def test_real_ranks_one_per_gpu():
     import torch
 
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")

@@ -74,3 +74,77 @@ def test_missing_rank_times_out_with_status():
     plans, flat, heap, off = _setup(4, 2, fp8=False)
     results = emulated_reshard(heap, plans, off, timeout_ns=50_000_000, participating=3)
     assert all(st & 0xFF == 1 and st >> 8 == 3 for _, _, st in results)
+
+
+def _real_rank(rank, world, port, q):
+    try:
+        import torch
+
+        from memfabric_hybrid_b200.models import LlamaConfig, param_specs
+        from memfabric_hybrid_b200.ops.fp8_gemm import dequant_weight
+        from memfabric_hybrid_b200.ops.reshard import Resharder, ReshardPlan, reference_reshard
+        from memfabric_hybrid_b200.parallel.heap import SymmetricHeap
+
+        torch.cuda.set_device(rank)
+        tp = 4 if world % 4 == 0 else (2 if world % 2 == 0 else 1)
+        cfg = LlamaConfig(layers=2, hidden=1024, heads=8, kv_heads=4, ffn=2048, vocab=4096)
+        specs = param_specs(cfg)
+        plans = {fp8: ReshardPlan(specs, world, rank % tp, tp, fp8=fp8) for fp8 in (False, True)}
+        p = plans[False]
+        heap = SymmetricHeap(rank, world, rank, p.shard_elems * 2 + (4 << 20), store_url=f"tcp://127.0.0.1:{port}")
+        # the same seeded flat vector on every rank: each writes only its own shard, each can build the oracle
+        g = torch.Generator(device="cuda").manual_seed(17)
+        flat = torch.zeros(p.shard_elems * world, dtype=torch.bfloat16, device="cuda")
+        flat[:p.total_elems] = (torch.randn(p.total_elems, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+        rs = Resharder(heap, plans[False])
+        rs8 = Resharder(heap, plans[True], shard=(rs.shard_off, rs.shard))
+        rs.shard.copy_(flat[rank * p.shard_elems:(rank + 1) * p.shard_elems])
+        torch.cuda.synchronize()
+        heap.barrier()
+        for it in range(2):
+            views = rs()
+            views8 = rs8()
+            torch.cuda.synchronize()
+            assert rs.check_status() == 0 and rs8.check_status() == 0
+            ref, ref8 = reference_reshard(flat, plans[False]), reference_reshard(flat, plans[True])
+            for e in plans[False].entries:
+                assert torch.equal(views[e.spec.name].reshape(-1), ref[e.spec.name].reshape(-1)), f"rank {rank} {e.spec.name}"
+            for e in plans[True].entries:
+                if not e.quant:
+                    assert torch.equal(views8[e.spec.name].reshape(-1), ref8[e.spec.name].reshape(-1))
+                    continue
+                qd, sc = views8[e.spec.name]
+                q_ref, sc_ref = ref8[e.spec.name]
+                torch.testing.assert_close(sc, sc_ref, rtol=1e-6, atol=0)
+                assert float((qd.float() != q_ref.float()).float().mean()) < 2e-3
+                assert float((dequant_weight(qd, sc) - dequant_weight(q_ref, sc_ref)).abs().max()) <= float(sc.max()) * 32 + 1e-6
+            heap.barrier()
+        heap.close()
+        q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(e)))
+
+
+def test_real_ranks_one_per_gpu():
+    import multiprocessing as mp
+
+    import torch
+
+    from conftest import free_port
+
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    ps = [ctx.Process(target=_real_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in ps)
+    for p in ps:
+        p.join(timeout=60)
+    assert res == [(r, "ok") for r in range(world)], res

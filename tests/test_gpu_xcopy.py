@@ -123,6 +123,53 @@ def test_all_directions_roundtrip(mf, pool):
     assert h.copy_data(ld.data_ptr(), pool.hbm() + pool.hbm_bytes - 16, 4096, T.L2G, 0) != 0
 
 
+def test_batch_with_mixed_local_sides_is_split_by_placement(mf, pool):
+    """One batch whose local sides are pageable host, pinned host, device and pooled memory: every element is placed on its
+    own; the pageable ones go to the copy engine as their own group and the kernel engine never sees them (checked on the
+    engine counters, not by provoking a fault), and every byte arrives."""
+    import torch
+
+    T = mf.bm.BmCopyType
+    blk = 64 * 1024
+    gd = pool.hbm() + 8 * MiB
+    pageable = _rand(4 * blk, 1)
+    pinned = torch.from_numpy(_rand(4 * blk, 2)).pin_memory()
+    device = torch.from_numpy(_rand(4 * blk, 3)).cuda()
+    pooled = pool.hbm() + 64 * MiB
+    pooled_ref = _rand(4 * blk, 4)
+    assert pool.handle.copy_data(pooled_ref.ctypes.data, pooled, 4 * blk, T.H2G, 0) == 0
+    torch.cuda.synchronize()
+    srcs, expect = [], []
+    for i in range(4):  # interleaved on purpose: element 0 is pinned (device-visible), pageable elements come later
+        srcs += [pinned.data_ptr() + i * blk, pageable.ctypes.data + i * blk, device.data_ptr() + i * blk, pooled + i * blk]
+        expect += [pinned.numpy()[i * blk:(i + 1) * blk], pageable[i * blk:(i + 1) * blk], device.cpu().numpy()[i * blk:(i + 1) * blk],
+                   pooled_ref[i * blk:(i + 1) * blk]]
+    dsts = [gd + i * blk for i in range(16)]
+    before = mf.native.data_op_stats()
+    assert pool.handle.copy_data_batch(srcs, dsts, [blk] * 16, 16, T.AUTO, 0) == 0, mf.get_last_err_msg()
+    after = mf.native.data_op_stats()
+    assert after["batch_groups_last"] >= 2
+    assert after["copy_engine_elems"] - before["copy_engine_elems"] == 4   # exactly the four pageable elements
+    assert after["kernel_elems"] - before["kernel_elems"] == 12
+    out = np.zeros(16 * blk, dtype=np.uint8)
+    assert pool.handle.copy_data(gd, out.ctypes.data, 16 * blk, T.G2H, 0) == 0
+    for i in range(16):
+        assert (out[i * blk:(i + 1) * blk] == expect[i]).all(), f"element {i}"
+    # the other way round: pooled sources into pageable, pinned and device destinations
+    out_page = np.zeros(2 * blk, dtype=np.uint8)
+    out_pin = torch.zeros(2 * blk, dtype=torch.uint8).pin_memory()
+    out_dev = torch.zeros(2 * blk, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    dsts2 = [out_pin.data_ptr(), out_page.ctypes.data, out_dev.data_ptr(), out_page.ctypes.data + blk, out_pin.data_ptr() + blk, out_dev.data_ptr() + blk]
+    srcs2 = [gd + i * blk for i in range(6)]
+    before = mf.native.data_op_stats()
+    assert pool.handle.copy_data_batch(srcs2, dsts2, [blk] * 6, 6, T.AUTO, 0) == 0, mf.get_last_err_msg()
+    after = mf.native.data_op_stats()
+    assert after["copy_engine_elems"] - before["copy_engine_elems"] == 2
+    assert (out_pin.numpy()[:blk] == expect[0]).all() and (out_page[:blk] == expect[1]).all() and (out_dev.cpu().numpy()[:blk] == expect[2]).all()
+    assert (out_page[blk:] == expect[3]).all() and (out_pin.numpy()[blk:] == expect[4]).all() and (out_dev.cpu().numpy()[blk:] == expect[5]).all()
+
+
 @pytest.mark.parametrize("count", [1, 7, 122, 168, 169, 1000])
 def test_batch_copy(mf, pool, count):
     import torch
