@@ -4,6 +4,7 @@
 
 #include "../net/mf_rpc.h"
 #include "../store/mf_store_client.h"
+#include "../net/mf_tls.h"
 #include "../util/mf_log.h"
 #include "../util/mf_tracer.h"
 #include "mf/mf.h"
@@ -167,19 +168,55 @@ extern "C" int32_t mf_set_log_level(int level)
     return MF_OK;
 }
 
-extern "C" int32_t mf_set_conf_store_tls(bool enable, const char * /*tlsInfo*/, uint32_t /*tlsInfoLen*/)
+// TLS for every config-store link of this process (reference: smem_set_conf_store_tls / smem_set_config_store_tls_key,
+// src/smem/include/host/smem.h; text form of doc/SECURITYNOTE.md:27-61). The options take effect for servers started and
+// clients connected afterwards; both ends of a store must use the same setting.
+extern "C" int32_t mf_set_conf_store_tls(bool enable, const char *tlsInfo, uint32_t tlsInfoLen)
 {
-    if (enable) {
-        MF_ERROR("set_conf_store_tls: TLS for the store link is not available in this build");
+    net::TlsOptions opt = net::GetStoreTlsOptions();
+    if (!enable) {
+        opt.enable = false;
+        net::SetStoreTlsOptions(opt);
+        return MF_OK;
+    }
+    if (tlsInfo == nullptr || tlsInfoLen == 0 || tlsInfoLen > 64 * 1024) {
+        MF_ERROR("set_conf_store_tls: enabling TLS needs the option text (tlsCaPath, tlsCaFile, tlsCert, ...)");
+        return MF_INVALID_PARAM;
+    }
+    net::TlsOptions parsed;
+    parsed.pk = opt.pk;  // a key registered earlier stays
+    parsed.pkPwd = opt.pkPwd;
+    parsed.decrypt = opt.decrypt;
+    std::string err;
+    if (!net::ParseTlsInfo(std::string(tlsInfo, tlsInfoLen), &parsed, &err)) {
+        MF_ERROR("set_conf_store_tls: " << err);
+        return MF_INVALID_PARAM;
+    }
+    if (!net::TlsLibraryAvailable(parsed.packagePath, &err)) {
+        MF_ERROR("set_conf_store_tls: " << err);
         return MF_ERROR;
     }
+    parsed.enable = true;
+    net::SetStoreTlsOptions(parsed);
     return MF_OK;
 }
 
-extern "C" int32_t mf_set_config_store_tls_key(const char *, uint32_t, const char *, uint32_t, mf_decrypt_handler)
+extern "C" int32_t mf_set_config_store_tls_key(const char *tlsPk, uint32_t tlsPkLen, const char *tlsPkPw, uint32_t tlsPkPwLen, mf_decrypt_handler h)
 {
-    MF_ERROR("set_config_store_tls_key: TLS for the store link is not available in this build");
-    return MF_ERROR;
+    if (tlsPk == nullptr || tlsPkLen == 0 || tlsPkLen > (1u << 20) || (tlsPkPw == nullptr && tlsPkPwLen != 0) || tlsPkPwLen > (10u << 20)) {
+        MF_ERROR("set_config_store_tls_key: the private key (PEM text or file path) is required; the pass phrase is at most 10 MiB");
+        return MF_INVALID_PARAM;
+    }
+    net::TlsOptions opt = net::GetStoreTlsOptions();
+    opt.pk.assign(tlsPk, tlsPkLen);
+    opt.pkPwd.assign(tlsPkPw != nullptr ? tlsPkPw : "", tlsPkPwLen);
+    if (h != nullptr) {
+        opt.decrypt = [h](const char *cipher, size_t cipherLen, char *plain, size_t &plainLen) { return h(cipher, cipherLen, plain, &plainLen); };
+    } else {
+        opt.decrypt = nullptr;
+    }
+    net::SetStoreTlsOptions(opt);
+    return MF_OK;
 }
 
 extern "C" const char *mf_get_last_err_msg(void) { return LastError::Get(); }

@@ -1,5 +1,7 @@
 #include "mf_rpc.h"
 
+#include "mf_tls.h"
+
 #include <arpa/inet.h>
 #include <cerrno>
 #include <cstring>
@@ -179,6 +181,7 @@ static std::string Encode(const Frame &f)
 // ---------------------------------------------------------------------------------------------- server
 
 struct RpcServer::Conn {
+    std::unique_ptr<TlsSession> tls;  // guarded by RpcServer::mu_
     int fd{-1};
     LinkId id{0};
     bool hello{false};
@@ -191,6 +194,8 @@ struct RpcServer::Conn {
 
 RpcServer::RpcServer() = default;
 RpcServer::~RpcServer() { Stop(); }
+
+void RpcServer::SetTls(std::shared_ptr<TlsContext> ctx) { tls_ = std::move(ctx); }
 
 void RpcServer::SetHandlers(MsgHandler onMsg, LinkUpHandler onUp, LinkDownHandler onDown)
 {
@@ -248,6 +253,26 @@ int RpcServer::Start(const Endpoint &ep)
 
 void RpcServer::Stop()
 {
+    if (!running_.load()) {
+        return;
+    }
+    {
+        // Orderly end: every peer hears it before its socket closes.
+        std::vector<LinkId> ids;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            for (auto &kv : conns_) {
+                if (kv.second->hello) {
+                    ids.push_back(kv.first);
+                }
+            }
+        }
+        Frame bye;
+        bye.type = MSG_GOODBYE;
+        for (LinkId id : ids) {
+            Send(id, bye);
+        }
+    }
     if (!running_.exchange(false)) {
         return;
     }
@@ -297,6 +322,19 @@ int RpcServer::Send(LinkId link, const Frame &f)
         return -1;
     }
     Conn &c = *it->second;
+    if (c.tls) {
+        std::string wire;
+        if (c.tls->Encrypt(bytes.data(), bytes.size(), &wire) != 0) {
+            MF_WARN("rpc server: tls write failed on link " << c.id << ": " << c.tls->LastError());
+            return -1;
+        }
+        bytes.swap(wire);
+    }
+    return SendBytesLocked(c, std::move(bytes));
+}
+
+int RpcServer::SendBytesLocked(Conn &c, std::string bytes)
+{
     size_t off = 0;
     if (c.out.empty()) {
         // Fast path: nothing queued, try to push the bytes out right now.
@@ -344,6 +382,13 @@ void RpcServer::Accept()
         SetNoDelay(fd);
         auto c = std::make_shared<Conn>();
         c->fd = fd;
+        if (tls_) {
+            c->tls = tls_->NewSession();
+            if (!c->tls) {
+                ::close(fd);
+                continue;
+            }
+        }
         {
             std::lock_guard<std::mutex> g(mu_);
             c->id = nextLink_++;
@@ -407,24 +452,49 @@ void RpcServer::Flush(const std::shared_ptr<Conn> &c)
 void RpcServer::OnReadable(const std::shared_ptr<Conn> &c)
 {
     char buf[65536];
+    std::string raw;
+    std::string &sink = c->tls ? raw : c->in;
+    bool eof = false;
     while (true) {
         ssize_t n = ::recv(c->fd, buf, sizeof(buf), 0);
         if (n > 0) {
-            c->in.append(buf, (size_t)n);
+            sink.append(buf, (size_t)n);
             if ((size_t)n < sizeof(buf)) {
                 break;
             }
         } else if (n == 0) {
-            Drop(c);
-            return;
+            eof = true;
+            break;
         } else if (errno == EINTR) {
             continue;
         } else if (errno == EAGAIN || errno == EWOULDBLOCK) {
             break;
         } else {
+            eof = true;
+            break;
+        }
+    }
+    if (c->tls && !raw.empty()) {
+        // Ciphertext in, plaintext out; records the session itself wants to send (handshake, alerts) go to the queue.
+        std::string wire;
+        bool ok;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            ok = c->tls->Feed(raw.data(), raw.size()) && c->tls->Pump(&c->in, &wire) == 0;
+            if (!wire.empty() && !c->dead) {
+                SendBytesLocked(*c, std::move(wire));
+            }
+        }
+        if (!ok) {
+            MF_WARN("rpc server: tls failure on link " << c->id << " (" << c->tls->LastError() << "), dropping the link");
+            Flush(c);
             Drop(c);
             return;
         }
+    }
+    if (eof && c->in.size() < sizeof(WireHeader)) {
+        Drop(c);
+        return;
     }
     size_t pos = 0;
     while (c->in.size() - pos >= sizeof(WireHeader)) {
@@ -476,6 +546,9 @@ void RpcServer::OnReadable(const std::shared_ptr<Conn> &c)
     }
     if (pos > 0) {
         c->in.erase(0, pos);
+    }
+    if (eof) {
+        Drop(c);
     }
 }
 
@@ -552,6 +625,8 @@ void RpcServer::Loop()
 RpcClient::RpcClient() = default;
 RpcClient::~RpcClient() { Close(); }
 
+void RpcClient::SetTls(std::shared_ptr<TlsContext> ctx) { tlsCtx_ = std::move(ctx); }
+
 static bool ReadFull(int fd, void *buf, size_t len)
 {
     char *p = (char *)buf;
@@ -586,10 +661,100 @@ static bool WriteFull(int fd, const void *buf, size_t len)
     return true;
 }
 
+bool RpcClient::IoWrite(const void *p, size_t n)
+{
+    if (!tls_) {
+        return WriteFull(fd_, p, n);
+    }
+    std::string wire;
+    {
+        std::lock_guard<std::mutex> g(tlsMu_);
+        if (tls_->Encrypt(static_cast<const char *>(p), n, &wire) != 0) {
+            return false;
+        }
+    }
+    return WriteFull(fd_, wire.data(), wire.size());
+}
+
+bool RpcClient::IoRead(void *p, size_t n)
+{
+    if (!tls_) {
+        return ReadFull(fd_, p, n);
+    }
+    char buf[65536];
+    while (plainBuf_.size() - plainOff_ < n) {
+        ssize_t r = ::recv(fd_, buf, sizeof(buf), 0);
+        if (r < 0 && errno == EINTR) {
+            continue;
+        }
+        if (r <= 0) {
+            return false;
+        }
+        // Whatever the session wants to send in response (key updates, alerts) must leave in record order: take the send
+        // lock first, as every writer does.
+        std::lock_guard<std::mutex> gs(sendMu_);
+        std::string wire;
+        int rc;
+        {
+            std::lock_guard<std::mutex> g(tlsMu_);
+            rc = tls_->Feed(buf, (size_t)r) ? tls_->Pump(&plainBuf_, &wire) : -1;
+        }
+        if (!wire.empty()) {
+            WriteFull(fd_, wire.data(), wire.size());
+        }
+        if (rc < 0) {
+            MF_WARN("rpc client: tls failure: " << tls_->LastError());
+            return false;
+        }
+    }
+    std::memcpy(p, plainBuf_.data() + plainOff_, n);
+    plainOff_ += n;
+    if (plainOff_ == plainBuf_.size()) {
+        plainBuf_.clear();
+        plainOff_ = 0;
+    }
+    return true;
+}
+
+bool RpcClient::TlsHandshake(int fd)
+{
+    tls_ = tlsCtx_->NewSession();
+    if (!tls_) {
+        return false;
+    }
+    plainBuf_.clear();
+    plainOff_ = 0;
+    char buf[16384];
+    while (true) {
+        std::string wire;
+        if (tls_->Pump(&plainBuf_, &wire) < 0) {
+            if (!wire.empty()) {
+                WriteFull(fd, wire.data(), wire.size());
+            }
+            MF_WARN("rpc client: tls handshake failed: " << tls_->LastError());
+            return false;
+        }
+        if (!wire.empty() && !WriteFull(fd, wire.data(), wire.size())) {
+            return false;
+        }
+        if (tls_->HandshakeDone()) {
+            return true;
+        }
+        ssize_t r = ::recv(fd, buf, sizeof(buf), 0);
+        if (r < 0 && errno == EINTR) {
+            continue;
+        }
+        if (r <= 0 || !tls_->Feed(buf, (size_t)r)) {
+            return false;
+        }
+    }
+}
+
 int RpcClient::Connect(const Endpoint &ep, uint64_t peerId, int retries, int retryDelayMs)
 {
     Close();
     closing_.store(false);
+    goodbye_.store(false);
     sockaddr_storage ss{};
     socklen_t len = 0;
     if (Resolve(ep, &ss, &len, false) != 0) {
@@ -612,12 +777,18 @@ int RpcClient::Connect(const Endpoint &ep, uint64_t peerId, int retries, int ret
             WireHeader h{};
             timeval tv{10, 0};
             setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
-            bool ok = WriteFull(fd, bytes.data(), bytes.size()) && ReadFull(fd, &h, sizeof(h)) && h.magic == kWireMagic &&
-                      h.type == MSG_HELLO_ACK && h.bodyLen == 0 && h.result == RPC_OK;
+            fd_ = fd;
+            tls_.reset();
+            bool ok = tlsCtx_ == nullptr || TlsHandshake(fd);
+            ok = ok && IoWrite(bytes.data(), bytes.size()) && IoRead(&h, sizeof(h)) && h.magic == kWireMagic && h.type == MSG_HELLO_ACK &&
+                 h.bodyLen == 0 && h.result == RPC_OK;
+            if (!ok) {
+                fd_ = -1;
+                tls_.reset();
+            }
             if (ok) {
                 tv = timeval{0, 0};
                 setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
-                fd_ = fd;
                 connected_.store(true);
                 reader_ = std::thread([this]() { ReaderLoop(); });
                 return 0;
@@ -681,7 +852,7 @@ int RpcClient::SendFrame(uint16_t type, uint32_t seq, const std::string &body)
     if (!connected_.load() || fd_ < 0) {
         return -1;
     }
-    return WriteFull(fd_, bytes.data(), bytes.size()) ? 0 : -1;
+    return IoWrite(bytes.data(), bytes.size()) ? 0 : -1;
 }
 
 int RpcClient::Call(uint16_t type, const std::string &body, Frame *reply, int64_t timeoutMs)
@@ -754,7 +925,7 @@ void RpcClient::ReaderLoop()
 {
     while (!closing_.load()) {
         WireHeader h{};
-        if (!ReadFull(fd_, &h, sizeof(h)) || h.magic != kWireMagic || h.bodyLen > kMaxBodyLen) {
+        if (!IoRead(&h, sizeof(h)) || h.magic != kWireMagic || h.bodyLen > kMaxBodyLen) {
             break;
         }
         Frame f;
@@ -762,8 +933,12 @@ void RpcClient::ReaderLoop()
         f.result = h.result;
         f.seq = h.seq;
         f.body.resize(h.bodyLen);
-        if (h.bodyLen > 0 && !ReadFull(fd_, &f.body[0], h.bodyLen)) {
+        if (h.bodyLen > 0 && !IoRead(&f.body[0], h.bodyLen)) {
             break;
+        }
+        if (f.type == MSG_GOODBYE) {
+            goodbye_.store(true);  // the close that follows is the end of the job, not a failure
+            continue;
         }
         std::shared_ptr<Pending> p;
         {

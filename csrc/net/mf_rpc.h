@@ -22,13 +22,17 @@
 namespace mf {
 namespace net {
 
+class TlsContext;
+class TlsSession;
+
 constexpr uint32_t kWireMagic = 0x4D464231u;  // "MFB1"
 constexpr uint16_t kWireVersion = 1;
 constexpr uint32_t kMaxBodyLen = 80u * 1024u * 1024u;  // a little above the 64 MiB value cap of the store
 
 // Transport-level result codes placed in Frame::result by the transport itself (store codes share the field).
 enum : int16_t { RPC_OK = 0, RPC_IO_ERROR = -602, RPC_TIMEOUT = -601 };
-enum : uint16_t { MSG_HELLO = 0xFFF0, MSG_HELLO_ACK = 0xFFF1 };
+// MSG_GOODBYE: sent by a server that shuts down in good order, so that clients can tell an orderly end from a broken link.
+enum : uint16_t { MSG_HELLO = 0xFFF0, MSG_HELLO_ACK = 0xFFF1, MSG_GOODBYE = 0xFFF2 };
 
 #pragma pack(push, 1)
 struct WireHeader {
@@ -78,8 +82,11 @@ public:
     RpcServer();
     ~RpcServer();
     void SetHandlers(MsgHandler onMsg, LinkUpHandler onUp, LinkDownHandler onDown);
+    // Every link accepted from now on speaks TLS 1.3 with this (server-role) context; nullptr = plain TCP. Call before Start.
+    void SetTls(std::shared_ptr<TlsContext> ctx);
     // Binds and starts the I/O thread. port 0 picks a free port. Returns 0 or -errno; EADDRINUSE is reported as such.
     int Start(const Endpoint &ep);
+    // Tells every link goodbye (so that the peers see an orderly end, not a failure), then closes them and the listener.
     void Stop();
     uint16_t Port() const { return port_; }
     bool Running() const { return running_.load(); }
@@ -96,6 +103,7 @@ private:
     void Flush(const std::shared_ptr<Conn> &c);
     void Drop(const std::shared_ptr<Conn> &c);
     void Wake();
+    int SendBytesLocked(Conn &c, std::string bytes);
 
     MsgHandler onMsg_;
     LinkUpHandler onUp_;
@@ -109,6 +117,7 @@ private:
     std::unordered_map<int, LinkId> byFd_;
     std::deque<LinkId> pendingClose_;
     LinkId nextLink_{1};
+    std::shared_ptr<TlsContext> tls_;
 };
 
 class RpcClient {
@@ -118,6 +127,10 @@ public:
 
     RpcClient();
     ~RpcClient();
+    // Speak TLS 1.3 with this (client-role) context on the next Connect; nullptr = plain TCP.
+    void SetTls(std::shared_ptr<TlsContext> ctx);
+    // True if the server announced an orderly shutdown on the link that was open last.
+    bool PeerSaidGoodbye() const { return goodbye_.load(); }
     // Tries up to `retries` times, sleeping retryDelayMs between attempts. 0 on success.
     int Connect(const Endpoint &ep, uint64_t peerId, int retries, int retryDelayMs);
     void Close();
@@ -142,7 +155,16 @@ private:
     int SendFrame(uint16_t type, uint32_t seq, const std::string &body);
     void ReaderLoop();
     void FailAll();
+    bool IoWrite(const void *p, size_t n);  // caller holds sendMu_ (or is the only thread: during Connect)
+    bool IoRead(void *p, size_t n);         // reader thread (or Connect)
+    bool TlsHandshake(int fd);
 
+    std::shared_ptr<TlsContext> tlsCtx_;
+    std::unique_ptr<TlsSession> tls_;
+    std::mutex tlsMu_;        // lock order: sendMu_ before tlsMu_
+    std::string plainBuf_;    // decrypted bytes not yet consumed by the reader
+    size_t plainOff_{0};
+    std::atomic<bool> goodbye_{false};
     int fd_{-1};
     std::atomic<bool> connected_{false};
     std::atomic<bool> closing_{false};

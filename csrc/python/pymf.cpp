@@ -5,6 +5,8 @@
 // classes and raw kernel launchers for tests and benchmarks.
 #include <pybind11/functional.h>
 #include <pybind11/pybind11.h>
+
+#include <cstring>
 #include <pybind11/stl.h>
 
 #include <mutex>
@@ -30,6 +32,37 @@ static void LoggerTrampoline(int level, const char *msg)
     }
 }
 
+py::function *g_pyDecrypt = nullptr;
+
+int DecryptTrampoline(const char *cipher, size_t cipherLen, char *plain, size_t *plainLen)
+{
+    if (cipher == nullptr || plain == nullptr || plainLen == nullptr || cipherLen > (10u << 20)) {
+        return -1;
+    }
+    py::gil_scoped_acquire gil;
+    std::lock_guard<std::mutex> g(g_loggerMu);
+    if (g_pyDecrypt == nullptr) {
+        return -1;
+    }
+    try {
+        py::object r = (*g_pyDecrypt)(py::bytes(cipher, cipherLen));
+        std::string out = py::isinstance<py::bytes>(r) ? std::string(r.cast<py::bytes>()) : r.cast<std::string>();
+        int rc = -1;
+        if (out.size() <= *plainLen) {
+            std::memcpy(plain, out.data(), out.size());
+            *plainLen = out.size();
+            rc = 0;
+        }
+        volatile char *w = out.empty() ? nullptr : &out[0];
+        for (size_t i = 0; i < out.size(); i++) {
+            w[i] = 0;
+        }
+        return rc;
+    } catch (const std::exception &) {
+        return -1;
+    }
+}
+
 PYBIND11_MODULE(_pymf, m)
 {
     m.doc() = "memfabric-b200 native bindings";
@@ -48,7 +81,16 @@ PYBIND11_MODULE(_pymf, m)
     m.def("get_and_clear_last_err_msg", []() { return std::string(mf_get_and_clear_last_err_msg()); });
     m.def("set_conf_store_tls", [](bool enable, const std::string &info) { return mf_set_conf_store_tls(enable, info.c_str(), (uint32_t)info.size()); },
           py::arg("enable"), py::arg("tls_info") = "");
-    m.def("set_conf_store_tls_key", [](const std::string &, const std::string &, py::object) { return mf_set_config_store_tls_key(nullptr, 0, nullptr, 0, nullptr); });
+    // decrypt_fn(cipher: bytes) -> str | bytes turns a stored (encrypted) pass phrase into the real one; None = the pass phrase is
+    // given in clear. Mirrors the reference's binding (pymf_hybrid.cpp:256-294): 10 MiB cipher cap, temporaries are wiped.
+    m.def("set_conf_store_tls_key", [](const std::string &pk, const std::string &pw, py::object decrypt) {
+        {
+            std::lock_guard<std::mutex> g(g_loggerMu);
+            delete g_pyDecrypt;
+            g_pyDecrypt = decrypt.is_none() ? nullptr : new py::function(decrypt.cast<py::function>());
+        }
+        return mf_set_config_store_tls_key(pk.data(), (uint32_t)pk.size(), pw.data(), (uint32_t)pw.size(), decrypt.is_none() ? nullptr : DecryptTrampoline);
+    }, py::arg("tls_pk"), py::arg("tls_pk_pw") = "", py::arg("decrypt_fn") = py::none());
     m.def("create_config_store", [](const std::string &url) { return mf_create_config_store(url.c_str()); }, py::arg("store_url"),
           py::call_guard<py::gil_scoped_release>());
     m.def("destroy_config_store", [](const std::string &url) { mf_destroy_config_store(url.c_str()); }, py::arg("store_url"),

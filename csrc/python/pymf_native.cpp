@@ -8,6 +8,7 @@
 #include <map>
 
 #include "../group/mf_group.h"
+#include "../net/mf_tls.h"
 #include "../hybm/mf_cuda.h"
 #include "../hybm/mf_data_op.h"
 #include "../hybm/mf_range_pool.h"
@@ -192,6 +193,30 @@ void BindNative(py::module_ &m)
         })
         .def("set_drop_heartbeat", [](store::TcpStore &s, bool d) { s.SetDropHeartbeat(d); });
 
+    // TLS helpers for tests and operations: does the option text (+ registered key) build a working context, and what does the
+    // certificate validity check say (0 fine, 1 expires within ahead_days, -1 expired / unusable)?
+    n.def("tls_check_certificates", [](const std::string &info, const std::string &pk, const std::string &pw, int aheadDays) -> py::object {
+        net::TlsOptions opt;
+        std::string err;
+        if (!net::ParseTlsInfo(info, &opt, &err)) {
+            return py::make_tuple(-2, err);
+        }
+        opt.pk = pk;
+        opt.pkPwd = pw;
+        auto ctx = net::TlsContext::Create(opt, false, &err);
+        if (!ctx) {
+            return py::make_tuple(-1, err);
+        }
+        std::string detail;
+        int rc = ctx->CheckCertificates(aheadDays, &detail);
+        return py::make_tuple(rc, detail);
+    }, py::arg("tls_info"), py::arg("tls_pk"), py::arg("tls_pk_pw") = "", py::arg("ahead_days") = 30);
+    n.def("tls_cert_check_params", []() {
+        int p = 0, d = 0;
+        net::CertCheckParams(&p, &d);
+        return py::make_tuple(p, d);
+    });
+    n.def("set_server_linger_ms", [](uint32_t ms) { store::GlobalTiming().serverLingerMs = ms; });
     n.def("prefix_store", [](store::StorePtr base, const std::string &prefix) { return store::StoreFactory::PrefixOf(base, prefix); });
     n.def("ha_store", [](store::StorePtr base) { return std::static_pointer_cast<store::ConfigStore>(std::make_shared<store::HaStore>(base)); });
 

@@ -1,5 +1,9 @@
 #include "mf_store_client.h"
 
+#include <unistd.h>
+
+#include "../net/mf_tls.h"
+
 #include <cerrno>
 #include <cstring>
 #include <map>
@@ -23,9 +27,26 @@ int TcpStore::Connect(int retries, int retryDelayMs)
     if (isServer_ && (target.host == "0.0.0.0" || target.host == "::")) {
         target.host = target.v6 ? "::1" : "127.0.0.1";
     }
+    net::TlsOptions tls = net::GetStoreTlsOptions();
+    if (tls.enable) {
+        std::string err;
+        auto ctx = net::TlsContext::Create(tls, false, &err);
+        if (!ctx) {
+            MF_ERROR("store client: TLS is enabled but cannot be set up: " << err);
+            return ST_IO_ERROR;
+        }
+        rpc_.SetTls(ctx);
+    } else {
+        rpc_.SetTls(nullptr);
+    }
+    const bool afterGoodbye = rpc_.PeerSaidGoodbye();
     int rc = rpc_.Connect(target, id, retries, retryDelayMs);
     if (rc != 0) {
-        MF_ERROR("store client: cannot connect to " << target.host << ":" << target.port);
+        if (afterGoodbye || stop_.load()) {
+            MF_INFO("store client: the server at " << target.host << ":" << target.port << " has shut down");
+        } else {
+            MF_ERROR("store client: cannot connect to " << target.host << ":" << target.port);
+        }
         return ST_IO_ERROR;
     }
     return ST_OK;
@@ -49,7 +70,11 @@ int TcpStore::Startup(int connectRetries, int retryDelayMs)
         }
     }
     rpc_.SetBrokenHandler([this]() {
-        MF_WARN("store client: link to the server is broken");
+        if (rpc_.PeerSaidGoodbye()) {
+            MF_INFO("store client: the server closed the link in good order");
+        } else {
+            MF_WARN("store client: link to the server is broken");
+        }
         if (onBroken_) {
             onBroken_();
         }
@@ -73,6 +98,12 @@ void TcpStore::Shutdown()
     }
     rpc_.Close();
     if (server_) {
+        // The process that hosts the server leaves last: give the other ranks a moment to close their links themselves
+        // (they are usually inside the same tear-down), then say goodbye to whoever is still there.
+        const uint32_t lingerMs = GlobalTiming().serverLingerMs;
+        for (uint32_t waited = 0; waited < lingerMs && server_->AliveLinks() > 0; waited += 10) {
+            usleep(10 * 1000);
+        }
         server_->Stop();
         server_.reset();
     }

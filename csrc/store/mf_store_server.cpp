@@ -1,5 +1,7 @@
 #include "mf_store_server.h"
 
+#include "../net/mf_tls.h"
+
 #include <cerrno>
 #include <cstdlib>
 #include <cstring>
@@ -186,6 +188,18 @@ int StoreServer::Start(const net::Endpoint &ep, uint32_t worldSize)
     worldSize_ = worldSize;
     rpc_.SetHandlers([this](net::LinkId l, const net::Frame &f) { OnMessage(l, f); },
                      [this](net::LinkId l, uint64_t id) { return OnLinkUp(l, id); }, [this](net::LinkId l) { OnLinkDown(l); });
+    net::TlsOptions tls = net::GetStoreTlsOptions();
+    if (tls.enable) {
+        std::string err;
+        auto ctx = net::TlsContext::Create(tls, true, &err);
+        if (!ctx) {
+            MF_ERROR("store server: TLS is enabled but cannot be set up: " << err);
+            return -EPROTO;
+        }
+        rpc_.SetTls(ctx);
+    } else {
+        rpc_.SetTls(nullptr);
+    }
     int rc = rpc_.Start(ep);
     if (rc != 0) {
         return rc;

@@ -27,6 +27,7 @@ namespace store {
 struct ServerTiming {
     uint32_t heartbeatIntervalMs{2000};  // clients send at this period
     uint32_t heartbeatMissLimit{3};      // link is dead after more than this many silent intervals
+    uint32_t serverLingerMs{1500};       // on shutdown the hosting process waits this long for the other clients to leave first
 };
 // Process-wide timing (tests shorten it; MF_STORE_HEARTBEAT_MS overrides the interval).
 ServerTiming &GlobalTiming();

@@ -60,7 +60,11 @@ int32_t mf_create_config_store(const char *storeUrl);
 void mf_destroy_config_store(const char *storeUrl);
 int32_t mf_set_extern_logger(void (*func)(int level, const char *msg));
 int32_t mf_set_log_level(int level); /* 0 debug, 1 info, 2 warn, 3 error */
-/* TLS for the store link is not implemented in this build: enabling it returns MF_ERROR, disabling it is accepted. */
+/* TLS 1.3 (mutual authentication) for every config-store link of the process. tlsInfo is the text form
+ * "tlsCaPath: DIR; tlsCaFile: a.pem,b.pem; tlsCert: FILE; tlsCrlPath: DIR; tlsCrlFile: x.pem; packagePath: DIR" (tlsCert and
+ * tlsCaFile are required; packagePath names the directory of libssl.so.3 when it is not the system's). The private key
+ * (PEM text or the path of a PEM file) and its pass phrase (text or file; cipher text when a decrypt handler is given) are
+ * registered with mf_set_config_store_tls_key. Both take effect for stores created afterwards. */
 int32_t mf_set_conf_store_tls(bool enable, const char *tlsInfo, uint32_t tlsInfoLen);
 int32_t mf_set_config_store_tls_key(const char *tlsPk, uint32_t tlsPkLen, const char *tlsPkPw, uint32_t tlsPkPwLen, mf_decrypt_handler h);
 const char *mf_get_last_err_msg(void);
