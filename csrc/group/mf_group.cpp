@@ -66,6 +66,8 @@ std::shared_ptr<GroupEngine> GroupEngine::Create(store::StorePtr st, const Group
         return nullptr;
     }
     std::shared_ptr<GroupEngine> g(new GroupEngine(std::move(st), opt));
+    GroupEngine *raw = g.get();
+    g->reconnectListener_ = g->store_->AddReconnectListener([raw]() { raw->needRepair_.store(true); });
     if (!opt.dynamic) {
         g->size_.store(opt.rankSize);
         g->joined_.store(true);
@@ -83,6 +85,10 @@ void GroupEngine::Stop()
     if (stop_.exchange(true)) {
         return;
     }
+    if (reconnectListener_ != 0) {
+        store_->RemoveReconnectListener(reconnectListener_);
+        reconnectListener_ = 0;
+    }
     if (listener_.joinable()) {
         listener_.join();
     }
@@ -92,6 +98,49 @@ void GroupEngine::Stop()
     if (exitWid_ != 0) {
         store_->Unwatch(exitWid_);
     }
+}
+
+void GroupEngine::RepairAfterReconnect()
+{
+    if (!needRepair_.load()) {
+        return;
+    }
+    std::lock_guard<std::mutex> g(repairMu_);
+    if (!needRepair_.exchange(false)) {
+        return;
+    }
+    // Watches were tied to the old link.
+    if (opt_.dynamic && listener_.joinable()) {
+        rankDownWid_ = 0;
+        ArmWatches();
+    }
+    if (exitFn_) {
+        auto fn = exitFn_;
+        store_->Watch(kExitKey, [fn](int rc, const std::string &, const std::string &v) {
+            if (rc == ST_OK) {
+                fn((int)std::strtol(v.c_str(), nullptr, 10));
+            }
+        }, &exitWid_);
+    }
+    if (opt_.dynamic && joined_.load()) {
+        // A restarted server knows nothing: the first member that gets here restores the counter and the list, the others find
+        // them in place. A server that merely lost the link still has both and nothing is written.
+        const uint64_t want = PackVerSize(version_.load(), size_.load());
+        int64_t cur = 0;
+        if (store_->Add(kSizeKey, 0, &cur) == ST_OK && (uint64_t)cur < want) {
+            std::string prev;
+            store_->Cas(kSizeKey, std::to_string(cur), std::to_string(want), &prev);
+        }
+        std::string stored;
+        if (store_->Get(kMembersKey, &stored, 0) != ST_OK) {
+            std::lock_guard<std::mutex> gm(memberMu_);
+            std::string prev;
+            store_->Cas(kMembersKey, "", EncodeMembers(members_), &prev);
+        }
+    }
+    repairs_.fetch_add(1);
+    MF_INFO("group: state repaired after the store link came back (rank " << opt_.rank << ", version " << version_.load() << ", size " << size_.load()
+                                                                          << ")");
 }
 
 std::vector<uint32_t> GroupEngine::Members()
@@ -156,6 +205,7 @@ int GroupEngine::GroupBarrier()
     int ret = 0;
     MF_TRACE_SCOPE(MF_TP(TM_GROUP, 0), "GROUP_BARRIER", &ret);
     std::lock_guard<std::mutex> g(opMu_);
+    RepairAfterReconnect();
     uint32_t sn = 0;
     uint32_t ver = version_.load();
     std::string prefix = RoundPrefix(&sn);
@@ -226,6 +276,7 @@ int GroupEngine::GroupAllGather(const void *send, uint32_t sendSize, void *recv,
     int ret = 0;
     MF_TRACE_SCOPE(MF_TP(TM_GROUP, 1), "GROUP_ALLGATHER", &ret);
     std::lock_guard<std::mutex> g(opMu_);
+    RepairAfterReconnect();
     uint32_t sn = 0;
     uint32_t ver = version_.load();
     std::string prefix = RoundPrefix(&sn);
@@ -341,6 +392,9 @@ void GroupEngine::ListenLoop()
         }
         for (uint32_t r : down) {
             HandleRankDown(r);
+        }
+        if (store_->Connected()) {
+            RepairAfterReconnect();
         }
         if (!store_->Connected()) {
             usleep(100 * 1000);

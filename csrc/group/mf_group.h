@@ -94,6 +94,10 @@ private:
     void HandleRankDown(uint32_t rank);
     void ApplyMembership(uint32_t rank, bool join);
     void ArmWatches();
+    // After the link to the store came back (the server may have restarted empty): re-arm the rank-down and exit watches and
+    // put this group's shared state — the packed (version, size) counter and the member list — back where it is missing.
+    // Deferred: the reconnect notification only raises a flag, the next collective (or the listener thread) does the work.
+    void RepairAfterReconnect();
 
     store::StorePtr store_;
     GroupOption opt_;
@@ -114,6 +118,13 @@ private:
     std::unordered_map<std::string, uint32_t> subSn_;
     std::mutex downMu_;
     std::vector<uint32_t> pendingDown_;
+    std::atomic<bool> needRepair_{false};
+    std::mutex repairMu_;
+    uint32_t reconnectListener_{0};
+    std::atomic<uint32_t> repairs_{0};
+
+public:
+    uint32_t Repairs() const { return repairs_.load(); }
 };
 
 }  // namespace group

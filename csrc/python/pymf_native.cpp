@@ -253,6 +253,7 @@ void BindNative(py::module_ &m)
              }),
              py::arg("store"), py::arg("rank_size"), py::arg("rank"), py::arg("timeout_ms") = 120000, py::arg("dynamic") = false,
              py::arg("join_cb") = py::none(), py::arg("leave_cb") = py::none())
+        .def("repairs", &group::GroupEngine::Repairs)
         .def("barrier", &group::GroupEngine::GroupBarrier, py::call_guard<py::gil_scoped_release>())
         .def("allgather", [](group::GroupEngine &g, py::bytes send) {
             std::string s(send);

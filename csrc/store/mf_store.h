@@ -85,6 +85,11 @@ public:
     virtual void SetBrokenHandler(std::function<void()>) {}
     virtual void SetReconnectHandler(std::function<void()>) {}
     virtual int ReconnectAfterBroken(int /*retries*/) { return ST_OK; }
+    // Any number of additional subscribers to "the link to the server is up again" (the group engines on one store each
+    // repair their own state). Returns an id for RemoveReconnectListener; 0 if the store has no notion of a link. The
+    // callback runs on whichever thread noticed the reconnect and must not call back into the store.
+    virtual uint32_t AddReconnectListener(std::function<void()>) { return 0; }
+    virtual void RemoveReconnectListener(uint32_t) {}
 };
 using StorePtr = std::shared_ptr<ConfigStore>;
 
@@ -116,6 +121,8 @@ public:
     void SetBrokenHandler(std::function<void()> f) override { base_->SetBrokenHandler(std::move(f)); }
     void SetReconnectHandler(std::function<void()> f) override { base_->SetReconnectHandler(std::move(f)); }
     int ReconnectAfterBroken(int r) override { return base_->ReconnectAfterBroken(r); }
+    uint32_t AddReconnectListener(std::function<void()> f) override { return base_->AddReconnectListener(std::move(f)); }
+    void RemoveReconnectListener(uint32_t id) override { base_->RemoveReconnectListener(id); }
     StorePtr Base() const { return base_; }
 
 private:

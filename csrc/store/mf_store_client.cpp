@@ -135,10 +135,41 @@ int TcpStore::ReconnectAfterBroken(int retries)
         return ST_OK;
     }
     int rc = Connect(retries, 1000);
-    if (rc == ST_OK && onReconnect_) {
-        onReconnect_();
+    if (rc == ST_OK) {
+        NotifyReconnected();
     }
     return rc;
+}
+
+void TcpStore::NotifyReconnected()
+{
+    if (onReconnect_) {
+        onReconnect_();
+    }
+    std::vector<std::function<void()>> fns;
+    {
+        std::lock_guard<std::mutex> g(listenerMu_);
+        for (auto &kv : reconnectListeners_) {
+            fns.push_back(kv.second);
+        }
+    }
+    for (auto &f : fns) {
+        f();
+    }
+}
+
+uint32_t TcpStore::AddReconnectListener(std::function<void()> f)
+{
+    std::lock_guard<std::mutex> g(listenerMu_);
+    uint32_t id = nextListener_++;
+    reconnectListeners_[id] = std::move(f);
+    return id;
+}
+
+void TcpStore::RemoveReconnectListener(uint32_t id)
+{
+    std::lock_guard<std::mutex> g(listenerMu_);
+    reconnectListeners_.erase(id);
 }
 
 int TcpStore::Request(uint16_t op, const StoreMessage &m, int64_t waitMs, net::Frame *reply)
@@ -153,9 +184,7 @@ int TcpStore::Request(uint16_t op, const StoreMessage &m, int64_t waitMs, net::F
             again = rpc_.Connected() || Connect(2, 200) == ST_OK;
         }
         if (again) {
-            if (onReconnect_) {
-                onReconnect_();
-            }
+            NotifyReconnected();
             rc = rpc_.Call(op, body, reply, waitMs);
         }
     }

@@ -45,6 +45,8 @@ public:
     void SetBrokenHandler(std::function<void()> f) override { onBroken_ = std::move(f); }
     void SetReconnectHandler(std::function<void()> f) override { onReconnect_ = std::move(f); }
     int ReconnectAfterBroken(int retries) override;
+    uint32_t AddReconnectListener(std::function<void()> f) override;
+    void RemoveReconnectListener(uint32_t id) override;
     // Test hook: stop sending heartbeats (the server will declare this link dead).
     void SetDropHeartbeat(bool drop) { dropHeartbeat_.store(drop); }
 
@@ -67,6 +69,10 @@ private:
     std::mutex reconnectMu_;
     std::function<void()> onBroken_;
     std::function<void()> onReconnect_;
+    void NotifyReconnected();
+    std::mutex listenerMu_;
+    std::map<uint32_t, std::function<void()>> reconnectListeners_;
+    uint32_t nextListener_{1};
     std::mutex watchMu_;
     std::unordered_map<uint32_t, uint32_t> watchSeq_;  // watch id → rpc seq
     uint32_t nextWid_{1};
@@ -90,6 +96,11 @@ public:
     int WatchRankDown(WatchRankCb cb, uint32_t *wid) override { return Current()->WatchRankDown(std::move(cb), wid); }
     int Unwatch(uint32_t wid) override { return Current()->Unwatch(wid); }
     bool Connected() const override { return const_cast<HaStore *>(this)->Current()->Connected(); }
+    void SetBrokenHandler(std::function<void()> f) override { Current()->SetBrokenHandler(std::move(f)); }
+    void SetReconnectHandler(std::function<void()> f) override { Current()->SetReconnectHandler(std::move(f)); }
+    int ReconnectAfterBroken(int r) override { return Current()->ReconnectAfterBroken(r); }
+    uint32_t AddReconnectListener(std::function<void()> f) override { return Current()->AddReconnectListener(std::move(f)); }
+    void RemoveReconnectListener(uint32_t id) override { Current()->RemoveReconnectListener(id); }
 
 private:
     std::mutex mu_;

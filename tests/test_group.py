@@ -211,3 +211,52 @@ def test_processes_over_one_store():
     res = sorted(q.get(timeout=120) for _ in ps)
     [p.join(30) for p in ps]
     assert res == [(r, "ok") for r in range(world)], res
+
+
+def test_group_survives_a_store_restart(mf, port):
+    """The store server is restarted (and comes back empty) under a joined dynamic group: the clients reconnect, every member
+    re-arms its watches and the first one back restores the shared (version, size) counter and the member list; barriers,
+    all-gathers and a later join work as before. The reference repairs the same state in its reconnect handler
+    (src/smem/csrc/net/smem_net_group_engine.cpp:1045-1083)."""
+    n = mf.native
+    n.set_server_linger_ms(0)
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    W = 3
+    clients = [n.TcpStore("127.0.0.1", port, False, W, r) for r in range(W)]
+    for c in clients:
+        assert c.startup(5, 100) == 0
+    engines = [n.GroupEngine(clients[r], W, r, 5000, True, lambda rank: 0, lambda rank: 0) for r in range(W)]
+    for e in engines:
+        e.start_listen()
+    assert engines[0].join() == 0 and engines[1].join() == 0
+    time.sleep(0.2)
+    assert _run([engines[0].barrier, engines[1].barrier]) == [0, 0]
+    before = clients[0].add("DSIZE", 0)[1]
+    assert before >> 30 == 2 and before & ((1 << 30) - 1) == 2
+    srv.stop()
+    time.sleep(0.3)
+    srv2 = n.StoreServer()
+    assert srv2.start("127.0.0.1", port) == 0
+    for c in clients:
+        assert c.reconnect(10) == 0
+    # the next collective on each member repairs first, then runs
+    assert _run([engines[0].barrier, engines[1].barrier]) == [0, 0]
+    assert engines[0].repairs() >= 1 and engines[1].repairs() >= 1
+    after = clients[2].add("DSIZE", 0)[1]
+    assert after == before, (hex(before), hex(after))
+    assert clients[2].get("MEMBERS", 0) == (0, b"0,1,")
+    res = _run([lambda r=r: engines[r].allgather(bytes([65 + r])) for r in range(2)])
+    assert [x[0] for x in res] == [0, 0] and res[0][1] == b"AB"
+    # membership still works on the repaired state: the third rank joins and everybody sees it
+    assert engines[2].join() == 0
+    time.sleep(0.3)
+    for e in engines:
+        assert e.members() == [0, 1, 2]
+    assert _run([e.barrier for e in engines]) == [0, 0, 0]
+    for e in engines:
+        e.stop()
+    for c in clients:
+        c.shutdown()
+    srv2.stop()
+    n.set_server_linger_ms(1500)
