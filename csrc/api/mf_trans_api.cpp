@@ -24,6 +24,7 @@
 #include "../hybm/mf_cuda.h"
 #include "../store/mf_store_client.h"
 #include "../util/mf_log.h"
+#include "../util/mf_retry.h"
 #include "../util/mf_tracer.h"
 #include "mf/mf_trans.h"
 #include "mf_api_internal.h"
@@ -89,7 +90,20 @@ public:
             return rc;
         }
         base_->SetBrokenHandler([this]() { OnBroken(); });
+        // A peer whose link to the store breaks (it died, or it left without a word): what is cached about it is stale from that
+        // moment on, the next transfer re-reads its records instead of writing into memory of a process that is gone.
+        base_->WatchRankDown([this](uint32_t rank) { MarkStale(rank); }, &rankDownWid_);
         return MF_OK;
+    }
+
+    void MarkStale(uint32_t rank)
+    {
+        std::unique_lock<std::shared_mutex> lk(remoteMu_);
+        for (auto &kv : remotes_) {
+            if (kv.second.rank == rank) {
+                kv.second.stale = true;
+            }
+        }
     }
 
     void Shutdown()
@@ -97,6 +111,10 @@ public:
         stop_.store(true);
         if (reconnect_.joinable()) {
             reconnect_.join();
+        }
+        if (base_ && rankDownWid_ != 0) {
+            base_->Unwatch(rankDownWid_);
+            rankDownWid_ = 0;
         }
         if (store_ && base_ && base_->Connected()) {
             // Tell the peers we are gone before the link drops.
@@ -143,7 +161,23 @@ public:
             }
             return nullptr;
         }
-        void *p = ::mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd, 0);
+        // Blocks come out of one fixed window of the address space, bump-allocated (reference: the 128 GiB VA reservation of
+        // smem_trans_entry.cpp:179-243), so that a restarted process gets the same addresses again and its peers' bookkeeping of
+        // "where the decode side keeps its buffers" stays valid. If the slot is taken the kernel picks the address.
+        static std::atomic<uint64_t> bump{0};
+        constexpr uint64_t kWindowBase = 0x500000000000ull, kWindowSize = 128ull << 30;
+        void *p = MAP_FAILED;
+        const uint64_t off = bump.fetch_add(size);
+        if (off + size <= kWindowSize) {
+            p = ::mmap((void *)(kWindowBase + off), size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE | MAP_FIXED_NOREPLACE, fd, 0);
+            if (p != MAP_FAILED && (uint64_t)p != kWindowBase + off) {  // kernels before 4.17 treat the flag as a hint
+                ::munmap(p, size);
+                p = MAP_FAILED;
+            }
+        }
+        if (p == MAP_FAILED) {
+            p = ::mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd, 0);
+        }
         if (p == MAP_FAILED) {
             MF_ERROR("trans malloc: mmap failed: " << strerror(errno));
             ::close(fd);
@@ -237,8 +271,33 @@ public:
         return MF_OK;
     }
 
+    // A transfer that fails because the peer is gone, restarting or not mappable right now is tried again after 1 s and after
+    // 2 more seconds; before each new attempt everything known about the peer is dropped, so that the attempt re-reads the
+    // peer's records from the store and maps its memory afresh (a restarted peer has new descriptors and maybe new
+    // addresses). Errors in the arguments themselves are returned at once.
     int Transfer(bool write, const void *const *locals, const char *remoteId, const void *const *remotes, const size_t *sizes, uint32_t n,
                  void *stream, bool async, uint32_t flags)
+    {
+        int ret = MF_OK;
+        RetryWithBackoff(
+            [&]() {
+                ret = TransferOnce(write, locals, remoteId, remotes, sizes, n, stream, async, flags);
+                return ret == MF_OK || ret == MF_INVALID_PARAM || ret == MF_NOT_INITIALIZED || stop_.load();
+            },
+            [&](uint32_t failed) {
+                MF_WARN("trans transfer to " << remoteId << " failed (" << ret << "), attempt " << failed + 1 << " after re-reading the peer's records");
+                std::unique_lock<std::shared_mutex> lk(remoteMu_);
+                auto it = remotes_.find(remoteId);
+                if (it != remotes_.end()) {
+                    DropRemote(it->second);
+                    it->second.rank = hybm::RANK_MAX;
+                }
+            });
+        return ret;
+    }
+
+    int TransferOnce(bool write, const void *const *locals, const char *remoteId, const void *const *remotes, const size_t *sizes, uint32_t n,
+                     void *stream, bool async, uint32_t flags)
     {
         int ret = MF_OK;
         MF_TRACE_SCOPE(MF_TP(TM_TRANS, write ? 0 : 1), write ? "TRANS_BATCH_WRITE" : "TRANS_BATCH_READ", &ret);
@@ -305,6 +364,7 @@ private:
         std::map<uint64_t, RemoteRange> ranges;  // peer address → mapping
         std::map<uint32_t, uint64_t> recordAddr;  // record offset → peer address (to honour later status changes)
         uint32_t rank{hybm::RANK_MAX};
+        bool stale{false};  // the peer's link to the store broke after these mappings were made
     };
 
     std::shared_ptr<hybm::MemSegment> UserSegment() { return entity_ ? entity_->Segment(hybm::MEM_TYPE_DEVICE) : nullptr; }
@@ -342,7 +402,7 @@ private:
         {
             std::shared_lock<std::shared_mutex> lk(remoteMu_);
             auto it = remotes_.find(remoteId);
-            if (it != remotes_.end() && Lookup(it->second, addr, size, mapped, memType)) {
+            if (it != remotes_.end() && !it->second.stale && Lookup(it->second, addr, size, mapped, memType)) {
                 return MF_OK;
             }
         }
@@ -369,6 +429,11 @@ private:
         std::memcpy(&d, dev.data(), sizeof(d));
         std::unique_lock<std::shared_mutex> lk(remoteMu_);
         Remote &r = remotes_[remoteId];
+        if (r.stale) {
+            DropRemote(r);  // the process these mappings belonged to is gone; whoever holds the id now is mapped from scratch
+            r.rank = hybm::RANK_MAX;
+            r.stale = false;
+        }
         if (d.status != kNormal) {
             DropRemote(r);
             MF_ERROR("trans: peer " << remoteId << " has left or died");
@@ -378,6 +443,15 @@ private:
             DropRemote(r);  // the id was taken over by a new process
         }
         r.rank = d.rank;
+        // Transfers run between a sender and a receiver (or with an engine that is both): a sender never maps another sender's
+        // memory, a receiver never another receiver's.
+        const hybm::Role peerRole = d.role == MF_TRANS_SENDER ? hybm::ROLE_SENDER : (d.role == MF_TRANS_RECEIVER ? hybm::ROLE_RECEIVER : hybm::ROLE_PEER);
+        entity_->SetPeerRole(d.rank, peerRole);
+        if (!entity_->RolePermits(d.rank)) {
+            MF_ERROR("trans: " << remoteId << " has the same role (" << (d.role == MF_TRANS_SENDER ? "sender" : "receiver")
+                               << ") as this engine; transfers need a sender on one side and a receiver on the other");
+            return MF_INVALID_PARAM;
+        }
         std::string all;
         rc = store_->Get("slices/" + remoteId, &all, 0);
         if (rc == store::ST_NOT_EXIST) {
@@ -467,6 +541,7 @@ private:
         MF_INFO("trans: records of " << id_ << " republished after a store reconnect");
     }
 
+    uint32_t rankDownWid_{0};
     std::string url_, id_;
     mf_trans_config_t cfg_;
     store::StorePtr base_, store_;

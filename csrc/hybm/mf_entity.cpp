@@ -339,6 +339,22 @@ int MemEntity::Export(uint64_t sliceHandle, uint32_t flags, ExchangeInfo *out)
     return BM_OK;
 }
 
+void MemEntity::SetPeerRole(uint32_t rank, Role role)
+{
+    std::lock_guard<std::mutex> g(roleMu_);
+    peerRoles_[rank] = role;
+}
+
+bool MemEntity::RolePermits(uint32_t rank)
+{
+    if (opt_.role == ROLE_PEER) {
+        return true;
+    }
+    std::lock_guard<std::mutex> g(roleMu_);
+    auto it = peerRoles_.find(rank);
+    return it == peerRoles_.end() || it->second == ROLE_PEER || it->second != opt_.role;
+}
+
 int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresses, uint32_t /*flags*/)
 {
     MF_CHECK_RET(infos != nullptr && count > 0, BM_INVALID_PARAM, "entity: nothing to import");
@@ -356,6 +372,7 @@ int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresse
             if (rc != BM_OK) {
                 return rc;
             }
+            SetPeerRole(e.rank, (Role)e.role);
             if (addresses != nullptr) {
                 addresses[i] = nullptr;
             }
@@ -364,6 +381,13 @@ int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresse
         MF_CHECK_RET(magic == SLICE_EXPORT_MAGIC && x.descLen == sizeof(SliceExport), BM_INVALID_PARAM, "entity: unknown exchange info #" << i);
         SliceExport e;
         std::memcpy(&e, x.desc, sizeof(e));
+        if (!RolePermits(e.rank)) {
+            MF_INFO("entity: rank " << e.rank << " has the same one-sided role as this rank; its memory is not mapped");
+            if (addresses != nullptr) {
+                addresses[i] = nullptr;
+            }
+            continue;
+        }
         std::shared_ptr<MemSegment> seg;
         if (e.segType == SEG_DEVICE_VMM) {
             seg = hbm_;

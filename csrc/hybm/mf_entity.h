@@ -42,6 +42,11 @@ public:
     int Mmap();
     int Unmap();
     int RemoveImported(uint32_t rank);
+    // Role of a peer (learned from its entity export, or told by the layer above). A SENDER maps the memory of RECEIVERs and of
+    // PEERs only, a RECEIVER that of SENDERs and PEERs: slices of a rank with the same one-sided role are recorded nowhere and
+    // never mapped (reference: the sender/receiver-only connections of transport/device/bipartite_ranks_qp_manager.cpp).
+    void SetPeerRole(uint32_t rank, Role role);
+    bool RolePermits(uint32_t rank);
     int SetExtraContext(const void *ctx, uint32_t size);
     // Bit mask of DataOpType usable towards `rank`.
     uint32_t ReachTypes(uint32_t rank);
@@ -84,6 +89,8 @@ private:
     // Copies hold this shared; unmapping a peer takes it exclusively, so a range is never pulled from under a copy.
     std::shared_mutex mapMu_;
     bool reserved_{false};
+    std::mutex roleMu_;
+    std::map<uint32_t, Role> peerRoles_;
 };
 
 class EntityFactory {

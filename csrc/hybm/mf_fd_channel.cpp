@@ -11,6 +11,7 @@
 #include <unistd.h>
 
 #include "../util/mf_log.h"
+#include "../util/mf_retry.h"
 
 namespace mf {
 namespace hybm {
@@ -192,6 +193,18 @@ int FdChannel::Fetch(const std::string &name, uint64_t token, int timeoutMs)
         }
         usleep(2000);
     }
+}
+
+int FdChannel::FetchWithRetry(const std::string &name, uint64_t token, int timeoutMsPerAttempt)
+{
+    int fd = -1;
+    RetryWithBackoff(
+        [&]() {
+            fd = Fetch(name, token, timeoutMsPerAttempt);
+            return fd >= 0;
+        },
+        [&](uint32_t failed) { MF_WARN("fd channel: fetching token " << token << " from " << name << " failed, attempt " << failed + 1); });
+    return fd;
 }
 
 void FdChannel::Shutdown()

@@ -26,6 +26,9 @@ public:
     void Unpublish(uint64_t token);
     // Fetches a duplicate of the descriptor registered under `token` in the process serving `name`. -1 on failure.
     static int Fetch(const std::string &name, uint64_t token, int timeoutMs = 10000);
+    // Fetch under the process-wide retry policy (three attempts, 1 s and 2 s apart by default): a peer that is restarting its
+    // descriptor server gets the time to come back. -1 when every attempt failed.
+    static int FetchWithRetry(const std::string &name, uint64_t token, int timeoutMsPerAttempt = 3000);
     void Shutdown();
     // After fork(): forget the parent's server thread and descriptors.
     void ResetAfterFork();

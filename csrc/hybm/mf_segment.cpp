@@ -278,7 +278,7 @@ public:
                 continue;
             }
             const SliceExport &e = imp.info;
-            int fd = FdChannel::Fetch(e.fdName, e.fdToken);
+            int fd = FdChannel::FetchWithRetry(e.fdName, e.fdToken);
             MF_CHECK_RET(fd >= 0, BM_ERROR, "device segment: cannot fetch the handle of rank " << e.rank);
             CUmemGenericAllocationHandle h = 0;
             CUresult r = d->MemImportFromShareableHandle(&h, (void *)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
@@ -544,7 +544,7 @@ public:
                 continue;
             }
             const SliceExport &e = imp.info;
-            int fd = FdChannel::Fetch(e.fdName, e.fdToken);
+            int fd = FdChannel::FetchWithRetry(e.fdName, e.fdToken);
             MF_CHECK_RET(fd >= 0, BM_ERROR, "host segment: cannot fetch the backing file of rank " << e.rank);
             void *p = ::mmap((void *)e.gva, e.size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, (off_t)e.fileOffset);
             int err = errno;
@@ -923,7 +923,7 @@ private:
             const cu::DriverApi *d = cu::Driver();
             MF_CHECK_RET(d != nullptr, BM_NOT_SUPPORTED, "user segment: no CUDA driver");
             cudaSetDevice(opt_.devId);
-            int fd = FdChannel::Fetch(e.fdName, e.fdToken);
+            int fd = FdChannel::FetchWithRetry(e.fdName, e.fdToken);
             MF_CHECK_RET(fd >= 0, BM_ERROR, "user segment: cannot fetch the handle of rank " << e.rank);
             CUmemGenericAllocationHandle h = 0;
             CUresult r = d->MemImportFromShareableHandle(&h, (void *)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
@@ -958,7 +958,7 @@ private:
                 }
             }
             if (o.mappedBase == 0) {
-                int fd = FdChannel::Fetch(e.fdName, e.fdToken);
+                int fd = FdChannel::FetchWithRetry(e.fdName, e.fdToken);
                 MF_CHECK_RET(fd >= 0, BM_ERROR, "user segment: cannot fetch the host block of rank " << e.rank);
                 void *p = ::mmap(nullptr, e.windowSize, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
                 int err = errno;

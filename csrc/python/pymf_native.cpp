@@ -14,6 +14,7 @@
 #include "../hybm/mf_range_pool.h"
 #include "../hybm/mf_tag_info.h"
 #include "../util/mf_log.h"
+#include "../util/mf_retry.h"
 #include "../util/mf_tracer.h"
 #include "../hybm/mf_va_manager.h"
 #include "../kernels/mf_kernels.h"
@@ -216,6 +217,13 @@ void BindNative(py::module_ &m)
         net::CertCheckParams(&p, &d);
         return py::make_tuple(p, d);
     });
+    n.def("set_retry_policy", [](uint32_t attempts, uint32_t firstDelayMs, uint32_t factor) {
+        RetryPolicy &p = GlobalRetryPolicy();
+        p.attempts = attempts == 0 ? 1 : attempts;
+        p.firstDelayMs = firstDelayMs;
+        p.factor = factor == 0 ? 1 : factor;
+    }, py::arg("attempts") = 3, py::arg("first_delay_ms") = 1000, py::arg("factor") = 2);
+    n.def("retry_stats", []() { return py::make_tuple(GlobalRetryStats().retries.load(), GlobalRetryStats().gaveUp.load()); });
     n.def("set_server_linger_ms", [](uint32_t ms) { store::GlobalTiming().serverLingerMs = ms; });
     n.def("prefix_store", [](store::StorePtr base, const std::string &prefix) { return store::StoreFactory::PrefixOf(base, prefix); });
     n.def("ha_store", [](store::StorePtr base) { return std::static_pointer_cast<store::ConfigStore>(std::make_shared<store::HaStore>(base)); });
