@@ -345,7 +345,7 @@ def run_extras(pool, rank, local_rank, world, stream):
     from memfabric_hybrid_b200.parallel.heap import SymmetricHeap
 
     shard_bytes = ReshardPlan(param_specs(LLAMA3_8B), world, 0, min(4, world)).shard_elems * 2
-    heap_bytes = 2 * (256 << 20) + workloads.moe_heap_bytes(4096, world, 32 * world, 7168, 8, 2.0) + shard_bytes + (64 << 20)
+    heap_bytes = 3 * (256 << 20) + workloads.moe_heap_bytes(4096, world, 32 * world, 7168, 8, 2.0) + shard_bytes + (64 << 20)
     heap = None
     try:
         heap = SymmetricHeap(rank, world, local_rank, heap_bytes, nvls=world > 1)

@@ -77,7 +77,8 @@ def allreduce_sizes(heap, sizes: List[int], hidden: int = 8192, iters: int = 20,
         T = max(1, nbytes // (H * 2))
         x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
         res = torch.randn(T, H, generator=gc, device="cuda").to(torch.bfloat16)
-        ar.x[:T].copy_(x)
+        for buf in ar._xs:  # the same addend in both input buffers: timed calls alternate between them
+            buf[:T].copy_(x)
         torch.cuda.synchronize()
         barrier()
         row = {"bytes": T * H * 2, "T": T, "H": H}

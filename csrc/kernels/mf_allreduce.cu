@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "mf/device/mf_shm_device.cuh"
 #include "mf_kernels.h"
 
@@ -164,7 +166,7 @@ __device__ __forceinline__ void Fail(const mf_allreduce_args_t &a, int code)
 
 // ------------------------------------------------------------------------------------------------ one-shot
 
-template <int VPT>
+template <int VPT, bool TAIL>
 __global__ void __launch_bounds__(kThreads, 1)
 mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epoch,
                                     uint64_t timeoutNs)
@@ -202,10 +204,13 @@ mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args
         }
         NormAndStore<VPT>(acc, vecsPerRow, (const char *)a.weight, (char *)a.out + rowOff, H, eps);
     }
-    // Nobody may overwrite its x before every rank has finished reading it.
-    rc = mf_barrier_cta(m, channel, blockIdx.x, 2 * epoch, timeoutNs);
-    if (rc != MF_DEV_OK) {
-        Fail(a, rc);
+    // Nobody may overwrite its x before every rank has finished reading it. Callers that alternate between two x buffers get
+    // that guarantee from the opening barrier of their next call and skip this round trip.
+    if (TAIL) {
+        rc = mf_barrier_cta(m, channel, blockIdx.x, 2 * epoch, timeoutNs);
+        if (rc != MF_DEV_OK) {
+            Fail(a, rc);
+        }
     }
 }
 
@@ -356,7 +361,10 @@ template <int VPT>
 const void *PickKernel(int algo, int rankCount)
 {
     if (algo == MF_AR_ONESHOT) {
-        return (const void *)mf_allreduce_rmsnorm_oneshot_kernel<VPT>;
+        return (const void *)mf_allreduce_rmsnorm_oneshot_kernel<VPT, true>;
+    }
+    if (algo == MF_AR_ONESHOT_NOTAIL) {
+        return (const void *)mf_allreduce_rmsnorm_oneshot_kernel<VPT, false>;
     }
     if (algo == MF_AR_NVLS) {
         return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<true, VPT, 0>;
@@ -373,7 +381,7 @@ const void *PickKernel(int algo, int rankCount)
     return (const void *)mf_allreduce_rmsnorm_twoshot_kernel<false, VPT, 0>;
 }
 
-int CoopCapacity(const void *kernel)
+int CoopCapacityQuery(const void *kernel)
 {
     int perSm = 0, dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
@@ -382,6 +390,41 @@ int CoopCapacity(const void *kernel)
         return 0;
     }
     return perSm * sms;
+}
+
+// Resident-CTA capacity of a kernel on the current device. The occupancy query costs microseconds, which is real money on a
+// 10 us call path: the answer is remembered per (device, kernel).
+int CoopCapacity(const void *kernel)
+{
+    struct Entry {
+        const void *kernel;
+        int dev;
+        int capacity;
+    };
+    static Entry cache[64];
+    static int used = 0;
+    static std::mutex mu;
+    int curDev = 0;
+    if (cudaGetDevice(&curDev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    {
+        std::lock_guard<std::mutex> g(mu);
+        for (int i = 0; i < used; i++) {
+            if (cache[i].kernel == kernel && cache[i].dev == curDev) {
+                return cache[i].capacity;
+            }
+        }
+    }
+    int cap = CoopCapacityQuery(kernel);
+    if (cap > 0) {
+        std::lock_guard<std::mutex> g(mu);
+        if (used < 64) {
+            cache[used++] = Entry{kernel, curDev, cap};
+        }
+    }
+    return cap;
 }
 
 }  // namespace
@@ -412,7 +455,8 @@ extern "C" int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nE
     }
     int perRank = capacity / nEmulatedRanks;
     int grid;
-    if (algo == MF_AR_ONESHOT) {
+    const bool oneshot = algo == MF_AR_ONESHOT || algo == MF_AR_ONESHOT_NOTAIL;
+    if (oneshot) {
         grid = T < (int)MF_SIGNAL_SLOTS ? T : (int)MF_SIGNAL_SLOTS;  // one signal slot per CTA
     } else {
         int rowsMine = (T + rankCount - 1) / rankCount;
@@ -429,8 +473,11 @@ extern "C" int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nE
         return MF_K_TOO_LARGE;
     }
     dim3 g((unsigned)grid, (unsigned)nEmulatedRanks, 1), b(kThreads, 1, 1);
-    // Cooperative launch: all CTAs (and, when emulating, all ranks) are co-resident, so the waits inside can complete.
-    cudaError_t e = cudaLaunchCooperativeKernel(kernel, g, b, kargs, 0, (cudaStream_t)stream);
+    // Cooperative launch: all CTAs (and, when emulating, all ranks) are co-resident, so the waits inside can complete. The
+    // one-shot kernel of a real rank needs neither a grid barrier nor co-residency on this GPU (each of its at most 64 CTAs only
+    // waits for the CTA of the same index on the OTHER GPUs) and takes the cheaper ordinary launch.
+    cudaError_t e = (oneshot && nEmulatedRanks == 1) ? cudaLaunchKernel(kernel, g, b, kargs, 0, (cudaStream_t)stream)
+                                                     : cudaLaunchCooperativeKernel(kernel, g, b, kargs, 0, (cudaStream_t)stream);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         return MF_K_LAUNCH_FAILED;

@@ -58,7 +58,10 @@ typedef struct {
     void *reserved;
 } mf_allreduce_args_t;
 
-enum { MF_AR_AUTO = 0, MF_AR_ONESHOT = 1, MF_AR_TWOSHOT = 2, MF_AR_NVLS = 3 };
+// MF_AR_ONESHOT_NOTAIL: one-shot without the closing cross-rank barrier. Only legal when the caller alternates between two x
+// buffers from call to call: a rank then rewrites a buffer two calls later at the earliest, and by then every peer has passed
+// the opening barrier of the call in between, i.e. has finished reading it.
+enum { MF_AR_AUTO = 0, MF_AR_ONESHOT = 1, MF_AR_TWOSHOT = 2, MF_AR_NVLS = 3, MF_AR_ONESHOT_NOTAIL = 4 };
 
 // argsDev: device array of nEmulatedRanks blocks (1 in production; R when a test runs all ranks of a fake heap on one GPU
 // as slices of one cooperative launch). rankCount must equal meta->rankCount. epoch: strictly increasing per (heap,

@@ -26,6 +26,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "mf/device/mf_shm_device.cuh"
 #include "mf_kernels.h"
 
@@ -422,15 +424,46 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
     }
 }
 
+// Resident-CTA capacity of a kernel on the current device for a given dynamic shared-memory size; remembered per (device,
+// kernel, size) because the occupancy query costs microseconds on a latency-critical call path.
 int CoopCap(const void *kernel, size_t smem)
 {
-    int perSm = 0, dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+    struct Entry {
+        const void *kernel;
+        size_t smem;
+        int dev;
+        int capacity;
+    };
+    static Entry cache[32];
+    static int used = 0;
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    {
+        std::lock_guard<std::mutex> g(mu);
+        for (int i = 0; i < used; i++) {
+            if (cache[i].kernel == kernel && cache[i].smem == smem && cache[i].dev == dev) {
+                return cache[i].capacity;
+            }
+        }
+    }
+    int perSm = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, kThreads, smem) != cudaSuccess) {
         (void)cudaGetLastError();
         return 0;
     }
-    return perSm * sms;
+    const int cap = perSm * sms;
+    if (cap > 0) {
+        std::lock_guard<std::mutex> g(mu);
+        if (used < 32) {
+            cache[used++] = Entry{kernel, smem, dev, cap};
+        }
+    }
+    return cap;
 }
 
 }  // namespace

@@ -17,6 +17,7 @@ void BindOps(py::module_ &m)
     ops.attr("AR_ONESHOT") = (int)MF_AR_ONESHOT;
     ops.attr("AR_TWOSHOT") = (int)MF_AR_TWOSHOT;
     ops.attr("AR_NVLS") = (int)MF_AR_NVLS;
+    ops.attr("AR_ONESHOT_NOTAIL") = (int)MF_AR_ONESHOT_NOTAIL;
     ops.attr("ALLREDUCE_ARGS_BYTES") = (int)sizeof(mf_allreduce_args_t);
 
     // Packs one argument block (to be copied to device memory by the caller).

@@ -4,6 +4,11 @@
     ar.x[:T].copy_(partial)                      # or have the producing GEMM write straight into ar.x
     out, new_residual = ar(T, residual, weight)  # every rank calls with the same T
 
+`ar.x` is the input buffer of the NEXT call: by default there are two, used alternately (`double_buffer=True`), which lets the
+small-input (one-shot) algorithm drop its closing cross-rank barrier — a rank rewrites a buffer two calls later at the earliest,
+when every peer has long passed the opening barrier of the call in between. Fetch `ar.x` anew before every call. With
+`double_buffer=False` there is one buffer (half the heap space) and the one-shot algorithm keeps its closing barrier.
+
 `out = RMSNorm(residual + sum_r x_r) * weight`, `new_residual = residual + sum_r x_r`, both bf16 [T, hidden]. The kernel
 (csrc/kernels/mf_allreduce.cu) picks one-shot / two-shot / NVLS by size unless `algo` is given.
 """
@@ -15,7 +20,9 @@ from .. import _loader  # noqa: F401
 from .._loader import _pymf
 
 _ops = _pymf.ops
-ALGOS = {"auto": _ops.AR_AUTO, "oneshot": _ops.AR_ONESHOT, "twoshot": _ops.AR_TWOSHOT, "nvls": _ops.AR_NVLS}
+ALGOS = {"auto": _ops.AR_AUTO, "oneshot": _ops.AR_ONESHOT, "twoshot": _ops.AR_TWOSHOT, "nvls": _ops.AR_NVLS,
+         "oneshot_notail": _ops.AR_ONESHOT_NOTAIL}
+ONESHOT_MAX_BYTES = 512 << 10
 
 
 def reference(xs, residual, weight, eps: float):
@@ -31,7 +38,7 @@ def reference(xs, residual, weight, eps: float):
 
 
 class AllReduceRMSNorm:
-    def __init__(self, heap, max_tokens: int, hidden: int, eps: float = 1e-6, channel: int = 0, timeout_ns: int = 0):
+    def __init__(self, heap, max_tokens: int, hidden: int, eps: float = 1e-6, channel: int = 0, timeout_ns: int = 0, double_buffer: bool = True):
         import torch
 
         if hidden % 8 != 0 or hidden > 16384:
@@ -39,26 +46,36 @@ class AllReduceRMSNorm:
         self.heap, self.max_tokens, self.hidden, self.eps = heap, max_tokens, hidden, eps
         self.channel, self.timeout_ns = channel, timeout_ns
         nbytes = max_tokens * hidden * 2
-        self.x_off = heap.alloc(nbytes)
+        self.double_buffer = double_buffer
+        self._x_offs = [heap.alloc(nbytes) for _ in range(2 if double_buffer else 1)]
         self.res_off = heap.alloc(nbytes)
-        self.x = heap.tensor(self.x_off, (max_tokens, hidden), torch.bfloat16)
+        self._xs = [heap.tensor(off, (max_tokens, hidden), torch.bfloat16) for off in self._x_offs]
+        self._cur = 0
+        self.x_off = self._x_offs[0]
         self.residual_out = heap.tensor(self.res_off, (max_tokens, hidden), torch.bfloat16)
-        self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=self.x.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.x.device)
-        self._args = torch.empty(_ops.ALLREDUCE_ARGS_BYTES, dtype=torch.uint8, device=self.x.device)
-        self._args_key = None
+        dev = self._xs[0].device
+        self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._args = [torch.empty(_ops.ALLREDUCE_ARGS_BYTES, dtype=torch.uint8, device=dev) for _ in range(2)]
+        self._args_key = [None, None]
         self.launches = 0
+
+    @property
+    def x(self):
+        """Input buffer of the next call (bf16 [max_tokens, hidden])."""
+        return self._xs[self._cur]
 
     def _pack(self, residual, weight):
         import torch
 
+        c = self._cur
         key = (residual.data_ptr() if residual is not None else 0, weight.data_ptr())
-        if key != self._args_key:
-            blob = _ops.pack_allreduce_args(self.heap.meta_ptr, self.x.data_ptr(), key[0], key[1], self.residual_out.data_ptr(),
+        if key != self._args_key[c]:
+            blob = _ops.pack_allreduce_args(self.heap.meta_ptr, self._xs[c].data_ptr(), key[0], key[1], self.residual_out.data_ptr(),
                                             self.out.data_ptr(), self.status.data_ptr())
-            self._args.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8), non_blocking=False)
-            self._args_key = key
-        return self._args.data_ptr()
+            self._args[c].copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8), non_blocking=False)
+            self._args_key[c] = key
+        return self._args[c].data_ptr()
 
     def __call__(self, tokens: int, residual, weight, algo: str = "auto", ctas: int = 0, stream=None):
         import torch
@@ -66,8 +83,18 @@ class AllReduceRMSNorm:
         if tokens > self.max_tokens:
             raise ValueError("tokens exceeds max_tokens")
         a = ALGOS[algo]
-        if a == _ops.AR_AUTO and self.heap.multicast_ptr and tokens * self.hidden * 2 > (512 << 10):
-            a = _ops.AR_NVLS
+        nbytes = tokens * self.hidden * 2
+        if a == _ops.AR_AUTO:
+            if nbytes <= ONESHOT_MAX_BYTES:
+                a = _ops.AR_ONESHOT_NOTAIL if self.double_buffer else _ops.AR_ONESHOT
+            elif self.heap.multicast_ptr and self.heap.world > 2:
+                a = _ops.AR_NVLS  # in-switch reduction pays from three ranks on (measured: with two, plain peer loads are faster)
+            else:
+                a = _ops.AR_TWOSHOT
+        elif a == _ops.AR_ONESHOT and self.double_buffer:
+            a = _ops.AR_ONESHOT_NOTAIL  # inputs alternate between two buffers (see the module docstring): the closing barrier is not needed
+        elif a == _ops.AR_ONESHOT_NOTAIL and not self.double_buffer:
+            raise ValueError("oneshot_notail needs double_buffer=True")
         if a == _ops.AR_NVLS and not self.heap.multicast_ptr:
             raise RuntimeError("the NVLS algorithm needs a heap created with nvls=True on a platform with multicast")
         args = self._pack(residual, weight)
@@ -77,6 +104,8 @@ class AllReduceRMSNorm:
         if rc != 0:
             raise RuntimeError(f"allreduce_rmsnorm launch failed ({rc})")
         self.launches += 1
+        if self.double_buffer:
+            self._cur = 1 - self._cur
         return self.out[:tokens], self.residual_out[:tokens]
 
     def check_status(self) -> int:

@@ -47,6 +47,31 @@ def test_emulated_ranks_match_oracle(algo, world, T, H):
         assert torch.equal(outs[r], outs[0]), "ranks must agree bit for bit"
 
 
+def test_emulated_oneshot_without_closing_barrier_on_alternating_buffers():
+    """The one-shot variant that skips its closing barrier, driven the way it must be: inputs alternate between two buffers."""
+    import torch
+
+    from memfabric_hybrid_b200.ops.allreduce import emulated_allreduce, reference
+
+    from memfabric_hybrid_b200.parallel.heap import EmulatedHeap
+
+    world, T, H = 4, 6, 4096
+    heap = EmulatedHeap(world, 3 * T * H * 2 + 8192)
+    x_offs = [heap.alloc(T * H * 2), heap.alloc(T * H * 2)]
+    r_off = heap.alloc(T * H * 2)
+    for it in range(5):
+        xs, res, w = _make_inputs(world, T, H, 77 + it)
+        off = x_offs[it % 2]
+        for r in range(world):
+            heap.tensor(r, off, (T, H), torch.bfloat16).copy_(xs[r])
+        outs, status = emulated_allreduce(heap, off, r_off, [res] * world, w, T, H, 1e-6, "oneshot_notail")
+        assert status == [0] * world
+        ref_out, ref_h = reference(xs, res, w, 1e-6)
+        for r in range(world):
+            assert torch.equal(heap.tensor(r, r_off, (T, H), torch.bfloat16).float(), ref_h)
+            torch.testing.assert_close(outs[r].float(), ref_out, atol=2e-2, rtol=2e-2)
+
+
 def test_emulated_second_call_reuses_signal_words():
     """Epochs only grow: repeated calls on one heap need no flag reset."""
     import torch
@@ -98,7 +123,7 @@ def _real_rank(rank, world, port, q):
         heap = SymmetricHeap(rank, world, rank, 64 << 20, store_url=f"tcp://127.0.0.1:{port}")
         T, H = 300, 8192
         ar = AllReduceRMSNorm(heap, T, H)
-        for algo, t in (("oneshot", 7), ("twoshot", 300), ("auto", 64)):
+        for algo, t in (("oneshot", 7), ("oneshot", 9), ("auto", 5), ("twoshot", 300), ("auto", 64), ("auto", 3)):
             xs, res, w = _make_inputs(world, t, H, 4242 + t)  # same seed everywhere: every rank can build the oracle
             ar.x[:t].copy_(xs[rank])
             torch.cuda.synchronize()
