@@ -65,7 +65,15 @@ asan: $(CUDA_OBJS)
 	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -o $(BUILD)/asan/mf_native_tests_asan \
 	    $(TEST_SRCS) $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
 
+# Example programs and tools that are built against the installed headers and library.
+EXAMPLES := examples/bm_perf/bm_perf examples/bm_cpp/bm_example
+examples: $(EXAMPLES)
+examples/bm_perf/bm_perf: examples/bm_perf/bm_perf.cpp $(CORE)
+	$(CXX) -std=c++17 -O2 -Iinclude -I$(CUDA_HOME)/include -o $@ $< -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' -L$(CUDA_HOME)/lib64 -lcudart -pthread
+examples/bm_cpp/bm_example: examples/bm_cpp/main.cpp $(CORE)
+	$(CXX) -std=c++17 -O2 -Iinclude -o $@ $< -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' -pthread
+
 clean:
 	rm -rf $(BUILD) $(CORE) $(PYMOD) $(TESTBIN)
 
-.PHONY: all clean asan
+.PHONY: all clean asan examples

@@ -8,6 +8,7 @@
 // New here: (1) the ranks agree on the heap address by all-gathering proposals (CUDA treats a requested VA as a hint);
 // (2) a second tiny symmetric segment holds signal words for device-side barriers; (3) the heap is optionally aliased
 // by an NVLS multicast mapping for multimem reductions.
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <map>
@@ -169,6 +170,7 @@ public:
     uint32_t RankId() const { return rankId_; }
     uint64_t Multicast() const { return mcVa_; }
     uint64_t NextEpoch(uint32_t ch) { return ch < MF_SHM_CHANNELS ? ++epochs_[ch] : 0; }
+    int SetDebugFlags(uint64_t flags) { return data_ ? MapHybmCode(data_->SetDebugFlags(flags)) : MF_NOT_INITIALIZED; }
     std::function<void(int)> exitFn;
 
 private:
@@ -297,8 +299,14 @@ private:
     {
         SetupMulticast();  // optional: failure only means multimem kernels are not offered
         uint64_t sig = signal_->MemoryPtr(hybm::MEM_TYPE_DEVICE);
-        return MapHybmCode(data_->SetMetaExtras(sig, mcVa_));
+        int rc = MapHybmCode(data_->SetMetaExtras(sig, mcVa_));
+        const char *chk = std::getenv("MF_CHECK_BOUNDS");
+        if (rc == MF_OK && chk != nullptr && chk[0] == '1') {
+            rc = MapHybmCode(data_->SetDebugFlags(1));
+        }
+        return rc;
     }
+
 
     // NVLS: one multicast object spanning the heap; every rank binds its own slice at offset 0, so a multimem access at
     // mc + off touches heap offset `off` of every rank.
@@ -709,6 +717,12 @@ extern "C" void *mf_shm_get_multicast_ptr(mf_shm_t handle)
 {
     ShmEntry *e = EntryOf(handle);
     return e == nullptr ? nullptr : (void *)e->Multicast();
+}
+
+extern "C" int32_t mf_shm_set_debug_flags(mf_shm_t handle, uint64_t flags)
+{
+    ShmEntry *e = EntryOf(handle);
+    return e == nullptr ? MF_INVALID_PARAM : e->SetDebugFlags(flags);
 }
 
 extern "C" uint64_t mf_shm_next_epoch(mf_shm_t handle, uint32_t channel)

@@ -1,4 +1,8 @@
 #include "mf_data_op.h"
+#include "mf_range_pool.h"
+
+#include <deque>
+#include <memory>
 
 #include <algorithm>
 #include <cstdlib>
@@ -58,20 +62,31 @@ int BoundedStreamSync(int device, void *stream, uint32_t timeoutMs)
 
 namespace {
 
-struct StageSlot {
-    mf_copy_desc_t *host{nullptr};
-    mf_copy_desc_t *dev{nullptr};
+// Staging space for copy tables that do not fit the kernel parameters: one pinned host block and one device block of the same
+// size per thread, carved up by a range pool (the reference's RbtreeRangePool serves its staging buffers the same way,
+// src/hybm/csrc/common/hybm_rbtree_range_pool.{h,cpp}). A table's range is handed back when the kernel that reads it has
+// finished, which an event recorded AFTER the launch tells. Nothing is allocated on the request path once the arena exists;
+// a table larger than the arena makes it grow, once.
+struct StageArena {
+    char *host{nullptr};
+    char *dev{nullptr};
     size_t cap{0};
-    cudaEvent_t ev{nullptr};
-    bool used{false};
+    std::unique_ptr<RangePool> pool;
+    struct InFlight {
+        uint64_t off;
+        cudaEvent_t ev;
+    };
+    std::deque<InFlight> inflight;
+    std::vector<cudaEvent_t> freeEvents;
 };
+constexpr size_t kArenaBase = 256;  // offsets handed out by the pool start here: 0 means "no room"
+constexpr size_t kArenaDefault = 2u << 20;
 
 struct ThreadCtx {
     volatile uint32_t *flag{nullptr};  // pinned host word, device-visible under the same address
     uint32_t *counter{nullptr};        // device word, self-resetting
     uint32_t seq{0};
-    StageSlot slots[4];
-    int nextSlot{0};
+    StageArena arena;
     std::vector<mf_copy_desc_t> scratch;
 };
 
@@ -164,46 +179,34 @@ public:
         const bool sync = !(opt.flags & FLAG_ASYNC_COPY);
         const bool useFlag = sync && flagSync_ && opt.stream == nullptr;
         const mf_copy_desc_t *devTable = nullptr;
+        uint64_t stagedOff = 0;
         if (d.size() > MF_BATCH_INLINE_MAX) {
             // 2. Large tables: stage in pinned memory and copy to the device ahead of the kernel, on the same stream.
-            StageSlot &slot = ctx->slots[ctx->nextSlot];
-            ctx->nextSlot = (ctx->nextSlot + 1) % 4;
-            if (slot.used) {
-                cudaEventSynchronize(slot.ev);  // the previous H2D from this slot must have been consumed
-            }
             // Table layout: descriptors, then one uint32 per chunk naming its descriptor.
             const size_t descBytes = d.size() * sizeof(mf_copy_desc_t);
             const size_t bytes = descBytes + (size_t)chunks * sizeof(uint32_t);
-            if (slot.cap < bytes) {
-                if (slot.host != nullptr) {
-                    cudaStreamSynchronize(s);
-                    cudaFreeHost(slot.host);
-                    cudaFree(slot.dev);
-                }
-                size_t cap = std::max<size_t>(bytes * 2, 256 * 1024);
-                MF_CUDA_CHECK_RET(cudaHostAlloc((void **)&slot.host, cap, cudaHostAllocDefault), BM_MALLOC_FAILED);
-                MF_CUDA_CHECK_RET(cudaMalloc((void **)&slot.dev, cap), BM_MALLOC_FAILED);
-                slot.cap = cap;
-                if (slot.ev == nullptr) {
-                    MF_CUDA_CHECK_RET(cudaEventCreateWithFlags(&slot.ev, cudaEventDisableTiming), BM_ERROR);
-                }
+            int arc = StageAlloc(ctx->arena, bytes, s, &stagedOff);
+            if (arc != BM_OK) {
+                return arc;
             }
-            std::memcpy(slot.host, d.data(), descBytes);
-            uint32_t *map = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(slot.host) + descBytes);
+            char *host = ctx->arena.host + stagedOff;
+            std::memcpy(host, d.data(), descBytes);
+            uint32_t *map = reinterpret_cast<uint32_t *>(host + descBytes);
             for (uint32_t i = 0; i < d.size(); i++) {
                 const uint32_t n = (d[i].len + MF_BATCH_CHUNK_BYTES - 1) / MF_BATCH_CHUNK_BYTES;
                 for (uint32_t c = 0; c < n; c++) {
                     map[d[i].chunkStart + c] = i;
                 }
             }
-            MF_CUDA_CHECK_RET(cudaMemcpyAsync(slot.dev, slot.host, bytes, cudaMemcpyHostToDevice, s), BM_ERROR);
-            cudaEventRecord(slot.ev, s);
-            slot.used = true;
-            devTable = slot.dev;
+            MF_CUDA_CHECK_RET(cudaMemcpyAsync(ctx->arena.dev + stagedOff, host, bytes, cudaMemcpyHostToDevice, s), BM_ERROR);
+            devTable = reinterpret_cast<const mf_copy_desc_t *>(ctx->arena.dev + stagedOff);
         }
         uint32_t seq = ++ctx->seq;
         int rc = mf_k_batch_xcopy(d.data(), devTable, (uint32_t)d.size(), chunks, useFlag ? ctx->counter : nullptr,
                                   useFlag ? ctx->flag : nullptr, seq, 0, (mf_stream_t)s);
+        if (stagedOff != 0) {
+            StageRetire(ctx->arena, stagedOff, s);  // the range is free again once this kernel has run
+        }
         if (rc != MF_K_OK) {
             MF_ERROR("kernel engine: batch launch failed");
             return BM_ERROR;
@@ -229,6 +232,74 @@ public:
     int Wait() override { return BoundedStreamSync(device_, nullptr, DefaultSyncTimeoutMs()); }
 
 private:
+    // Hands back the ranges whose kernels have finished; with `block` it waits for the oldest one.
+    static void StageReclaim(StageArena &a, bool block)
+    {
+        while (!a.inflight.empty()) {
+            StageArena::InFlight &f = a.inflight.front();
+            cudaError_t q = block ? cudaEventSynchronize(f.ev) : cudaEventQuery(f.ev);
+            if (q != cudaSuccess) {
+                (void)cudaGetLastError();
+                return;
+            }
+            a.pool->Release(f.off);
+            a.freeEvents.push_back(f.ev);
+            a.inflight.pop_front();
+            block = false;
+        }
+    }
+
+    int StageAlloc(StageArena &a, size_t bytes, cudaStream_t s, uint64_t *off)
+    {
+        if (a.pool) {
+            StageReclaim(a, false);
+        }
+        if (!a.pool || bytes + kArenaBase > a.cap) {
+            // First use, or a table larger than the whole arena: (re)build it. Tables in flight still read the old blocks.
+            if (a.pool) {
+                cudaStreamSynchronize(s);
+                while (!a.inflight.empty()) {
+                    StageReclaim(a, true);
+                }
+                cudaFreeHost(a.host);
+                cudaFree(a.dev);
+                a.host = a.dev = nullptr;
+            }
+            size_t cap = kArenaDefault;
+            while (cap < 2 * bytes + kArenaBase) {
+                cap *= 2;
+            }
+            MF_CUDA_CHECK_RET(cudaHostAlloc((void **)&a.host, cap, cudaHostAllocDefault), BM_MALLOC_FAILED);
+            MF_CUDA_CHECK_RET(cudaMalloc((void **)&a.dev, cap), BM_MALLOC_FAILED);
+            a.cap = cap;
+            a.pool.reset(new RangePool(kArenaBase, cap - kArenaBase, 256));
+        }
+        uint64_t o = a.pool->Allocate(bytes);
+        while (o == 0 && !a.inflight.empty()) {
+            StageReclaim(a, true);  // full: wait for the oldest table to be consumed
+            o = a.pool->Allocate(bytes);
+        }
+        MF_CHECK_RET(o != 0, BM_MALLOC_FAILED, "kernel engine: no staging space for a table of " << bytes << " bytes");
+        *off = o;
+        return BM_OK;
+    }
+
+    static void StageRetire(StageArena &a, uint64_t off, cudaStream_t s)
+    {
+        cudaEvent_t ev = nullptr;
+        if (!a.freeEvents.empty()) {
+            ev = a.freeEvents.back();
+            a.freeEvents.pop_back();
+        } else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cudaStreamSynchronize(s);  // no event to be had: wait right here and free the range
+            a.pool->Release(off);
+            return;
+        }
+        cudaEventRecord(ev, s);
+        a.inflight.push_back(StageArena::InFlight{off, ev});
+    }
+
     ThreadCtx *Ctx()
     {
         thread_local std::unordered_map<const KernelDataOp *, ThreadCtx> ctxs;

@@ -68,6 +68,12 @@ public:
         hostMeta_.multicastBase = multicastBase;
         return UpdateDeviceMeta();
     }
+    // MF_DEBUG_* bits for device code (bit 0: kernels validate their heap arguments).
+    int SetDebugFlags(uint64_t flags)
+    {
+        hostMeta_.debugFlags = flags;
+        return UpdateDeviceMeta();
+    }
     std::shared_ptr<MemSegment> Segment(uint32_t memType) const;
     std::shared_ptr<ComposeDataOp> DataOp() const { return dataOp_; }
 

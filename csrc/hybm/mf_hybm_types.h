@@ -156,7 +156,8 @@ struct alignas(128) DeviceMeta {
     uint64_t signalBase;       // GVA offset-independent address of this entity's signal area on rank 0 (0 if none)
     uint64_t extraContextAddr; // device address of the ≤64 KiB user context
     uint64_t multicastBase;    // NVLS multicast mapping of the HBM window (0 if unavailable)
-    uint64_t reserved[7];
+    uint64_t debugFlags;       // bit 0: kernels validate their heap arguments against this record before touching peers
+    uint64_t reserved[6];
 };
 static_assert(sizeof(DeviceMeta) == 128, "device meta record is 128 bytes");
 

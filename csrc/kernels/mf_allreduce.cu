@@ -174,6 +174,10 @@ mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args
     const mf_allreduce_args_t a = args[blockIdx.y];
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     const int vecsPerRow = H / 8;
+    if (mf_check_bounds_enabled(m) && !mf_shm_in_own_window(m, a.x, (uint64_t)T * H * 2)) {
+        Fail(a, MF_DEV_ERR_BOUNDS);  // peers would read my x at this offset of their own heaps: it must be heap memory
+        return;
+    }
     // Peers' x is complete once their CTA of the same index has arrived here.
     int rc = mf_barrier_cta(m, channel, blockIdx.x, 2 * epoch - 1, timeoutNs);
     if (rc != MF_DEV_OK) {
@@ -228,6 +232,10 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
     const uint32_t R = m->rankCount, me = m->rankId;
     const int vecsPerRow = H / 8;
     __shared__ int abortFlag;
+    if (mf_check_bounds_enabled(m) && !(mf_shm_in_own_window(m, a.x, (uint64_t)T * H * 2) && mf_shm_in_own_window(m, a.residualOut, (uint64_t)T * H * 2))) {
+        Fail(a, MF_DEV_ERR_BOUNDS);  // every CTA of every rank decides alike from the same arguments: nobody waits for anybody
+        return;
+    }
 
     // Phase 0: every rank's x is ready. One CTA per rank shakes hands, the grid barrier spreads the news.
     if (blockIdx.x == 0) {

@@ -81,6 +81,13 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     unsigned char *stage = smem + (size_t)3 * kMaxExperts * sizeof(int);        // per warp: H bytes fp8 + nblk floats
     const size_t stagePerWarp = (size_t)H + (size_t)nblk * 4;
     __shared__ int abortFlag;
+    if (mf_check_bounds_enabled(m) &&
+        !(mf_shm_in_own_window(m, a.cnt, (uint64_t)R * E * 4) && mf_shm_in_own_window(m, a.recvX, (uint64_t)a.cap * H) &&
+          mf_shm_in_own_window(m, a.recvSf, (uint64_t)a.cap * nblk * 4) && mf_shm_in_own_window(m, a.recvMeta, (uint64_t)a.cap * 16) &&
+          mf_shm_in_own_window(m, a.recvSib, (uint64_t)a.cap * MF_MOE_MAX_SIBLINGS * 8))) {
+        FailD(a.status, MF_DEV_ERR_BOUNDS);  // the receive buffers are addressed by offset on every owner: they must be heap memory
+        return;
+    }
 
     // ---- (a) histogram of my pairs per global expert
     const int pairs = a.T * K;
@@ -293,6 +300,10 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
     __shared__ int offs[kMaxExperts + 1];
     __shared__ int cnts[kMaxExperts];
     __shared__ int abortFlag;
+    if (mf_check_bounds_enabled(m) && !mf_shm_in_own_window(m, a.retY, (uint64_t)a.retRows * H * 2)) {
+        FailD(a.status, MF_DEV_ERR_BOUNDS);
+        return;
+    }
     for (int i = threadIdx.x; i <= EL; i += kThreads) {
         offs[i] = a.expertOffset[i];
         if (i < EL) {

@@ -36,6 +36,12 @@ mf_reshard_kernel(const mf_reshard_args_t *__restrict__ args, uint32_t channel, 
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     __shared__ float warpMax[2][kThreads / 32];  // per quantisation block of the tile, per warp
     __shared__ int abortFlag;
+    if (mf_check_bounds_enabled(m) && !mf_shm_in_own_window(m, a.srcShard, a.shardElems * 2)) {
+        if (threadIdx.x == 0 && a.status != nullptr) {
+            atomicCAS(a.status, 0, MF_DEV_ERR_BOUNDS);
+        }
+        return;
+    }
 
     if (blockIdx.x == 0) {
         int rc = mf_barrier_cta(m, channel, 0, 2 * epoch - 1, timeoutNs);

@@ -102,6 +102,7 @@ void BindShm(py::module_ &m)
         .def_property_readonly("multicast_ptr", [](ShareMemory &s) { return (uint64_t)mf_shm_get_multicast_ptr(s.h); })
         .def("local_ptr", [](ShareMemory &s) { return s.gva + (uint64_t)mf_shm_get_global_rank(s.h) * s.symmetricSize; })
         .def("peer_ptr", [](ShareMemory &s, uint32_t rank) { return s.gva + (uint64_t)rank * s.symmetricSize; })
+        .def("set_debug_flags", [](ShareMemory &s, uint64_t flags) { return mf_shm_set_debug_flags(s.h, flags); }, py::arg("flags"))
         .def("next_epoch", [](ShareMemory &s, uint32_t channel) { return mf_shm_next_epoch(s.h, channel); }, py::arg("channel") = 0)
         .def("destroy", [](ShareMemory &s) { s.Destroy(); }, py::call_guard<py::gil_scoped_release>())
         .def("query_support_data_operation", [](ShareMemory &) { return mf_shm_query_support_data_operation(); })

@@ -26,8 +26,16 @@ struct alignas(128) MfDeviceMeta {
     uint64_t signalBase;
     uint64_t extraContextAddr;
     uint64_t multicastBase;
-    uint64_t reserved[7];
+    uint64_t debugFlags; /* MF_DEBUG_* bits, set with mf_shm_set_debug_flags() or MF_CHECK_BOUNDS=1 */
+    uint64_t reserved[6];
 };
+
+/* Debug aid for a platform without a device memory checker: with MF_DEBUG_CHECK_BOUNDS set in the heap's meta record, every
+ * library kernel first checks that each argument which peers will address at the same heap offset (inputs they read, landing
+ * zones they write) lies, with its full extent, inside THIS rank's window of the heap. A kernel whose arguments fail the check
+ * touches no peer memory at all: it records MF_DEV_ERR_BOUNDS in its status word and returns. The check costs one branch per
+ * kernel, so it may stay on in production runs that hunt a stray pointer. */
+#define MF_DEBUG_CHECK_BOUNDS 1ull
 
 /* Signal area of one rank (2 MiB): flags[channel][slot][rank] as 64-bit epochs, then scratch for library kernels. */
 #define MF_SIGNAL_BYTES (2u * 1024u * 1024u)
@@ -61,6 +69,14 @@ __device__ __forceinline__ bool mf_shm_in_heap(const MfDeviceMeta *m, const void
     uint64_t a = (uint64_t)p;
     return a >= m->hbmBase && a + n <= m->hbmBase + (uint64_t)m->rankCount * m->symmetricSize;
 }
+
+/* True if [p, p+n) lies inside the heap window of the calling rank (what peers address by offset must). */
+__device__ __forceinline__ bool mf_shm_in_own_window(const MfDeviceMeta *m, const void *p, uint64_t n)
+{
+    const uint64_t a = (uint64_t)p, lo = m->hbmBase + (uint64_t)m->rankId * m->symmetricSize;
+    return a >= lo && n <= m->symmetricSize && a + n <= lo + m->symmetricSize;
+}
+__device__ __forceinline__ bool mf_check_bounds_enabled(const MfDeviceMeta *m) { return (m->debugFlags & MF_DEBUG_CHECK_BOUNDS) != 0; }
 
 __device__ __forceinline__ uint64_t *mf_signal_ptr(const MfDeviceMeta *m, uint32_t onRank, uint32_t channel, uint32_t slot, uint32_t fromRank)
 {

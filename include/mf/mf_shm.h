@@ -63,6 +63,10 @@ void *mf_shm_get_signal_base(mf_shm_t handle);
 void *mf_shm_get_multicast_ptr(mf_shm_t handle);
 /* Next epoch value for device-side collectives on `channel` (0..MF_SHM_CHANNELS-1). All ranks must call in the same order. */
 uint64_t mf_shm_next_epoch(mf_shm_t handle, uint32_t channel);
+/* Debug switches read by device code (include/mf/device/mf_shm_device.cuh): bit 0 (MF_DEBUG_CHECK_BOUNDS) makes every library
+ * kernel validate its heap arguments before it touches a peer and report MF_DEV_ERR_BOUNDS instead of accessing memory outside
+ * the heap. Also switched on for every heap of the process by the environment variable MF_CHECK_BOUNDS=1. */
+int32_t mf_shm_set_debug_flags(mf_shm_t handle, uint64_t flags);
 #define MF_SHM_CHANNELS 16U
 
 #ifdef __cplusplus

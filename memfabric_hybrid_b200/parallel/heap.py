@@ -89,6 +89,12 @@ class SymmetricHeap:
     def next_epoch(self, channel: int = 0) -> int:
         return self.handle.next_epoch(channel)
 
+    def set_check_bounds(self, on: bool = True) -> None:
+        """Kernels validate their heap arguments before touching a peer (debug aid; also MF_CHECK_BOUNDS=1 in the environment)."""
+        rc = self.handle.set_debug_flags(1 if on else 0)
+        if rc != 0:
+            raise RuntimeError(f"set_debug_flags failed ({rc}): {get_last_err_msg()}")
+
     def barrier(self) -> None:
         rc = self.handle.barrier()
         if rc != 0:
@@ -117,7 +123,9 @@ class _EmulatedRank:
 class EmulatedHeap:
     """R ranks' heaps, signal areas and meta records inside one GPU (tests and single-GPU development only)."""
 
-    def __init__(self, world: int, size_bytes: int, device: int = 0):
+    def __init__(self, world: int, size_bytes: int, device: int = 0, check_bounds: bool = False):
+        """check_bounds sets the debug bit in every emulated rank's meta record: kernels then validate their heap arguments
+        before they touch a peer and report an error code instead of reaching outside the heap."""
         import torch
 
         self.world = world
@@ -127,7 +135,8 @@ class EmulatedHeap:
         self.gva = self._heap.data_ptr()
         metas = b""
         for r in range(world):
-            metas += struct.pack("<4I7Q7Q", 0, r, world, 0, self.size, self.gva, 0, 0, self._signal.data_ptr(), 0, 0, *([0] * 7))
+            metas += struct.pack("<4I7Q7Q", 0, r, world, 0, self.size, self.gva, 0, 0, self._signal.data_ptr(), 0, 0, 1 if check_bounds else 0,
+                                 *([0] * 6))
         assert len(metas) == world * META_BYTES
         self._meta = torch.frombuffer(bytearray(metas), dtype=torch.uint8).to(f"cuda:{device}")
         self.meta_base = self._meta.data_ptr()
