@@ -66,10 +66,12 @@ asan: $(CUDA_OBJS)
 	    $(TEST_SRCS) $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
 
 # Example programs and tools that are built against the installed headers and library.
-EXAMPLES := examples/bm_perf/bm_perf examples/bm_cpp/bm_example
+EXAMPLES := examples/bm_perf/bm_perf examples/bm_cpp/bm_example benchmarks/store_bench
 examples: $(EXAMPLES)
 examples/bm_perf/bm_perf: examples/bm_perf/bm_perf.cpp $(CORE)
 	$(CXX) -std=c++17 -O2 -Iinclude -I$(CUDA_HOME)/include -o $@ $< -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' -L$(CUDA_HOME)/lib64 -lcudart -pthread
+benchmarks/store_bench: benchmarks/store_bench.cpp $(CORE)
+	$(CXX) -std=c++17 -O2 -Icsrc -Iinclude -o $@ $< -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../$(OUTDIR)' -pthread
 examples/bm_cpp/bm_example: examples/bm_cpp/main.cpp $(CORE)
 	$(CXX) -std=c++17 -O2 -Iinclude -o $@ $< -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' -pthread
 

@@ -10,8 +10,8 @@ from its own pooled HBM to the next rank's pooled HBM through the public Big Mem
 copy type G2G). With one GPU the destination is the second half of the same rank's window (a local HBM copy). The value
 is the whole-job aggregate in GB/s (1 GB = 1e9 B), timed with CUDA events, max over ranks.
 
-`--impl reference` would run the unmodified reference; it only builds against Ascend CANN, so that arm reports
-`unavailable`. `--impl baseline` runs the same step with stock CUDA/NCCL calls (cudaMemcpyAsync on one GPU, NCCL
+`--impl reference` would run the unmodified reference; its data plane only builds against Ascend CANN, so that arm reports
+`unavailable` (plus, when baseline/build_ref.sh has been run, the reference's own config-store / group-barrier timings). `--impl baseline` runs the same step with stock CUDA/NCCL calls (cudaMemcpyAsync on one GPU, NCCL
 send/recv ring on several) as the measured thing-to-beat on this hardware.
 """
 from __future__ import annotations
@@ -55,8 +55,37 @@ def reference_arm(args):
             first = f.readline().strip()
         if first:
             reason = first
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    line = {"impl": "reference", "unavailable": reason}
+    # What of the reference does build here is its C++ control plane (baseline/build_ref.sh); its barrier and store round
+    # trips are timed with the same loop as ours (benchmarks/store_bench.cpp) so the two can be put side by side.
+    ref = control_plane(os.path.join(ROOT, "baseline", "_ref", "cpp", "ref_store_bench"), max(args.gpus, 2))
+    if ref is not None:
+        line["control_plane"] = ref
+    print(json.dumps(line))
     return 0
+
+
+def control_plane(binary: str, ranks: int):
+    """Runs a store micro-benchmark binary (ranks forked on this host) and returns its JSON line, or None."""
+    import socket
+    import subprocess
+
+    if not os.path.exists(binary):
+        return None
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    try:
+        out = subprocess.run([binary, str(ranks), str(port), "200"], capture_output=True, text=True, timeout=120)
+        for ln in reversed(out.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                rec = json.loads(ln)
+                return None if "error" in rec else rec
+    except (OSError, subprocess.SubprocessError, ValueError):
+        pass
+    return None
 
 
 def max_over_ranks(value: float, world: int) -> float:
@@ -360,6 +389,10 @@ def run_extras(pool, rank, local_rank, world, stream):
         heap.close()
     except Exception as e:  # noqa: BLE001
         extra["heap_close_error"] = repr(e)[:200]
+    if rank == 0:
+        cp = control_plane(os.path.join(ROOT, "benchmarks", "store_bench"), max(world, 2))
+        if cp is not None:
+            extra["control_plane"] = cp
     return extra
 
 

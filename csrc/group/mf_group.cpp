@@ -164,35 +164,26 @@ std::string GroupEngine::RoundPrefix(uint32_t *snOut)
     return std::to_string(version_.load()) + "_" + std::to_string(sn);
 }
 
-void GroupEngine::GcRound(uint32_t ver, uint32_t sn)
+// Keys of round sn-2, which every member has left once round sn completes: the request that completes round sn drops them
+// on the server, so garbage collection costs no round trip of its own.
+std::vector<std::string> GroupEngine::GcKeys(uint32_t ver, uint32_t sn)
 {
-    if (sn < 2) {
-        return;
-    }
-    std::string old = std::to_string(ver) + "_" + std::to_string(sn - 2);
-    for (const char *suffix : {"_BA", "_BW", "_GA", "_GW"}) {
-        store_->Remove(old + suffix, true);
-    }
-}
-
-int GroupEngine::BarrierOn(const std::string &prefix, uint32_t size)
-{
-    int64_t val = 0;
-    int rc = store_->Add(prefix + "_BA", 1, &val);
-    if (rc != ST_OK) {
-        MF_ERROR("group barrier: add failed rc=" << rc);
-        return MapStoreCode(rc);
-    }
-    if ((uint32_t)val == size) {
-        rc = store_->Set(prefix + "_BW", "ok");
-        if (rc != ST_OK) {
-            return MapStoreCode(rc);
+    std::vector<std::string> keys;
+    if (sn >= 2) {
+        std::string old = std::to_string(ver) + "_" + std::to_string(sn - 2);
+        for (const char *suffix : {"_BA", "_BW", "_GA", "_GW"}) {
+            keys.push_back(old + suffix);
         }
     }
-    std::string v;
-    rc = store_->Get(prefix + "_BW", &v, opt_.timeoutMs);
+    return keys;
+}
+
+int GroupEngine::BarrierOn(const std::string &prefix, uint32_t size, const std::vector<std::string> &gcKeys)
+{
+    int64_t val = 0;
+    int rc = store_->Arrive(prefix + "_BA", prefix + "_BW", size, opt_.timeoutMs, gcKeys, &val);
     if (rc != ST_OK) {
-        MF_ERROR("group barrier: wait failed rc=" << rc << " key=" << prefix << " arrived=" << val << "/" << size);
+        MF_ERROR("group barrier: failed rc=" << rc << " key=" << prefix << " arrived=" << val << "/" << size);
     }
     return MapStoreCode(rc);
 }
@@ -209,16 +200,13 @@ int GroupEngine::GroupBarrier()
     uint32_t sn = 0;
     uint32_t ver = version_.load();
     std::string prefix = RoundPrefix(&sn);
-    ret = BarrierOn(prefix, size_.load());
-    // Everybody has left round sn-2 once round sn-1 completed, so its keys are garbage now.
-    if (ret == GR_OK && opt_.rank == Members().front()) {
-        GcRound(ver, sn);
-    }
+    ret = BarrierOn(prefix, size_.load(), GcKeys(ver, sn));
     return ret;
 }
 
 int GroupEngine::AllGatherOn(const std::string &prefix, uint32_t size, uint32_t myRank, const void *send, uint32_t sendSize,
-                             void *recv, uint32_t recvSize, std::vector<uint32_t> *ranksOut)
+                             void *recv, uint32_t recvSize, std::vector<uint32_t> *ranksOut,
+                             const std::vector<std::string> &gcKeys)
 {
     if (send == nullptr || recv == nullptr || sendSize == 0 || sendSize > GROUP_ALLGATHER_MAX_PAYLOAD ||
         (uint64_t)recvSize < (uint64_t)sendSize * size) {
@@ -227,27 +215,14 @@ int GroupEngine::AllGatherOn(const std::string &prefix, uint32_t size, uint32_t 
     }
     std::string rec((const char *)&myRank, 4);
     rec.append((const char *)send, sendSize);
-    uint64_t total = 0;
-    int rc = store_->Append(prefix + "_GA", rec, &total);
-    if (rc != ST_OK) {
-        return MapStoreCode(rc);
-    }
     const uint64_t full = (uint64_t)size * (4 + sendSize);
-    if (total == full) {
-        rc = store_->Set(prefix + "_GW", "ok");
-        if (rc != ST_OK) {
-            return MapStoreCode(rc);
-        }
-    }
-    std::string v;
-    rc = store_->Get(prefix + "_GW", &v, opt_.timeoutMs);
+    std::string all;
+    int rc = store_->Gather(prefix + "_GA", prefix + "_GW", rec, full, opt_.timeoutMs, gcKeys, &all);
     if (rc != ST_OK) {
-        MF_ERROR("group allgather: wait failed rc=" << rc << " key=" << prefix << " bytes=" << total << "/" << full);
+        MF_ERROR("group allgather: failed rc=" << rc << " key=" << prefix << " expected bytes=" << full);
         return MapStoreCode(rc);
     }
-    std::string all;
-    rc = store_->Get(prefix + "_GA", &all, opt_.timeoutMs);
-    if (rc != ST_OK || all.size() != full) {
+    if (all.size() != full) {
         MF_ERROR("group allgather: bad gathered size " << all.size() << " expected " << full);
         return GR_ERROR;
     }
@@ -281,7 +256,7 @@ int GroupEngine::GroupAllGather(const void *send, uint32_t sendSize, void *recv,
     uint32_t ver = version_.load();
     std::string prefix = RoundPrefix(&sn);
     std::vector<uint32_t> ranks;
-    ret = AllGatherOn(prefix, size_.load(), opt_.rank, send, sendSize, recv, recvSize, &ranks);
+    ret = AllGatherOn(prefix, size_.load(), opt_.rank, send, sendSize, recv, recvSize, &ranks, GcKeys(ver, sn));
     if (ret == GR_OK && opt_.dynamic) {
         // A fresh joiner learns the membership from the first allgather it takes part in.
         std::lock_guard<std::mutex> mg(memberMu_);
@@ -291,9 +266,6 @@ int GroupEngine::GroupAllGather(const void *send, uint32_t sendSize, void *recv,
                 members_.set(r);
             }
         }
-    }
-    if (ret == GR_OK && opt_.rank == Members().front()) {
-        GcRound(ver, sn);
     }
     return ret;
 }
@@ -309,13 +281,12 @@ int GroupEngine::SubGroupBarrier(const std::string &key, uint32_t rankSize, uint
         sn = subSn_["B" + key]++;
     }
     std::string prefix = "SUB_" + key + "_" + std::to_string(sn);
-    int rc = BarrierOn(prefix, rankSize);
-    if (rc == GR_OK && rankId == 0 && sn >= 2) {
+    std::vector<std::string> gc;
+    if (sn >= 2) {
         std::string old = "SUB_" + key + "_" + std::to_string(sn - 2);
-        store_->Remove(old + "_BA", true);
-        store_->Remove(old + "_BW", true);
+        gc = {old + "_BA", old + "_BW"};
     }
-    return rc;
+    return BarrierOn(prefix, rankSize, gc);
 }
 
 int GroupEngine::SubGroupAllGather(const std::string &key, uint32_t rankSize, uint32_t rankId, const void *send,
@@ -330,13 +301,12 @@ int GroupEngine::SubGroupAllGather(const std::string &key, uint32_t rankSize, ui
         sn = subSn_["G" + key]++;
     }
     std::string prefix = "SUBG_" + key + "_" + std::to_string(sn);
-    int rc = AllGatherOn(prefix, rankSize, rankId, send, sendSize, recv, recvSize, nullptr);
-    if (rc == GR_OK && rankId == 0 && sn >= 2) {
+    std::vector<std::string> gc;
+    if (sn >= 2) {
         std::string old = "SUBG_" + key + "_" + std::to_string(sn - 2);
-        store_->Remove(old + "_GA", true);
-        store_->Remove(old + "_GW", true);
+        gc = {old + "_GA", old + "_GW"};
     }
-    return rc;
+    return AllGatherOn(prefix, rankSize, rankId, send, sendSize, recv, recvSize, nullptr, gc);
 }
 
 // ---------------------------------------------------------------------------------------------- dynamic membership

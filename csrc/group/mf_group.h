@@ -84,11 +84,11 @@ public:
 
 private:
     GroupEngine(store::StorePtr st, const GroupOption &opt);
-    int BarrierOn(const std::string &prefix, uint32_t size);
+    int BarrierOn(const std::string &prefix, uint32_t size, const std::vector<std::string> &gcKeys);
     int AllGatherOn(const std::string &prefix, uint32_t size, uint32_t myRank, const void *send, uint32_t sendSize,
-                    void *recv, uint32_t recvSize, std::vector<uint32_t> *ranksOut);
+                    void *recv, uint32_t recvSize, std::vector<uint32_t> *ranksOut, const std::vector<std::string> &gcKeys);
     std::string RoundPrefix(uint32_t *snOut);
-    void GcRound(uint32_t ver, uint32_t sn);
+    static std::vector<std::string> GcKeys(uint32_t ver, uint32_t sn);
     void ListenLoop();
     void HandleEvent(const std::string &value);
     void HandleRankDown(uint32_t rank);

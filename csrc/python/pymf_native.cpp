@@ -144,6 +144,23 @@ void BindNative(py::module_ &m)
             }
             return py::make_tuple(rc, sz);
         })
+        .def("arrive", [](store::ConfigStore &s, const std::string &counter, const std::string &wake, uint32_t expected, int64_t timeoutMs,
+                          const std::vector<std::string> &gc) {
+            int64_t arrived = 0;
+            py::gil_scoped_release nogil;
+            return s.Arrive(counter, wake, expected, timeoutMs, gc, &arrived);
+        }, py::arg("counter_key"), py::arg("wake_key"), py::arg("expected"), py::arg("timeout_ms"), py::arg("gc_keys") = std::vector<std::string>())
+        .def("gather", [](store::ConfigStore &s, const std::string &data, const std::string &wake, py::bytes record, uint64_t fullSize,
+                          int64_t timeoutMs, const std::vector<std::string> &gc) {
+            std::string rec(record), all;
+            int rc;
+            {
+                py::gil_scoped_release nogil;
+                rc = s.Gather(data, wake, rec, fullSize, timeoutMs, gc, &all);
+            }
+            return py::make_tuple(rc, py::bytes(all));
+        }, py::arg("data_key"), py::arg("wake_key"), py::arg("record"), py::arg("full_size"), py::arg("timeout_ms"),
+           py::arg("gc_keys") = std::vector<std::string>())
         .def("cas", [](store::ConfigStore &s, const std::string &k, py::bytes expect, py::bytes exchange) {
             std::string prev, e(expect), x(exchange);
             int rc;

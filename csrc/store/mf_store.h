@@ -43,6 +43,8 @@ enum StoreOp : uint16_t {
     OP_WRITE = 7,
     OP_WATCH_RANK_STATE = 8,
     OP_HEARTBEAT = 9,
+    OP_ARRIVE = 10,  // counter += 1 and wait for the wake key in one round trip (group barrier)
+    OP_GATHER = 11,  // append a record and wait until the value has its full size (group all-gather)
 };
 
 constexpr size_t MAX_KEY_LEN_CLIENT = 1024;
@@ -79,6 +81,60 @@ public:
     virtual int Watch(const std::string &key, WatchKeyCb cb, uint32_t *wid) = 0;
     virtual int WatchRankDown(WatchRankCb cb, uint32_t *wid) = 0;
     virtual int Unwatch(uint32_t wid) = 0;
+    // Barrier arrival: adds 1 to `counterKey`; the arrival that makes it `expected` sets `wakeKey` and removes `gcKeys`
+    // (keys of finished rounds); every caller returns once `wakeKey` exists or after `timeoutMs` (ST_TIMEOUT). The base
+    // version composes it from Add / Set / Get / Remove; a TCP store sends ONE request that the server parks until the last
+    // member has arrived, so a barrier costs one round trip per rank instead of three to seven.
+    virtual int Arrive(const std::string &counterKey, const std::string &wakeKey, uint32_t expected, int64_t timeoutMs,
+                       const std::vector<std::string> &gcKeys, int64_t *arrived)
+    {
+        int64_t val = 0;
+        int rc = Add(counterKey, 1, &val);
+        if (rc != ST_OK) {
+            return rc;
+        }
+        if (arrived != nullptr) {
+            *arrived = val;
+        }
+        if ((uint64_t)val == expected) {
+            for (const auto &k : gcKeys) {
+                Remove(k, true);
+            }
+            rc = Set(wakeKey, "ok");
+            if (rc != ST_OK) {
+                return rc;
+            }
+        }
+        std::string v;
+        return Get(wakeKey, &v, timeoutMs);
+    }
+    // All-gather contribution: appends `record` to `dataKey` and returns the whole value in *all once it is `fullSize`
+    // bytes long (every member has appended), or ST_TIMEOUT. `wakeKey` is set by the completing append. Base version:
+    // Append / Set / Get / Get; a TCP store does it in one request.
+    virtual int Gather(const std::string &dataKey, const std::string &wakeKey, const std::string &record, uint64_t fullSize,
+                       int64_t timeoutMs, const std::vector<std::string> &gcKeys, std::string *all)
+    {
+        uint64_t total = 0;
+        int rc = Append(dataKey, record, &total);
+        if (rc != ST_OK) {
+            return rc;
+        }
+        if (total == fullSize) {
+            for (const auto &k : gcKeys) {
+                Remove(k, true);
+            }
+            rc = Set(wakeKey, "ok");
+            if (rc != ST_OK) {
+                return rc;
+            }
+        }
+        std::string v;
+        rc = Get(wakeKey, &v, timeoutMs);
+        if (rc != ST_OK) {
+            return rc;
+        }
+        return Get(dataKey, all, timeoutMs);
+    }
     virtual std::string CommonPrefix() const { return ""; }
     virtual bool Connected() const { return true; }
     // Handlers for a lost / re-established link to the server (client stores only).
@@ -116,6 +172,24 @@ public:
     }
     int WatchRankDown(WatchRankCb cb, uint32_t *wid) override { return base_->WatchRankDown(std::move(cb), wid); }
     int Unwatch(uint32_t wid) override { return base_->Unwatch(wid); }
+    int Arrive(const std::string &c, const std::string &w, uint32_t expected, int64_t t, const std::vector<std::string> &gc,
+               int64_t *arrived) override
+    {
+        std::vector<std::string> full;
+        for (const auto &k : gc) {
+            full.push_back(prefix_ + k);
+        }
+        return base_->Arrive(prefix_ + c, prefix_ + w, expected, t, full, arrived);
+    }
+    int Gather(const std::string &d, const std::string &w, const std::string &rec, uint64_t fullSize, int64_t t,
+               const std::vector<std::string> &gc, std::string *all) override
+    {
+        std::vector<std::string> full;
+        for (const auto &k : gc) {
+            full.push_back(prefix_ + k);
+        }
+        return base_->Gather(prefix_ + d, prefix_ + w, rec, fullSize, t, full, all);
+    }
     std::string CommonPrefix() const override { return base_->CommonPrefix() + prefix_; }
     bool Connected() const override { return base_->Connected(); }
     void SetBrokenHandler(std::function<void()> f) override { base_->SetBrokenHandler(std::move(f)); }

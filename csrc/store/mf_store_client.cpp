@@ -281,6 +281,47 @@ int TcpStore::Append(const std::string &key, const std::string &value, uint64_t 
     return rc;
 }
 
+int TcpStore::Arrive(const std::string &counterKey, const std::string &wakeKey, uint32_t expected, int64_t timeoutMs,
+                     const std::vector<std::string> &gcKeys, int64_t *arrived)
+{
+    if (!KeyOk(counterKey) || !KeyOk(wakeKey) || gcKeys.size() + 2 > MAX_KEYS_PER_MSG) {
+        return ST_INVALID_KEY;
+    }
+    StoreMessage m;
+    m.userDef = timeoutMs;
+    m.keys = {counterKey, wakeKey};
+    m.keys.insert(m.keys.end(), gcKeys.begin(), gcKeys.end());
+    m.values = {std::to_string(expected)};
+    net::Frame r;
+    int rc = Request(OP_ARRIVE, m, timeoutMs < 0 ? -1 : timeoutMs + 5000, &r);
+    if (arrived != nullptr) {
+        *arrived = -1;  // only the server knows; the reply of a parked arrival carries the wake value
+    }
+    return rc;
+}
+
+int TcpStore::Gather(const std::string &dataKey, const std::string &wakeKey, const std::string &record, uint64_t fullSize,
+                     int64_t timeoutMs, const std::vector<std::string> &gcKeys, std::string *all)
+{
+    if (!KeyOk(dataKey) || !KeyOk(wakeKey) || gcKeys.size() + 2 > MAX_KEYS_PER_MSG) {
+        return ST_INVALID_KEY;
+    }
+    if (record.size() > MAX_VALUE_LEN || fullSize > MAX_VALUE_LEN) {
+        return ST_INVALID_MESSAGE;
+    }
+    StoreMessage m;
+    m.userDef = timeoutMs;
+    m.keys = {dataKey, wakeKey};
+    m.keys.insert(m.keys.end(), gcKeys.begin(), gcKeys.end());
+    m.values = {record, std::to_string(fullSize)};
+    net::Frame r;
+    int rc = Request(OP_GATHER, m, timeoutMs < 0 ? -1 : timeoutMs + 5000, &r);
+    if (rc == ST_OK && all != nullptr) {
+        *all = std::move(r.body);
+    }
+    return rc;
+}
+
 int TcpStore::Cas(const std::string &key, const std::string &expect, const std::string &exchange, std::string *previous)
 {
     if (!KeyOk(key)) {

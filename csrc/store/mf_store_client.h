@@ -41,6 +41,10 @@ public:
     int Watch(const std::string &key, WatchKeyCb cb, uint32_t *wid) override;
     int WatchRankDown(WatchRankCb cb, uint32_t *wid) override;
     int Unwatch(uint32_t wid) override;
+    int Arrive(const std::string &counterKey, const std::string &wakeKey, uint32_t expected, int64_t timeoutMs,
+               const std::vector<std::string> &gcKeys, int64_t *arrived) override;
+    int Gather(const std::string &dataKey, const std::string &wakeKey, const std::string &record, uint64_t fullSize,
+               int64_t timeoutMs, const std::vector<std::string> &gcKeys, std::string *all) override;
     bool Connected() const override { return rpc_.Connected(); }
     void SetBrokenHandler(std::function<void()> f) override { onBroken_ = std::move(f); }
     void SetReconnectHandler(std::function<void()> f) override { onReconnect_ = std::move(f); }
@@ -95,6 +99,16 @@ public:
     int Watch(const std::string &k, WatchKeyCb cb, uint32_t *wid) override { return Current()->Watch(k, std::move(cb), wid); }
     int WatchRankDown(WatchRankCb cb, uint32_t *wid) override { return Current()->WatchRankDown(std::move(cb), wid); }
     int Unwatch(uint32_t wid) override { return Current()->Unwatch(wid); }
+    int Arrive(const std::string &c, const std::string &w, uint32_t expected, int64_t t, const std::vector<std::string> &gc,
+               int64_t *arrived) override
+    {
+        return Current()->Arrive(c, w, expected, t, gc, arrived);
+    }
+    int Gather(const std::string &d, const std::string &w, const std::string &rec, uint64_t fullSize, int64_t t,
+               const std::vector<std::string> &gc, std::string *all) override
+    {
+        return Current()->Gather(d, w, rec, fullSize, t, gc, all);
+    }
     bool Connected() const override { return const_cast<HaStore *>(this)->Current()->Connected(); }
     void SetBrokenHandler(std::function<void()> f) override { Current()->SetBrokenHandler(std::move(f)); }
     void SetReconnectHandler(std::function<void()> f) override { Current()->SetReconnectHandler(std::move(f)); }

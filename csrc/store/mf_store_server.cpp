@@ -426,6 +426,83 @@ void StoreServer::HandleGet(net::LinkId link, const net::Frame &f, const StoreMe
     cv_.notify_all();
 }
 
+// OP_ARRIVE (keys: counter, wake, then keys to drop on completion; values: expected count) and OP_GATHER (keys: data, wake,
+// then keys to drop; values: record, full size). The request that completes the rendezvous stores the wake key, which answers every parked
+// request of the round through the ordinary waiter list; all others are parked on the wake key exactly like a blocking GET.
+// What a waiter receives is the wake key's value: "ok" for a barrier, the gathered bytes for an all-gather (the wake key of
+// a gather holds the data so that late or repeated GETs of it see the same thing).
+void StoreServer::HandleRendezvous(net::LinkId link, const net::Frame &f, const StoreMessage &m)
+{
+    const bool gather = f.type == OP_GATHER;
+    if (m.keys.size() < 2 || m.values.size() != (gather ? 2u : 1u)) {
+        Reply(link, f, ST_INVALID_MESSAGE, "bad rendezvous message");
+        return;
+    }
+    for (const auto &k : m.keys) {
+        if (k.empty() || k.size() > MAX_KEY_LEN_SERVER) {
+            Reply(link, f, ST_INVALID_KEY, "invalid key");
+            return;
+        }
+    }
+    char *end = nullptr;
+    errno = 0;
+    const std::string &targetText = m.values[gather ? 1 : 0];
+    unsigned long long target = std::strtoull(targetText.c_str(), &end, 10);
+    if (targetText.empty() || *end != '\0' || errno != 0 || target == 0 || (gather && target > MAX_VALUE_LEN)) {
+        Reply(link, f, ST_INVALID_MESSAGE, "bad rendezvous target");
+        return;
+    }
+    const std::string &key = m.keys[0];
+    const std::string &wake = m.keys[1];
+    std::string wakeValue;
+    bool complete = false;
+    {
+        std::unique_lock<std::mutex> lk(mu_);
+        std::string cur;
+        bool had = backend_->Get(key, &cur);
+        if (gather) {
+            if (cur.size() + m.values[0].size() > target) {
+                lk.unlock();
+                Reply(link, f, ST_INVALID_MESSAGE, "gather overflows its full size");
+                return;
+            }
+            cur.append(m.values[0]);
+            backend_->Put(key, cur);
+            complete = cur.size() == target;
+            if (complete) {
+                wakeValue = cur;
+            }
+        } else {
+            unsigned long long v = (had ? std::strtoull(cur.c_str(), nullptr, 10) : 0) + 1;
+            backend_->Put(key, std::to_string(v));
+            complete = v == target;
+            if (complete) {
+                wakeValue = "ok";
+            }
+        }
+        if (complete) {
+            for (size_t i = 2; i < m.keys.size(); i++) {
+                backend_->Delete(m.keys[i]);
+            }
+            backend_->Put(wake, wakeValue);
+        } else if (backend_->Get(wake, &wakeValue)) {
+            complete = true;  // a member that arrives after the round completed (re-sent request): answer at once
+        } else {
+            Waiter w{link, f.seq, m.userDef > 0 ? NowMs() + (uint64_t)m.userDef : 0, nextWaiterId_++};
+            keyWaiters_[wake].push_back(w);
+            if (w.deadlineMs != 0) {
+                timed_.emplace(w.deadlineMs, std::make_pair(wake, w.id));
+            }
+        }
+    }
+    if (complete) {
+        WakeWaiters(wake, wakeValue);
+        Reply(link, f, ST_OK, wakeValue);
+    } else {
+        cv_.notify_all();
+    }
+}
+
 void StoreServer::OnMessage(net::LinkId link, const net::Frame &f)
 {
     {
@@ -448,6 +525,10 @@ void StoreServer::OnMessage(net::LinkId link, const net::Frame &f)
         std::lock_guard<std::mutex> g(mu_);
         rankWatchers_.emplace_back(link, f.seq);
         return;  // no immediate reply: notifications are pushed on this seq
+    }
+    if (f.type == OP_ARRIVE || f.type == OP_GATHER) {
+        HandleRendezvous(link, f, m);
+        return;
     }
     if (m.keys.size() != 1 || m.keys[0].empty() || m.keys[0].size() > MAX_KEY_LEN_SERVER) {
         Reply(link, f, ST_INVALID_KEY, "invalid key");

@@ -67,6 +67,7 @@ private:
     void ReplyText(net::LinkId link, uint32_t seq, uint16_t type, int result, const std::string &value);
     void WakeWaiters(const std::string &key, const std::string &value);
     void HandleGet(net::LinkId link, const net::Frame &f, const StoreMessage &m);
+    void HandleRendezvous(net::LinkId link, const net::Frame &f, const StoreMessage &m);
     int AssignRank(net::LinkId link, const std::string &key, std::string *out);
     void HouseKeeping();
     void LinkGone(net::LinkId link, bool fromHeartbeat);

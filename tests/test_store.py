@@ -127,6 +127,70 @@ def test_prefix_and_nested_prefix(mf, pair):
     assert p1.get("k", 0)[0] == ST_NOT_EXIST
 
 
+def test_arrive_is_one_request_rendezvous(mf, port):
+    """Three clients arrive at a barrier key: nobody returns before the last one, the completing request drops the listed
+    keys of an older round, a late duplicate is answered at once, and an arrival that nobody completes times out."""
+    n = mf.native
+    srv = n.StoreServer()
+    assert srv.start("127.0.0.1", port) == 0
+    clients = [n.TcpStore("127.0.0.1", port, False, 0, i) for i in range(3)]
+    for c in clients:
+        assert c.startup(5, 100) == 0
+    assert clients[0].set("old_BA", b"3") == ST_OK and clients[0].set("old_BW", b"ok") == ST_OK
+    done = []
+
+    def arrive(i):
+        rc = clients[i].arrive("r1_BA", "r1_BW", 3, 5000, ["old_BA", "old_BW"])
+        done.append((i, rc, time.monotonic()))
+
+    threads = [threading.Thread(target=arrive, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    time.sleep(0.3)
+    assert done == []  # parked on the server
+    assert clients[0].get("old_BA", 0)[0] == ST_OK  # nothing collected before the round completes
+    t_last = time.monotonic()
+    assert clients[2].arrive("r1_BA", "r1_BW", 3, 5000, ["old_BA", "old_BW"]) == ST_OK
+    for t in threads:
+        t.join(5)
+    assert sorted(d[0] for d in done) == [0, 1] and all(d[1] == ST_OK and d[2] >= t_last for d in done)
+    assert clients[0].get("r1_BW", 0) == (ST_OK, b"ok")
+    assert clients[0].get("old_BA", 0)[0] == ST_NOT_EXIST and clients[0].get("old_BW", 0)[0] == ST_NOT_EXIST
+    assert clients[1].arrive("r1_BA", "r1_BW", 3, 5000) == ST_OK  # the wake key already exists
+    t0 = time.monotonic()
+    assert clients[1].arrive("r2_BA", "r2_BW", 3, 200) == ST_TIMEOUT
+    assert 0.15 <= time.monotonic() - t0 < 3
+    assert clients[1].arrive("r3_BA", "r3_BW", 0, 200) != ST_OK  # a rendezvous of nobody is refused
+    for c in clients:
+        c.shutdown()
+    srv.stop()
+
+
+def test_gather_returns_every_record_once_full(mf, pair):
+    srv, cli = pair
+    pre = mf.native.prefix_store(cli, "G_")
+    out = []
+    t = threading.Thread(target=lambda: out.append(pre.gather("d", "w", b"AAAA", 8, 5000)))
+    t.start()
+    time.sleep(0.2)
+    assert out == []
+    assert srv.gather("G_d", "G_w", b"BBBB", 8, 5000) == (ST_OK, b"AAAABBBB")
+    t.join(5)
+    assert out == [(ST_OK, b"AAAABBBB")]
+    assert srv.gather("G_d", "G_w", b"CCCC", 8, 1000)[0] != ST_OK  # the value would outgrow its full size
+    assert srv.gather("x", "xw", b"AAAA", 12, 150)[0] == ST_TIMEOUT
+
+
+def test_arrive_and_gather_base_composition(mf, pair):
+    """An HA store wrapper has no request of its own for the rendezvous; a store without one composes it from the basic
+    operations. Both routes end in the same state."""
+    srv, cli = pair
+    ha = mf.native.ha_store(cli) if hasattr(mf.native, "ha_store") else cli
+    assert ha.arrive("b_BA", "b_BW", 1, 1000) == ST_OK
+    assert srv.get("b_BW", 0) == (ST_OK, b"ok")
+    assert ha.gather("g", "gw", b"zz", 2, 1000) == (ST_OK, b"zz")
+
+
 def test_watch_and_unwatch(pair):
     srv, cli = pair
     seen = []
