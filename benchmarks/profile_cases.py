@@ -2,10 +2,13 @@
 """Small, self-ending single-GPU cases for profiler captures: each runs ONE kernel of the library a few times on inputs that
 are larger than L2 (126 MB) where DRAM figures matter but hold at most a few GB on the device.
 
-    python benchmarks/profile_cases.py xcopy | batch | gemm | allreduce | dispatch | reshard
+    python benchmarks/profile_cases.py xcopy | peer | batch | gemm | allreduce | dispatch | reshard
+
+`peer` needs two GPUs in ONE process (no second rank): GPU 0 pushes 256 MiB into GPU 1's memory over NVLink, so the link's byte
+counters (nvltx__bytes / nvlrx__bytes) can be read next to the kernel's duration.
 
 Capture (after the same command has exited 0 without the profiler), e.g.:
-    ncu --set full --clock-control none -k regex:mf_moe_grouped_gemm -c 2 -o gpurun_out/prof_gemm python benchmarks/profile_cases.py gemm
+    ncu --set full --clock-control none -k regex:mf_moe_grouped_gemm -c 2 -o <report> python benchmarks/profile_cases.py gemm
 """
 from __future__ import annotations
 
@@ -30,6 +33,27 @@ def case_xcopy():
         assert mf.native.xcopy(b.data_ptr(), a.data_ptr(), n, -1, s) == 0   # load/store variant
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+def case_peer():
+    import torch
+    import memfabric_hybrid_b200 as mf
+
+    assert torch.cuda.device_count() >= 2, "the peer case needs two GPUs in this process"
+    n = 256 << 20
+    a = torch.empty(n, dtype=torch.uint8, device="cuda:0")
+    b = torch.zeros(n, dtype=torch.uint8, device="cuda:1")
+    b.copy_(a)  # the first cross-device copy makes torch enable peer access both ways
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    s = torch.cuda.current_stream().cuda_stream
+    mf.native.fill_pattern(a.data_ptr(), n, 1, s)
+    for _ in range(3):
+        assert mf.native.xcopy(b.data_ptr(), a.data_ptr(), n, 0, s) == 0    # bulk-copy (TMA) variant, stores cross the link
+    for _ in range(3):
+        assert mf.native.xcopy(b.data_ptr(), a.data_ptr(), n, -1, s) == 0   # load/store variant
+    torch.cuda.synchronize(0)
+    assert torch.equal(a, b.to("cuda:0"))
 
 
 def case_batch():
@@ -139,5 +163,5 @@ if __name__ == "__main__":
     import torch
 
     torch.cuda.set_device(0)
-    {"xcopy": case_xcopy, "batch": case_batch, "gemm": case_gemm, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
+    {"xcopy": case_xcopy, "peer": case_peer, "batch": case_batch, "gemm": case_gemm, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
     print("ok", sys.argv[1])

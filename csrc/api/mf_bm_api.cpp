@@ -10,6 +10,7 @@
 #include <map>
 #include <mutex>
 
+#include "../net/mf_tls.h"
 #include "../hybm/mf_cuda.h"
 #include "../store/mf_store_client.h"
 #include "../util/mf_log.h"
@@ -386,6 +387,24 @@ extern "C" int32_t mf_bm_init(const char *storeURL, uint32_t worldSize, uint16_t
         return MF_OK;
     }
     int rc = MF_OK;
+    if (config->storeTlsConfig.tlsEnable) {
+        // The struct form of the store's TLS options; it applies to the stores created below.
+        auto text = [](const char *p) { return std::string(p, strnlen(p, MF_TLS_PATH_SIZE)); };
+        const mf_tls_config &t = config->storeTlsConfig;
+        net::TlsConfigPaths paths;
+        paths.enable = true;
+        paths.caPath = text(t.caPath);
+        paths.crlPath = text(t.crlPath);
+        paths.certPath = text(t.certPath);
+        paths.keyPath = text(t.keyPath);
+        paths.keyPassPath = text(t.keyPassPath);
+        paths.packagePath = text(t.packagePath);
+        paths.decrypterLibPath = text(t.decrypterLibPath);
+        net::TlsOptions opt;
+        std::string why;
+        MF_CHECK_RET(net::TlsOptionsFromPaths(paths, &opt, &why), MF_INVALID_PARAM, "bm init: " << why);
+        net::SetStoreTlsOptions(opt);
+    }
     if (config->startConfigStoreOnly) {
         g.base = mf::api::OpenStore(storeURL, true, true, worldSize, -1, config->initTimeout, &rc);
         return g.base ? MF_OK : rc;

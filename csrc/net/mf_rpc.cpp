@@ -1,5 +1,6 @@
 #include "mf_rpc.h"
 
+#include "../util/mf_net_util.h"
 #include "mf_tls.h"
 
 #include <arpa/inet.h>
@@ -76,7 +77,8 @@ bool ParseUrl(const std::string &urlIn, Endpoint *out)
             return false;
         }
     } else if (std::isdigit((unsigned char)host[0])) {
-        if (inet_pton(AF_INET, host.c_str(), buf) != 1) {
+        // Dotted quad: four 0-255 fields without leading zeros (0.0.0.0 is a legal listen address).
+        if (!util::IsValidIpv4(host, true) || inet_pton(AF_INET, host.c_str(), buf) != 1) {
             return false;
         }
     }

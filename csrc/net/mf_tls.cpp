@@ -17,6 +17,7 @@
 #include <ctime>
 #include <thread>
 
+#include "../util/mf_file_util.h"
 #include "../util/mf_log.h"
 
 namespace mf {
@@ -58,7 +59,11 @@ Api *LoadApi(const std::string &packagePath, std::string *err)
     auto open = [&](const char *name) -> void * {
         void *h = nullptr;
         if (!packagePath.empty()) {
-            h = dlopen((packagePath + "/" + name).c_str(), RTLD_NOW | RTLD_GLOBAL);
+            // Only a regular file that really lives in the configured directory is handed to dlopen.
+            std::string real;
+            if (util::ResolveLibrary(packagePath, name, &real)) {
+                h = dlopen(real.c_str(), RTLD_NOW | RTLD_GLOBAL);
+            }
         }
         return h != nullptr ? h : dlopen(name, RTLD_NOW | RTLD_GLOBAL);
     };
@@ -140,29 +145,20 @@ std::vector<std::string> SplitList(const std::string &s, char sep)
     return out;
 }
 
+// Certificates, keys, CRLs and pass-phrase files: regular files, leaf not a symbolic link, at most 10 MiB.
 bool ReadFile(const std::string &path, std::string *out)
 {
-    FILE *f = fopen(path.c_str(), "rb");
-    if (f == nullptr) {
+    std::string why;
+    if (!util::ReadConfigFile(path, util::kMaxConfigFileBytes, out, &why)) {
+        MF_WARN("tls: " << why);
         return false;
     }
-    char buf[4096];
-    size_t n;
-    out->clear();
-    while ((n = fread(buf, 1, sizeof(buf), f)) > 0) {
-        out->append(buf, n);
-        if (out->size() > (16u << 20)) {
-            break;
-        }
-    }
-    fclose(f);
     return true;
 }
 
 bool IsFile(const std::string &path)
 {
-    struct stat st {};
-    return !path.empty() && path.size() < 4096 && stat(path.c_str(), &st) == 0 && S_ISREG(st.st_mode);
+    return util::IsRegularFile(path);
 }
 
 std::string Join(const std::string &dir, const std::string &file)
@@ -294,6 +290,80 @@ std::vector<std::pair<void *, std::unique_ptr<CertWatcher>>> g_watchers;  // key
 }  // namespace
 
 bool TlsLibraryAvailable(const std::string &packagePath, std::string *err) { return LoadApi(packagePath, err) != nullptr; }
+
+TlsDecryptFn LoadDecrypterLibrary(const std::string &path, std::string *err)
+{
+    auto fail = [&](const std::string &m) {
+        if (err != nullptr) {
+            *err = m;
+        }
+        return TlsDecryptFn();
+    };
+    std::string why;
+    if (!util::CheckConfigFile(path, 256u << 20, false, &why)) {
+        return fail("decrypter library: " + why);
+    }
+    std::string real = path;
+    if (!util::Canonicalize(&real)) {
+        return fail("decrypter library: cannot resolve " + path);
+    }
+    void *h = dlopen(real.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (h == nullptr) {
+        const char *e = dlerror();
+        return fail(std::string("decrypter library: dlopen failed: ") + (e ? e : "unknown"));
+    }
+    using RawFn = int (*)(const char *, size_t, char *, size_t);
+    RawFn fn = (RawFn)dlsym(h, "DecryptPassword");
+    if (fn == nullptr) {
+        dlclose(h);
+        return fail("decrypter library: symbol DecryptPassword not found in " + real);
+    }
+    return [fn](const char *cipher, size_t cipherLen, char *plain, size_t &plainLen) -> int {
+        if (plain == nullptr || plainLen == 0) {
+            return -1;
+        }
+        std::memset(plain, 0, plainLen);
+        int rc = fn(cipher, cipherLen, plain, plainLen - 1);
+        if (rc != 0) {
+            return rc;
+        }
+        plainLen = strnlen(plain, plainLen - 1);
+        return 0;
+    };
+}
+
+bool TlsOptionsFromPaths(const TlsConfigPaths &in, TlsOptions *out, std::string *err)
+{
+    if (out == nullptr) {
+        return false;
+    }
+    *out = TlsOptions();
+    out->enable = in.enable;
+    if (!in.enable) {
+        return true;
+    }
+    if (in.caPath.empty() || in.certPath.empty() || in.keyPath.empty()) {
+        if (err != nullptr) {
+            *err = "tls config: caPath, certPath and keyPath are required";
+        }
+        return false;
+    }
+    out->caFiles = {in.caPath};
+    if (!in.crlPath.empty()) {
+        out->crlFiles = {in.crlPath};
+    }
+    out->cert = in.certPath;
+    out->pk = in.keyPath;
+    out->pkPwd = in.keyPassPath;
+    out->packagePath = in.packagePath;
+    if (!in.decrypterLibPath.empty()) {
+        out->decrypt = LoadDecrypterLibrary(in.decrypterLibPath, err);
+        if (!out->decrypt) {
+            return false;
+        }
+    }
+    return true;
+}
 
 void SetStoreTlsOptions(const TlsOptions &opt)
 {

@@ -89,6 +89,20 @@ private:
     std::string err_;
 };
 
+// The struct form of the options carried by the BM configuration (mf_tls_config: one CA file, one CRL file, certificate, key,
+// pass-phrase file, OpenSSL directory, decrypter library). Fills *out; loads the decrypter library when one is named.
+struct TlsConfigPaths {
+    bool enable{false};
+    std::string caPath, crlPath, certPath, keyPath, keyPassPath, packagePath, decrypterLibPath;
+};
+bool TlsOptionsFromPaths(const TlsConfigPaths &in, TlsOptions *out, std::string *err);
+// Loads a key-pass decrypter from a shared object by path and returns it as a TlsDecryptFn (empty on failure, *err says
+// why). The library must be a regular, non-symlinked file and export
+//     int DecryptPassword(const char *cipherText, size_t cipherTextLen, char *plainText, size_t plainTextCapacity)
+// which writes a NUL-terminated pass phrase (the reference's plug-in contract, src/util/csrc/mf_tls_util.h:32-48).
+// The library stays loaded for the life of the process.
+TlsDecryptFn LoadDecrypterLibrary(const std::string &path, std::string *err);
+
 // Process-wide options for the config store's links, set through mf_set_conf_store_tls / mf_set_config_store_tls_key.
 void SetStoreTlsOptions(const TlsOptions &opt);
 TlsOptions GetStoreTlsOptions();

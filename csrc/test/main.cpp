@@ -5,7 +5,11 @@
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <atomic>
+#include <climits>
+#include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <string>
@@ -19,6 +23,10 @@
 #include "mf/mf_bm.h"
 #include "mf/mf_hybm.h"
 #include "store/mf_store_client.h"
+#include "util/mf_file_util.h"
+#include "util/mf_net_util.h"
+#include "util/mf_str_util.h"
+#include "util/mf_sync.h"
 
 using namespace mf;
 
@@ -58,6 +66,115 @@ static bool TestCodec()
     EXPECT(store::UnpackMessage(b, &out) && out.userDef == 42 && out.keys == m.keys && out.values == m.values);
     EXPECT(!store::UnpackMessage(b.substr(0, b.size() - 1), &out));
     EXPECT(!store::UnpackMessage(b + "x", &out));
+    return ok;
+}
+
+static bool TestUtilLayer()
+{
+    bool ok = true;
+    using namespace mf::util;
+    // strings and numbers
+    EXPECT(Trim("  a b\t\n") == "a b" && Trim(" \t") == "");
+    EXPECT(Split("a,,b", ',').size() == 3 && Split("", ',').empty() && Split("x", ',').size() == 1);
+    EXPECT(StartsWith("tcp://x", "tcp://") && !StartsWith("tc", "tcp://"));
+    uint16_t u16 = 0;
+    int32_t i32 = 0;
+    EXPECT(ParseInt<uint16_t>("65535", &u16) && u16 == 65535 && !ParseInt<uint16_t>("65536", &u16));
+    EXPECT(!ParseInt<uint16_t>("-1", &u16) && !ParseInt<uint16_t>(" 1", &u16) && !ParseInt<uint16_t>("1x", &u16) && !ParseInt<uint16_t>("", &u16));
+    EXPECT(ParseInt<int32_t>("-2147483648", &i32) && i32 == INT32_MIN && !ParseInt<int32_t>("2147483648", &i32));
+    EXPECT(WouldOverflow<uint32_t>(0xFFFFFFF0u, 0x20u, UINT32_MAX, '+') && !WouldOverflow<uint32_t>(1, 2, UINT32_MAX, '+'));
+    EXPECT(WouldOverflow<uint64_t>(1ull << 40, 1ull << 30, UINT64_MAX, '*') && !WouldOverflow<uint64_t>(0, 5, 10, '*'));
+    EXPECT(ExtractBits(0xABCD1234u, 8, 8) == 0x12 && ExtractBits(0xFFFFFFFFu, 0, 32) == 0xFFFFFFFFu && ExtractBits(1, 30, 4) == 0);
+    // addresses
+    EXPECT(IsValidIpv4("10.0.0.1") && IsValidIpv4("255.255.255.255") && !IsValidIpv4("256.1.1.1") && !IsValidIpv4("1.2.3"));
+    EXPECT(!IsValidIpv4("01.2.3.4") && !IsValidIpv4("1.2.3.4.") && !IsValidIpv4("1..3.4") && !IsValidIpv4("a.b.c.d"));
+    EXPECT(!IsValidIpv4("0.0.0.0") && IsValidIpv4("0.0.0.0", true) && !IsValidIpv4("1.2.3.4 "));
+    EXPECT(IsValidIpv6("::1") && IsValidIpv6("fe80::1:2") && !IsValidIpv6("::g") && !IsValidIpv6(""));
+    std::string ip, why;
+    uint16_t port = 0;
+    EXPECT(ParseIpv4Port("127.0.0.1:8570", 1025, &ip, &port, &why) && ip == "127.0.0.1" && port == 8570);
+    EXPECT(!ParseIpv4Port("127.0.0.1:80", 1025, &ip, &port, &why) && !ParseIpv4Port("127.0.0.1", 0, &ip, &port, &why));
+    EXPECT(!ParseIpv4Port("127.0.0.1:70000", 0, &ip, &port, &why) && !ParseIpv4Port("300.0.0.1:8000", 0, &ip, &port, &why));
+    EXPECT(Ipv4InCidr("192.168.3.77", "192.168.0.0/16") && !Ipv4InCidr("192.169.0.1", "192.168.0.0/16") && Ipv4InCidr("8.8.8.8", "0.0.0.0/0"));
+    EXPECT(!Ipv4InCidr("1.2.3.4", "1.2.3.0/33") && !Ipv4InCidr("1.2.3.4", "1.2.3.0"));
+    NetAddr a4, a4b, a6;
+    EXPECT(NetAddr::Parse("10.1.2.3", &a4) && NetAddr::Parse("10.1.2.3", &a4b) && NetAddr::Parse("::1", &a6) && !NetAddr::Parse("nope", &a4b));
+    EXPECT(a4 == a4b && a4 != a6 && NetAddrHash()(a4) == NetAddrHash()(a4b) && a4.ToString() == "10.1.2.3" && a6.ToString() == "::1");
+    // files
+    char tmpl[] = "/tmp/mf_util_test_XXXXXX";
+    const char *root = mkdtemp(tmpl);
+    EXPECT(root != nullptr);
+    if (root != nullptr) {
+        std::string dir = std::string(root) + "/a/b/c";
+        EXPECT(MakeDirs(dir, 0750) && IsDir(dir) && MakeDirs(dir, 0750));
+        std::string file = dir + "/cert.pem", link = dir + "/link.pem", big = dir + "/big.bin";
+        FILE *f = fopen(file.c_str(), "w");
+        fputs("hello", f);
+        fclose(f);
+        EXPECT(symlink(file.c_str(), link.c_str()) == 0);
+        f = fopen(big.c_str(), "w");
+        for (int i = 0; i < 100; i++) {
+            fputs("0123456789", f);
+        }
+        fclose(f);
+        EXPECT(IsRegularFile(file) && !IsSymlink(file) && IsSymlink(link) && FileSize(file) == 5 && !IsEmptyFile(file));
+        EXPECT(CheckConfigFile(file, 1024, false, &why));
+        EXPECT(!CheckConfigFile(link, 1024, false, &why) && why.find("symbolic") != std::string::npos);
+        EXPECT(CheckConfigFile(link, 1024, true, &why));
+        EXPECT(!CheckConfigFile(big, 512, false, &why) && !CheckConfigFile(dir, 1024, false, &why));
+        EXPECT(!CheckConfigFile(dir + "/absent", 1024, false, &why) && !CheckConfigFile("", 1024, false, &why));
+        std::string content;
+        EXPECT(ReadConfigFile(file, 1024, &content, &why) && content == "hello");
+        std::string canon = dir + "/../c/cert.pem";
+        EXPECT(Canonicalize(&canon) && canon.find("..") == std::string::npos);
+        std::string lib;
+        EXPECT(ResolveLibrary(dir, "cert.pem", &lib) && lib == canon);
+        EXPECT(!ResolveLibrary(dir, "../c/cert.pem", &lib) && !ResolveLibrary(dir, "absent.so", &lib));
+        std::string outer = std::string(root) + "/outer.so", escape = dir + "/escape.so";
+        f = fopen(outer.c_str(), "w");
+        fputs("x", f);
+        fclose(f);
+        EXPECT(symlink(outer.c_str(), escape.c_str()) == 0);
+        EXPECT(!ResolveLibrary(dir, "escape.so", &lib));  // the link leads out of the directory
+        EXPECT(RemoveFile(link) && IsRegularFile(file));                          // the link goes, its target stays
+        EXPECT(!RemoveTree("/") && !RemoveTree("/tmp") && !RemoveTree("relative/path"));
+        EXPECT(RemoveTree(root) && !Exists(root));
+    }
+    // locks: readers run together, a writer runs alone
+    RwLock rw;
+    SpinLock spin;
+    std::atomic<int> readersInside{0}, maxReaders{0}, violations{0};
+    long counter = 0, spinCounter = 0;
+    std::vector<std::thread> th;
+    for (int t = 0; t < 6; t++) {
+        th.emplace_back([&, t]() {
+            for (int i = 0; i < 2000; i++) {
+                if (t < 2) {
+                    WriteGuard g(rw);
+                    if (readersInside.load() != 0) {
+                        violations++;
+                    }
+                    counter++;
+                } else {
+                    ReadGuard g(rw);
+                    int now = ++readersInside;
+                    int prev = maxReaders.load();
+                    while (now > prev && !maxReaders.compare_exchange_weak(prev, now)) {
+                    }
+                    --readersInside;
+                }
+                SpinGuard sg(spin);
+                spinCounter++;
+            }
+        });
+    }
+    for (auto &t : th) {
+        t.join();
+    }
+    EXPECT(violations.load() == 0 && counter == 4000 && spinCounter == 12000);
+    EXPECT(rw.TryLockWrite());
+    EXPECT(!rw.TryLockRead());
+    rw.Unlock();
     return ok;
 }
 
@@ -273,6 +390,7 @@ int main(int argc, char **argv)
     mf_set_log_level(3);
     std::vector<Case> cases = {
         {"codec", TestCodec},
+        {"util_layer", TestUtilLayer},
         {"va_manager_and_range_pool", TestVaAndPool},
         {"store_and_group_engine", TestStoreAndGroup},
         {"hybm_single_rank_host_pool", TestHybmSingleRankHostPool},

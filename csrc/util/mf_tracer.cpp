@@ -1,3 +1,4 @@
+#include "mf_file_util.h"
 #include "mf_tracer.h"
 
 #include <condition_variable>
@@ -49,8 +50,12 @@ int Tracer::Init(const std::string &dumpDir, int periodSec)
     impl_->periodSec = periodSec;
     enabled_.store(true);
     if (!dumpDir.empty()) {
-        ::mkdir(dumpDir.c_str(), 0750);
-        impl_->path = dumpDir + "/mf_tracer_" + std::to_string((int)getpid()) + ".dat";
+        std::string dir = dumpDir;
+        if (!util::MakeDirs(dir, 0750) || !util::Canonicalize(&dir) || !util::Writable(dir)) {
+            MF_WARN("tracer: dump directory " << dumpDir << " cannot be created or written; periodic dumps are off");
+            return 0;
+        }
+        impl_->path = dir + "/mf_tracer_" + std::to_string((int)getpid()) + ".dat";
         impl_->dumper = std::thread([this]() {
             std::unique_lock<std::mutex> lk(impl_->mu);
             while (!impl_->stop) {

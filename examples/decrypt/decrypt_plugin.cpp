@@ -35,6 +35,17 @@ extern "C" int mf_example_decrypt(const char *cipherText, size_t cipherTextLen, 
     return 0;
 }
 
+// The by-path contract (mf_tls_config.decrypterLibPath of the BM configuration): capacity by value, NUL-terminated result.
+extern "C" int DecryptPassword(const char *cipherText, size_t cipherTextLen, char *plainText, size_t plainTextCapacity)
+{
+    size_t n = plainTextCapacity;
+    if (mf_example_decrypt(cipherText, cipherTextLen, plainText, &n) != 0 || n >= plainTextCapacity) {
+        return -1;
+    }
+    plainText[n] = '\0';
+    return 0;
+}
+
 #ifndef MF_DECRYPT_PLUGIN_ONLY
 #include <dlfcn.h>
 
