@@ -23,7 +23,7 @@ NVFLAGS   := -ccbin /usr/bin/g++ -std=c++17 -O3 -lineinfo -gencode arch=compute_
              --expt-relaxed-constexpr -Xptxas -v
 LDFLAGS   := -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lrt -pthread -Wl,-z,relro,-z,now
 
-HOST_SRCS := $(wildcard csrc/util/*.cpp csrc/net/*.cpp csrc/store/*.cpp csrc/group/*.cpp csrc/hybm/*.cpp csrc/api/*.cpp)
+HOST_SRCS := $(wildcard csrc/util/*.cpp csrc/net/*.cpp csrc/transport/*.cpp csrc/store/*.cpp csrc/group/*.cpp csrc/hybm/*.cpp csrc/api/*.cpp)
 CUDA_SRCS := $(wildcard csrc/kernels/*.cu)
 HOST_OBJS := $(patsubst csrc/%.cpp,$(BUILD)/%.o,$(HOST_SRCS))
 CUDA_OBJS := $(patsubst csrc/%.cu,$(BUILD)/%.cu.o,$(CUDA_SRCS))

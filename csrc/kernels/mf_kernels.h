@@ -24,6 +24,8 @@ enum { MF_K_OK = 0, MF_K_INVALID = -2, MF_K_LAUNCH_FAILED = -1, MF_K_TIMEOUT = -
 // Single copy of n bytes between any two device-visible addresses (local HBM, peer HBM over NVLink, pinned host).
 // ctas 0 = pick from the size.
 int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_stream_t stream);
+int mf_k_xcopy_shaped(void *dst, const void *src, size_t n, uint32_t tile, uint32_t stages, uint32_t inflight, uint32_t blocked, int ctas,
+                      mf_stream_t stream);
 
 typedef struct {
     uint64_t src;

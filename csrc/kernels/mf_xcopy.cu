@@ -14,6 +14,7 @@
 // 512-thread CTAs at two per SM (128 KiB in flight per SM — enough to cover HBM3e and NVLink latency), persistent grid.
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstdlib>
 
 #include "mf_copy_device.cuh"
@@ -54,9 +55,9 @@ mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict
 // the bulk asynchronous copy engine of the SM (cp.async.bulk, no tensor map, no multicast), six tiles deep. One thread issues
 // loads, one thread issues stores; mbarriers hand tiles over. The SM's load/store units and register file stay out of the
 // data path, so the copy runs at what the memory system and NVLink deliver. Waits are bounded like everywhere else.
-constexpr int kTmaStages = 6;
-constexpr uint32_t kTmaTile = 32 * 1024;
-constexpr int kTmaStoresInFlight = 3;
+constexpr uint32_t kTmaDefaultStages = 6;
+constexpr uint32_t kTmaDefaultTile = 32 * 1024;
+constexpr uint32_t kTmaDefaultInFlight = 3;
 
 __device__ __forceinline__ uint32_t SmemU32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -78,12 +79,37 @@ __device__ __forceinline__ bool MbarWaitParity(uint64_t *bar, uint32_t parity)
     return false;  // about a minute of polling: the caller stops issuing work
 }
 
+constexpr int kTmaMaxStages = 16;
+
+// Shape of the bulk-copy pipeline: bytes per tile (a multiple of 16), tiles of shared memory per CTA, how many stores may
+// still be reading shared memory before a tile is handed back to the loader, and whether a CTA walks the copy with a stride
+// of the grid (0) or owns one contiguous run of tiles (1).
+struct TmaShape {
+    uint32_t tile;
+    uint32_t stages;
+    uint32_t inflight;
+    uint32_t blocked;
+};
+
+__device__ __forceinline__ void BulkWaitRead(uint32_t inflight)
+{
+    switch (inflight) {
+        case 1: asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.bulk.wait_group.read 4;" ::: "memory"); break;
+        case 6: asm volatile("cp.async.bulk.wait_group.read 6;" ::: "memory"); break;
+        default: asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); break;
+    }
+}
+
 __global__ void __launch_bounds__(128, 1)
-mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n)
+mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n, TmaShape shape)
 {
     extern __shared__ unsigned char tmaSmemRaw[];
     unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(tmaSmemRaw) + 127) & ~(uintptr_t)127);
-    __shared__ uint64_t full[kTmaStages], empty[kTmaStages];
+    __shared__ uint64_t full[kTmaMaxStages], empty[kTmaMaxStages];
+    const uint32_t kTmaTile = shape.tile, kTmaStages = shape.stages, kTmaStoresInFlight = shape.inflight;
     // Unaligned head (up to the first 16-byte boundary of dst) and tail bytes go through ordinary loads/stores.
     const size_t head = n < 16 ? n : ((16 - ((uintptr_t)dst & 15)) & 15);
     const size_t body = (n - head) & ~(size_t)15;
@@ -98,7 +124,7 @@ mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__rest
         }
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kTmaStages; i++) {
+        for (uint32_t i = 0; i < kTmaStages; i++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(SmemU32(&full[i])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(SmemU32(&empty[i])));
         }
@@ -108,9 +134,14 @@ mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__rest
     const size_t ntiles = (body + kTmaTile - 1) / kTmaTile;
     const unsigned char *s0 = src + head;
     unsigned char *d0 = dst + head;
+    // Strided walk: tile t belongs to CTA t % grid. Blocked walk: CTA b owns tiles [b*per, (b+1)*per).
+    const size_t per = (ntiles + gridDim.x - 1) / gridDim.x;
+    const size_t tBegin = shape.blocked ? (size_t)blockIdx.x * per : blockIdx.x;
+    const size_t tEnd = shape.blocked ? (tBegin + per < ntiles ? tBegin + per : ntiles) : ntiles;
+    const size_t tStep = shape.blocked ? 1 : gridDim.x;
     if (threadIdx.x == 0) {
         uint32_t it = 0;
-        for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
+        for (size_t t = tBegin; t < tEnd; t += tStep, it++) {
             const uint32_t st = it % kTmaStages, ph = (it / kTmaStages) & 1;
             if (!MbarWaitParity(&empty[st], ph ^ 1)) {
                 break;
@@ -125,7 +156,7 @@ mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__rest
         }
     } else if (threadIdx.x == 32) {
         uint32_t it = 0;
-        for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
+        for (size_t t = tBegin; t < tEnd; t += tStep, it++) {
             const uint32_t st = it % kTmaStages, ph = (it / kTmaStages) & 1;
             if (!MbarWaitParity(&full[st], ph)) {
                 break;
@@ -137,8 +168,8 @@ mf_xcopy_tma_kernel(unsigned char *__restrict__ dst, const unsigned char *__rest
                          : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             // All but the newest kTmaStoresInFlight stores have finished reading shared memory: hand that tile back.
-            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kTmaStoresInFlight) : "memory");
-            if (it >= (uint32_t)kTmaStoresInFlight) {
+            BulkWaitRead(kTmaStoresInFlight);
+            if (it >= kTmaStoresInFlight) {
                 const uint32_t done = (it - kTmaStoresInFlight) % kTmaStages;
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemU32(&empty[done])) : "memory");
             }
@@ -309,6 +340,45 @@ extern "C" int mf_k_memcpy_async(void *dst, const void *src, size_t n, mf_stream
     return (int)cudaMemcpyAsync(dst, src, n, cudaMemcpyDefault, (cudaStream_t)stream);
 }
 
+static bool ShapeValid(const TmaShape &sh)
+{
+    return sh.tile >= 1024 && sh.tile % 16 == 0 && sh.stages >= 2 && sh.stages <= kTmaMaxStages && (uint64_t)sh.tile * sh.stages <= 220u * 1024 &&
+           sh.inflight >= 1 && sh.inflight < sh.stages && (sh.inflight <= 4 || sh.inflight == 6) && sh.blocked <= 1;
+}
+
+static int LaunchTma(void *dst, const void *src, size_t n, const TmaShape &shape, int ctas, int sms, mf_stream_t stream)
+{
+    static size_t attrBytes = 0;
+    const size_t smem = (size_t)shape.stages * shape.tile + 128;
+    if (smem > attrBytes) {
+        if (cudaFuncSetAttribute(mf_xcopy_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return MF_K_LAUNCH_FAILED;
+        }
+        attrBytes = smem;
+    }
+    size_t tiles = (n + shape.tile - 1) / shape.tile;
+    size_t grid = ctas > 0 ? (size_t)ctas : (tiles < (size_t)sms ? tiles : (size_t)sms);
+    mf_xcopy_tma_kernel<<<(unsigned)grid, 128, smem, (cudaStream_t)stream>>>((unsigned char *)dst, (const unsigned char *)src, n, shape);
+    return LaunchResult();
+}
+
+// The bulk-copy kernel with an explicit pipeline shape, for tuning sweeps. Same preconditions as the automatic path: both
+// addresses congruent modulo 16. ctas 0 = one per SM.
+extern "C" int mf_k_xcopy_shaped(void *dst, const void *src, size_t n, uint32_t tile, uint32_t stages, uint32_t inflight, uint32_t blocked,
+                                 int ctas, mf_stream_t stream)
+{
+    const TmaShape shape{tile, stages, inflight, blocked};
+    if (dst == nullptr || src == nullptr || n == 0 || ctas < 0 || !ShapeValid(shape) || ((((uintptr_t)dst) ^ ((uintptr_t)src)) & 15) != 0) {
+        return MF_K_INVALID;
+    }
+    const int sms = SmCount();
+    if (sms <= 0) {
+        return MF_K_LAUNCH_FAILED;
+    }
+    return LaunchTma(dst, src, n, shape, ctas, sms, stream);
+}
+
 extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_stream_t stream)
 {
     if (n == 0) {
@@ -330,19 +400,20 @@ extern "C" int mf_k_xcopy(void *dst, const void *src, size_t n, int ctas, mf_str
         return !(e != nullptr && e[0] == '0');
     }();
     if (useTma && ctas >= 0 && n >= (4u << 20) && ((((uintptr_t)dst) ^ ((uintptr_t)src)) & 15) == 0) {
-        static bool attr = false;
-        const size_t smem = (size_t)kTmaStages * kTmaTile + 128;
-        if (!attr) {
-            if (cudaFuncSetAttribute(mf_xcopy_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-                (void)cudaGetLastError();
-                return MF_K_LAUNCH_FAILED;
+        // MF_XCOPY_SHAPE="tile,stages,inflight,blocked" overrides the pipeline shape (read once).
+        static const TmaShape shape = []() {
+            TmaShape sh{kTmaDefaultTile, kTmaDefaultStages, kTmaDefaultInFlight, 0};
+            const char *e = getenv("MF_XCOPY_SHAPE");
+            unsigned a = 0, b = 0, c = 0, d = 0;
+            if (e != nullptr && sscanf(e, "%u,%u,%u,%u", &a, &b, &c, &d) == 4) {
+                TmaShape cand{a, b, c, d};
+                if (ShapeValid(cand)) {
+                    sh = cand;
+                }
             }
-            attr = true;
-        }
-        size_t tiles = (n + kTmaTile - 1) / kTmaTile;
-        size_t grid = ctas > 0 ? (size_t)ctas : (tiles < (size_t)sms ? tiles : (size_t)sms);
-        mf_xcopy_tma_kernel<<<(unsigned)grid, 128, smem, (cudaStream_t)stream>>>((unsigned char *)dst, (const unsigned char *)src, n);
-        return LaunchResult();
+            return sh;
+        }();
+        return LaunchTma(dst, src, n, shape, ctas, sms, stream);
     }
     if (ctas < 0) {
         ctas = -ctas == 1 ? 0 : -ctas;  // negative: force the load/store kernel (with |ctas| CTAs, -1 = automatic)

@@ -111,4 +111,5 @@ PYBIND11_MODULE(_pymf, m)
     BindTrans(m);
     BindNative(m);
     BindOps(m);
+    BindTransport(m);
 }

@@ -452,6 +452,11 @@ void BindNative(py::module_ &m)
     n.def("xcopy", [](uint64_t dst, uint64_t src, uint64_t nbytes, int ctas, uint64_t stream) {
         return mf_k_xcopy((void *)dst, (const void *)src, nbytes, ctas, (mf_stream_t)stream);
     }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("ctas") = 0, py::arg("stream") = 0);
+    n.def("xcopy_shaped", [](uint64_t dst, uint64_t src, uint64_t nbytes, uint32_t tile, uint32_t stages, uint32_t inflight, uint32_t blocked,
+                             int ctas, uint64_t stream) {
+        return mf_k_xcopy_shaped((void *)dst, (const void *)src, nbytes, tile, stages, inflight, blocked, ctas, (mf_stream_t)stream);
+    }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("tile"), py::arg("stages"), py::arg("inflight"), py::arg("blocked") = 0,
+       py::arg("ctas") = 0, py::arg("stream") = 0);
     n.def("copy_engine", [](uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream) {
         return mf_k_memcpy_async((void *)dst, (const void *)src, nbytes, (mf_stream_t)stream);
     }, py::arg("dst"), py::arg("src"), py::arg("nbytes"), py::arg("stream") = 0);

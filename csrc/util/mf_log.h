@@ -81,6 +81,11 @@ inline uint64_t NowMs() { return NowNs() / 1000000ull; }
         if (::mf::Logger::Instance().Throttle()) { MF_ERROR(expr); } \
     } while (0)
 
+#define MF_WARN_LIMIT(expr)                                 \
+    do {                                                    \
+        if (::mf::Logger::Instance().Throttle()) { MF_WARN(expr); } \
+    } while (0)
+
 #define MF_CHECK_RET(cond, ret, expr) \
     do {                              \
         if (!(cond)) {                \

@@ -147,3 +147,36 @@ def test_enabling_tls_needs_options(mf, tls_off):
     assert mf.set_conf_store_tls(True, "") != 0
     assert mf.set_conf_store_tls(True, "tlsCaPath: /x/") != 0  # certificate and CA file missing
     assert mf.set_conf_store_tls(False, "") == 0
+
+
+def test_host_transport_over_tls(mf, certs):
+    """The one-sided host transport speaks TLS 1.3 with mutual authentication on its links when its options say so; a rank
+    whose certificate chains to another CA cannot link."""
+    import numpy as np
+
+    n = mf.native
+    n.set_retry_policy(2, 50, 2)
+    try:
+        ts, bufs = [], []
+        for r, (crt, ca) in enumerate((("node.crt", "ca.pem"), ("node.crt", "ca.pem"), ("stranger.crt", "otherca.pem"))):
+            t = n.Transport(n.TT_HOST_TCP)
+            key = f"{certs}/{crt.split('.')[0]}.plain.key"
+            assert t.open(r, 3, 0, "127.0.0.1:0", tls_info=_info(certs, crt, ca), tls_pk=key, op_timeout_ms=3000) == 0, mf.get_last_err_msg()
+            a = np.zeros(1 << 16, dtype=np.uint8)
+            assert t.register_region(a.ctypes.data, a.nbytes) == 0
+            ts.append(t)
+            bufs.append(a)
+        recs = {r: {"nic": ts[r].nic(), "role": 0, "keys": [ts[r].memory_key(bufs[r].ctypes.data)]} for r in range(3)}
+        assert ts[0].prepare({1: recs[1]}) == 0 and ts[0].connect() == 0
+        src = np.random.default_rng(0).integers(0, 256, 4096, dtype=np.uint8)
+        assert ts[0].write(1, src.ctypes.data, bufs[1].ctypes.data, 4096) == 0
+        assert np.array_equal(bufs[1][:4096], src)
+        # the stranger trusts only its own CA and presents a certificate ours does not trust: no link, no bytes
+        assert ts[2].prepare({1: recs[1]}) == 0
+        assert ts[2].connect() != 0 and not ts[2].linked(1)
+        assert ts[2].write(1, src.ctypes.data, bufs[1].ctypes.data + 8192, 4096) != 0
+        assert int(bufs[1][8192:8192 + 4096].sum()) == 0
+        for t in ts:
+            t.close()
+    finally:
+        n.set_retry_policy(3, 1000, 2)
