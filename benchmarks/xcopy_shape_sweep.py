@@ -64,6 +64,8 @@ def main():
         if inflight >= stages or smem > 220 << 10 or (per_sm == 2 and smem > 110 << 10):
             continue
         dst.zero_()
+        if args.peer:
+            torch.cuda.synchronize(1)  # the clearing ran on the other GPU's stream: it must be over before the copy starts
         rc = mf.native.xcopy_shaped(dst.data_ptr(), src.data_ptr(), n, tile, stages, inflight, blocked, sms * per_sm, s)
         torch.cuda.synchronize()
         if rc != 0 or not same():
@@ -75,7 +77,7 @@ def main():
     good = sorted((r for r in rows if "us" in r), key=lambda r: r["us"])
     out = {"bytes": n, "peer": args.peer, "copy_engine_us": round(ce_us, 2), "copy_engine_GBps": round(n / ce_us / 1e3, 1),
            "default_shape_us": round(base_us, 2), "default_shape_GBps": round(n / base_us / 1e3, 1), "best": good[:12],
-           "worst": good[-3:], "errors": [r for r in rows if "error" in r], "shapes_tried": len(rows)}
+           "worst": good[-3:], "all": good, "errors": [r for r in rows if "error" in r], "shapes_tried": len(rows)}
     text = json.dumps(out, indent=1)
     print(text)
     if args.out:

@@ -468,6 +468,7 @@ std::shared_ptr<DataOperator> MakeCpuDataOp() { return std::make_shared<CpuDataO
 namespace {
 std::atomic<uint64_t> g_served[6];
 std::atomic<uint64_t> g_batchGroupsLast{0};
+std::atomic<uint64_t> g_remote[2];
 
 void NoteServed(uint32_t type, uint64_t elems)
 {
@@ -487,10 +488,18 @@ DataOpStats GetDataOpStats()
     s.cpuCalls = g_served[4].load();
     s.cpuElems = g_served[5].load();
     s.batchGroupsLast = g_batchGroupsLast.load();
+    s.remoteCalls = g_remote[0].load();
+    s.remoteElems = g_remote[1].load();
     return s;
 }
 
 void NoteBatchGroups(uint32_t groups) { g_batchGroupsLast.store(groups, std::memory_order_relaxed); }
+
+void NoteRemoteCopy(uint64_t elems)
+{
+    g_remote[0].fetch_add(1, std::memory_order_relaxed);
+    g_remote[1].fetch_add(elems, std::memory_order_relaxed);
+}
 
 ComposeDataOp::ComposeDataOp(int device, uint32_t allowedOps, std::shared_ptr<TagInfo> tags)
     : device_(device), allowed_(allowedOps), tags_(std::move(tags))

@@ -29,6 +29,8 @@ struct ExtOptions {
     uint32_t flags{0};
     bool srcDeviceVisible{true};  // false: the source is pageable host memory a kernel cannot read
     bool dstDeviceVisible{true};
+    bool srcRemote{false};  // the source is pool memory of a rank on another host (not mapped here)
+    bool dstRemote{false};
 };
 
 class DataOperator {
@@ -59,10 +61,11 @@ class TagInfo;
 // Process-wide counters of which engine served how many calls and elements (observability, and the seam tests use to check
 // that an address a kernel cannot read never reached the kernel engine).
 struct DataOpStats {
-    uint64_t kernelCalls, kernelElems, copyEngineCalls, copyEngineElems, cpuCalls, cpuElems, batchGroupsLast;
+    uint64_t kernelCalls, kernelElems, copyEngineCalls, copyEngineElems, cpuCalls, cpuElems, batchGroupsLast, remoteCalls, remoteElems;
 };
 DataOpStats GetDataOpStats();
 void NoteBatchGroups(uint32_t groups);
+void NoteRemoteCopy(uint64_t elems);  // copies carried by the host transport (pool memory on another host)
 
 class ComposeDataOp : public DataOperator {
 public:

@@ -1,5 +1,6 @@
 #include "mf_entity.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <pthread.h>
 #include <unistd.h>
@@ -96,6 +97,12 @@ MemEntity::~MemEntity()
     if (devCtx_ != nullptr) {
         cudaFree(devCtx_);
     }
+    if (tp_) {
+        tp_->Host()->CloseDevice();
+    }
+    if (bounce_ != nullptr) {
+        cudaFreeHost(bounce_);
+    }
     VaManager::Instance().RemoveEntity(id_);
 }
 
@@ -109,6 +116,22 @@ int MemEntity::Initialize()
     int rc = tags_->Init(opt_.rankId, opt_.tag, opt_.tagOpInfo);
     if (rc != BM_OK) {
         return rc;
+    }
+    // Link table. Mapping and copying are done by this entity's own import / copy paths, so the device transport gets no
+    // hooks: it is the record of what those paths did.
+    devTp_ = std::make_shared<transport::DevicePeerTransport>();
+    transport::Options to;
+    to.rankId = opt_.rankId;
+    to.rankCount = opt_.rankCount;
+    to.role = opt_.role;
+    devTp_->OpenDevice(to);
+    devTp_->Links().SetSelf(opt_.rankId, opt_.role, HostIdentity());
+    const char *cross = getenv("MF_CROSS_HOST");
+    if ((opt_.flags & FLAG_CROSS_HOST) != 0 || (cross != nullptr && cross[0] == '1')) {
+        rc = OpenCrossHost();
+        if (rc != BM_OK) {
+            return rc;
+        }
     }
     SegmentOptions so;
     so.entityId = id_;
@@ -156,6 +179,183 @@ int MemEntity::Initialize()
         rc = UpdateDeviceMeta();
     }
     return rc;
+}
+
+int MemEntity::OpenCrossHost()
+{
+    auto host = std::make_shared<transport::HostTcpTransport>();
+    transport::Options to;
+    to.rankId = opt_.rankId;
+    to.rankCount = opt_.rankCount;
+    to.role = opt_.role;
+    // Address peers on other hosts use to reach this rank: MF_HOST_NIC ("ip" or "ip:port"), else the first non-loopback
+    // IPv4 address of the host, else loopback. Port 0 = any free port.
+    std::string nic;
+    const char *env = getenv("MF_HOST_NIC");
+    if (env != nullptr && env[0] != '\0') {
+        nic = env;
+        if (nic.find(':') == std::string::npos) {
+            nic += ":0";
+        }
+    } else {
+        auto ips = net::LocalIpv4List();
+        nic = (ips.empty() ? std::string("127.0.0.1") : ips[0]) + ":0";
+    }
+    to.nic = nic;
+    to.tls = net::GetStoreTlsOptions();  // the data links between hosts use the PKI configured for the control plane
+    int rc = host->OpenDevice(to);
+    MF_CHECK_RET(rc == BM_OK, rc, "entity: cannot open the host transport on " << nic);
+    if (opt_.devId >= 0 && cu::Available()) {
+        const int dev = opt_.devId;
+        host->SetDeviceCopier([dev](void *dst, const void *src, size_t n) {
+            if (cudaSetDevice(dev) != cudaSuccess || cudaMemcpy(dst, src, n, cudaMemcpyDefault) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return -1;
+            }
+            return 0;
+        });
+    }
+    tp_ = std::make_shared<transport::ComposeTransport>(devTp_, host);
+    tp_->SetSelf(opt_.rankId);
+    MF_INFO("entity " << id_ << ": cross-host mode, pool memory served at " << host->GetNic());
+    return BM_OK;
+}
+
+// Registers the exported slice with the host transport and writes its address and key into the export blob.
+int MemEntity::ServeSlice(std::string *blob)
+{
+    SliceExport e;
+    if (!tp_ || blob->size() != sizeof(e)) {
+        return BM_OK;
+    }
+    std::memcpy(&e, blob->data(), sizeof(e));
+    if (e.segType == SEG_USER_MEM || e.size == 0) {
+        return BM_OK;  // registered user memory has owner-local addresses: not served across hosts
+    }
+    auto host = tp_->Host();
+    if (!host->QueryHasRegistered(e.gva, e.size)) {
+        transport::MemoryRegion mr;
+        mr.addr = e.gva;
+        mr.size = e.size;
+        mr.flags = e.memType == MEM_TYPE_DEVICE ? transport::MR_FLAG_HBM : transport::MR_FLAG_DRAM;
+        int rc = host->RegisterMemoryRegion(mr);
+        MF_CHECK_RET(rc == BM_OK, rc, "entity: cannot serve slice 0x" << std::hex << e.gva << std::dec << " over the host transport");
+    }
+    transport::MemoryKey k;
+    MF_CHECK_RET(host->QueryMemoryKey(e.gva, &k) == BM_OK, BM_ERROR, "entity: no key for a slice just registered");
+    std::memset(e.tpNic, 0, sizeof(e.tpNic));
+    std::strncpy(e.tpNic, host->GetNic().c_str(), sizeof(e.tpNic) - 1);
+    e.tpToken = k.token;
+    e.tpAccess = k.access;
+    e.tpFlags = k.flags;
+    blob->assign((const char *)&e, sizeof(e));
+    return BM_OK;
+}
+
+int MemEntity::ImportRemoteSlice(const SliceExport &e)
+{
+    MF_CHECK_RET(tp_ != nullptr, BM_NOT_SUPPORTED,
+                 "entity: rank " << e.rank << " is on another host; cross-host mode (MF_CROSS_HOST=1) is off on this rank");
+    MF_CHECK_RET(e.tpNic[0] != '\0' && e.tpToken != 0, BM_NOT_SUPPORTED,
+                 "entity: rank " << e.rank << " is on another host and does not serve its memory (cross-host mode is off there)");
+    MF_CHECK_RET(e.segType == SEG_DEVICE_VMM || e.segType == SEG_HOST_SHM, BM_NOT_SUPPORTED, "entity: only pooled memory is reachable across hosts");
+    auto seg = e.segType == SEG_DEVICE_VMM ? hbm_ : dram_;
+    MF_CHECK_RET(seg != nullptr && seg->InWindow(e.gva, e.size) && seg->RankOf(e.gva) == e.rank, BM_INVALID_PARAM,
+                 "entity: slice of rank " << e.rank << " does not lie in that rank's window here (the ranks reserved different windows)");
+    std::lock_guard<std::mutex> g(remoteMu_);
+    for (const auto &r : remoteSlices_) {
+        if (r.gva == e.gva) {
+            return BM_OK;  // idempotent
+        }
+    }
+    AllocatedRange a;
+    a.gva = e.gva;
+    a.size = e.size;
+    a.memType = e.memType;
+    a.ownerRank = e.rank;
+    a.entityId = id_;
+    a.imported = true;
+    a.remote = true;
+    VaManager::Instance().AddAllocated(a);
+    remoteSlices_.push_back(RemoteSlice{e.rank, e.gva, e.size});
+    transport::RankInfo &info = pendingRanks_.ranks[e.rank];
+    char nic[sizeof(e.tpNic) + 1] = {0};
+    std::memcpy(nic, e.tpNic, sizeof(e.tpNic));
+    info.nic = nic;
+    info.sameHost = false;
+    transport::MemoryKey k;
+    k.token = e.tpToken;
+    k.addr = e.gva;
+    k.size = e.size;
+    k.access = e.tpAccess;
+    k.flags = e.tpFlags;
+    info.keys.push_back(k);
+    devTp_->Links().NoteSlice(e.rank, e.size, true);
+    return BM_OK;
+}
+
+bool MemEntity::IsDeviceAddress(uint64_t addr)
+{
+    bool vis = false;
+    PtrClass pc = Classify(addr, &vis);
+    return pc == PC_GLOBAL_DEVICE || pc == PC_LOCAL_DEVICE;
+}
+
+// A copy whose pool side lives on another host: carried by the host transport. A host-side local goes straight over the
+// wire; a device-side local is staged through a pinned bounce buffer; remote-to-remote is staged through it twice.
+int MemEntity::RemoteCopy(uint64_t src, uint64_t dst, uint64_t size, const ExtOptions &opt)
+{
+    MF_CHECK_RET(tp_ != nullptr, BM_NOT_SUPPORTED, "copy: pool memory on another host needs cross-host mode");
+    constexpr uint64_t kBounce = 8ull << 20;
+    auto host = tp_->Host();
+    NoteRemoteCopy(1);
+    const bool srcDev = !opt.srcRemote && IsDeviceAddress(src), dstDev = !opt.dstRemote && IsDeviceAddress(dst);
+    if (!(opt.srcRemote && opt.dstRemote) && !srcDev && !dstDev) {
+        return opt.dstRemote ? host->WriteRemote(opt.dstRank, src, dst, size) : host->ReadRemote(opt.srcRank, dst, src, size);
+    }
+    std::lock_guard<std::mutex> g(bounceMu_);
+    const bool cuda = opt_.devId >= 0 && cu::Available();
+    if (bounce_ == nullptr) {
+        if (cuda) {
+            MF_CUDA_CHECK_RET(cudaMallocHost(&bounce_, kBounce), BM_MALLOC_FAILED);
+        } else {
+            bounce_ = nullptr;
+        }
+    }
+    std::vector<char> plain;
+    char *stage = (char *)bounce_;
+    if (stage == nullptr) {
+        plain.resize(kBounce);
+        stage = plain.data();
+    }
+    if ((srcDev || dstDev) && opt.stream != nullptr) {
+        MF_CUDA_CHECK_RET(cudaStreamSynchronize((cudaStream_t)opt.stream), BM_ERROR);  // what the stream wrote is what we read
+    }
+    for (uint64_t off = 0; off < size; off += kBounce) {
+        const uint64_t n = std::min(kBounce, size - off);
+        int rc = BM_OK;
+        if (opt.srcRemote) {
+            rc = host->ReadRemote(opt.srcRank, (uint64_t)stage, src + off, n);
+        } else if (srcDev) {
+            MF_CUDA_CHECK_RET(cudaMemcpy(stage, (const void *)(src + off), n, cudaMemcpyDefault), BM_ERROR);
+        } else {
+            std::memcpy(stage, (const void *)(src + off), n);
+        }
+        if (rc != BM_OK) {
+            return rc;
+        }
+        if (opt.dstRemote) {
+            rc = host->WriteRemote(opt.dstRank, (uint64_t)stage, dst + off, n);
+        } else if (dstDev) {
+            MF_CUDA_CHECK_RET(cudaMemcpy((void *)(dst + off), stage, n, cudaMemcpyDefault), BM_ERROR);
+        } else {
+            std::memcpy((void *)(dst + off), stage, n);
+        }
+        if (rc != BM_OK) {
+            return rc;
+        }
+    }
+    return BM_OK;
 }
 
 int MemEntity::UpdateDeviceMeta()
@@ -290,6 +490,9 @@ int MemEntity::FreeLocalMemory(uint64_t sliceHandle)
     MemSlice s;
     auto seg = SegmentOfSlice(sliceHandle, &s);
     MF_CHECK_RET(seg != nullptr, BM_INVALID_PARAM, "entity: invalid slice handle");
+    if (tp_ && tp_->Host()->QueryHasRegistered(s.vAddress, 1)) {
+        tp_->Host()->UnregisterMemoryRegion(s.vAddress);  // waits for requests that are touching the slice right now
+    }
     return seg->ReleaseSlice(s);
 }
 
@@ -333,27 +536,19 @@ int MemEntity::Export(uint64_t sliceHandle, uint32_t flags, ExchangeInfo *out)
     if (rc != BM_OK) {
         return rc;
     }
+    rc = ServeSlice(&blob);
+    if (rc != BM_OK) {
+        return rc;
+    }
     MF_CHECK_RET(blob.size() <= EXCHANGE_DESC_MAX, BM_ERROR, "entity: export blob too large");
     std::memcpy(out->desc, blob.data(), blob.size());
     out->descLen = (uint32_t)blob.size();
     return BM_OK;
 }
 
-void MemEntity::SetPeerRole(uint32_t rank, Role role)
-{
-    std::lock_guard<std::mutex> g(roleMu_);
-    peerRoles_[rank] = role;
-}
+void MemEntity::SetPeerRole(uint32_t rank, Role role) { devTp_->Links().NoteIdentity(rank, role, ""); }
 
-bool MemEntity::RolePermits(uint32_t rank)
-{
-    if (opt_.role == ROLE_PEER) {
-        return true;
-    }
-    std::lock_guard<std::mutex> g(roleMu_);
-    auto it = peerRoles_.find(rank);
-    return it == peerRoles_.end() || it->second == ROLE_PEER || it->second != opt_.role;
-}
+bool MemEntity::RolePermits(uint32_t rank) { return devTp_->Links().Permits(rank); }
 
 int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresses, uint32_t /*flags*/)
 {
@@ -372,7 +567,8 @@ int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresse
             if (rc != BM_OK) {
                 return rc;
             }
-            SetPeerRole(e.rank, (Role)e.role);
+            e.hostId[sizeof(e.hostId) - 1] = '\0';
+            devTp_->Links().NoteIdentity(e.rank, (Role)e.role, e.hostId);
             if (addresses != nullptr) {
                 addresses[i] = nullptr;
             }
@@ -385,6 +581,18 @@ int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresse
             MF_INFO("entity: rank " << e.rank << " has the same one-sided role as this rank; its memory is not mapped");
             if (addresses != nullptr) {
                 addresses[i] = nullptr;
+            }
+            continue;
+        }
+        e.hostId[sizeof(e.hostId) - 1] = '\0';
+        if (e.rank != opt_.rankId && e.size != 0 && HostIdentity() != e.hostId) {
+            // Another host: nothing to map. The slice is recorded and reached through the host transport.
+            int rrc = ImportRemoteSlice(e);
+            if (rrc != BM_OK) {
+                return rrc;
+            }
+            if (addresses != nullptr) {
+                addresses[i] = (void *)e.gva;
             }
             continue;
         }
@@ -415,6 +623,9 @@ int MemEntity::Import(const ExchangeInfo *infos, uint32_t count, void **addresse
         if (rc != BM_OK) {
             return rc;
         }
+        if (e.rank != opt_.rankId) {
+            devTp_->Links().NoteSlice(e.rank, e.size, false);
+        }
         if (addresses != nullptr) {
             addresses[i] = local.empty() ? nullptr : (void *)local[0];
         }
@@ -431,6 +642,26 @@ int MemEntity::Mmap()
             if (rc != BM_OK) {
                 return rc;
             }
+        }
+    }
+    devTp_->Links().NoteMapped();
+    if (tp_) {
+        // "Mapping" a rank on another host is opening the link to it (under the retry policy).
+        transport::PrepareOptions fresh;
+        {
+            std::lock_guard<std::mutex> g(remoteMu_);
+            fresh.ranks.swap(pendingRanks_.ranks);
+        }
+        if (!fresh.ranks.empty()) {
+            for (auto &kv : fresh.ranks) {
+                for (const auto &l : devTp_->Links().Snapshot()) {
+                    if (l.rank == kv.first) {
+                        kv.second.role = l.role;
+                    }
+                }
+            }
+            int rc = tp_->Host()->UpdateRankOptions(fresh);
+            MF_CHECK_RET(rc == BM_OK, rc, "entity: cannot link to the ranks on other hosts");
         }
     }
     return BM_OK;
@@ -455,6 +686,22 @@ int MemEntity::RemoveImported(uint32_t rank)
             seg->RemoveImported({rank});
         }
     }
+    {
+        std::lock_guard<std::mutex> g(remoteMu_);
+        for (auto it = remoteSlices_.begin(); it != remoteSlices_.end();) {
+            if (it->rank == rank) {
+                VaManager::Instance().RemoveAllocated(it->gva);
+                it = remoteSlices_.erase(it);
+            } else {
+                ++it;
+            }
+        }
+        pendingRanks_.ranks.erase(rank);
+    }
+    if (tp_) {
+        tp_->Host()->RemoveRanks({rank});
+    }
+    devTp_->Links().NoteRemoved(rank);
     tags_->RemoveRankTag(rank);
     return BM_OK;
 }
@@ -578,6 +825,9 @@ int MemEntity::ResolveDirection(uint64_t src, uint64_t dst, CopyDirection *dir, 
     opt->dstRank = dr == RANK_MAX ? opt_.rankId : dr;
     opt->srcDeviceVisible = sv;
     opt->dstDeviceVisible = dv;
+    AllocatedRange ar;
+    opt->srcRemote = sr != RANK_MAX && sr != opt_.rankId && VaManager::Instance().FindAllocated(src, 1, &ar) && ar.remote;
+    opt->dstRemote = dr != RANK_MAX && dr != opt_.rankId && VaManager::Instance().FindAllocated(dst, 1, &ar) && ar.remote;
     return BM_OK;
 }
 
@@ -604,6 +854,9 @@ int MemEntity::CopyData(const CopyParams &p, CopyDirection dir, void *stream, ui
         MF_CHECK_RET(AddressInEntity((uint64_t)p.dest, p.dataSize), BM_INVALID_PARAM,
                      "copy: " << p.dataSize << " bytes to " << VaManager::Instance().VaToInfo((uint64_t)p.dest) << " leave the pool");
     }
+    if (opt.srcRemote || opt.dstRemote) {
+        return RemoteCopy((uint64_t)p.src, (uint64_t)p.dest, p.dataSize, opt);
+    }
     return dataOp_->DataCopy(p, dir, opt);
 }
 
@@ -627,7 +880,7 @@ int MemEntity::BatchCopyData(const BatchCopyParams &p, CopyDirection dir, void *
     std::vector<Group> groups;
     auto sameGroup = [](const Group &g, CopyDirection d, const ExtOptions &o) {
         return g.dir == d && g.opt.srcRank == o.srcRank && g.opt.dstRank == o.dstRank && g.opt.srcDeviceVisible == o.srcDeviceVisible &&
-               g.opt.dstDeviceVisible == o.dstDeviceVisible;
+               g.opt.dstDeviceVisible == o.dstDeviceVisible && g.opt.srcRemote == o.srcRemote && g.opt.dstRemote == o.dstRemote;
     };
     size_t last = 0;
     for (uint32_t i = 0; i < p.batchSize; i++) {
@@ -663,10 +916,46 @@ int MemEntity::BatchCopyData(const BatchCopyParams &p, CopyDirection dir, void *
         groups[last].idx.push_back(i);
     }
     NoteBatchGroups((uint32_t)groups.size());
-    if (groups.size() == 1) {
+    if (groups.size() == 1 && !groups[0].opt.srcRemote && !groups[0].opt.dstRemote) {
         return dataOp_->BatchDataCopy(p, groups[0].dir, groups[0].opt);  // the common case: the caller's arrays as they are
     }
     for (const Group &g : groups) {
+        if (g.opt.srcRemote || g.opt.dstRemote) {
+            // Host-side locals of one remote rank go out as one asynchronous batch and are waited for together; anything that
+            // needs staging goes element by element.
+            auto host = tp_ ? tp_->Host() : nullptr;
+            MF_CHECK_RET(host != nullptr, BM_NOT_SUPPORTED, "batch copy: pool memory on another host needs cross-host mode");
+            const bool oneSided = !(g.opt.srcRemote && g.opt.dstRemote);
+            const uint32_t rank = g.opt.dstRemote ? g.opt.dstRank : g.opt.srcRank;
+            bool queued = false;
+            uint64_t queuedElems = 0;
+            for (uint32_t i : g.idx) {
+                const uint64_t src = (uint64_t)p.sources[i], dst = (uint64_t)p.destinations[i];
+                const uint64_t local = g.opt.dstRemote ? src : dst;
+                int rc;
+                if (oneSided && !IsDeviceAddress(local)) {
+                    rc = g.opt.dstRemote ? host->WriteRemoteAsync(rank, src, dst, p.dataSizes[i]) : host->ReadRemoteAsync(rank, dst, src, p.dataSizes[i]);
+                    queued = true;
+                    queuedElems++;
+                } else {
+                    rc = RemoteCopy(src, dst, p.dataSizes[i], g.opt);
+                }
+                if (rc != BM_OK) {
+                    if (queued) {
+                        host->Synchronize(rank);
+                    }
+                    return rc;
+                }
+            }
+            if (queued) {
+                NoteRemoteCopy(queuedElems);
+                int rc = host->Synchronize(rank);
+                if (rc != BM_OK) {
+                    return rc;
+                }
+            }
+            continue;
+        }
         std::vector<void *> srcs(g.idx.size()), dsts(g.idx.size());
         std::vector<uint64_t> sizes(g.idx.size());
         for (size_t k = 0; k < g.idx.size(); k++) {

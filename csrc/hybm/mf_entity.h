@@ -14,6 +14,7 @@
 #include "mf_hybm_types.h"
 #include "mf_segment.h"
 #include "mf_tag_info.h"
+#include "../transport/mf_compose_transport.h"
 
 namespace mf {
 namespace hybm {
@@ -47,6 +48,11 @@ public:
     // never mapped (reference: the sender/receiver-only connections of transport/device/bipartite_ranks_qp_manager.cpp).
     void SetPeerRole(uint32_t rank, Role role);
     bool RolePermits(uint32_t rank);
+    // The per-peer link table (role, host, state, slices) kept by the device transport of this entity.
+    transport::PeerLinkManager &Links() { return devTp_->Links(); }
+    // Cross-host mode only (FLAG_CROSS_HOST / MF_CROSS_HOST=1): the router over the device links and the TCP host transport
+    // that serves this rank's pool memory to ranks on other hosts and reaches theirs. nullptr otherwise.
+    std::shared_ptr<transport::ComposeTransport> Transport() const { return tp_; }
     int SetExtraContext(const void *ctx, uint32_t size);
     // Bit mask of DataOpType usable towards `rank`.
     uint32_t ReachTypes(uint32_t rank);
@@ -95,8 +101,24 @@ private:
     // Copies hold this shared; unmapping a peer takes it exclusively, so a range is never pulled from under a copy.
     std::shared_mutex mapMu_;
     bool reserved_{false};
-    std::mutex roleMu_;
-    std::map<uint32_t, Role> peerRoles_;
+    // Pool memory of ranks on other hosts: known (so that addresses classify and bounds-check) but never mapped.
+    struct RemoteSlice {
+        uint32_t rank;
+        uint64_t gva;
+        uint64_t size;
+    };
+    int OpenCrossHost();
+    int ServeSlice(std::string *blob);
+    int ImportRemoteSlice(const SliceExport &e);
+    int RemoteCopy(uint64_t src, uint64_t dst, uint64_t size, const ExtOptions &opt);
+    bool IsDeviceAddress(uint64_t addr);
+    std::shared_ptr<transport::DevicePeerTransport> devTp_;
+    std::shared_ptr<transport::ComposeTransport> tp_;
+    std::mutex remoteMu_;
+    std::vector<RemoteSlice> remoteSlices_;
+    transport::PrepareOptions pendingRanks_;  // records learned by Import, handed to the transport by Mmap
+    std::mutex bounceMu_;
+    void *bounce_{nullptr};  // pinned staging buffer for device-side locals of cross-host copies
 };
 
 class EntityFactory {

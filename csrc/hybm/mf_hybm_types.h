@@ -95,11 +95,14 @@ inline PtrClass DstClassOf(CopyDirection d)
 constexpr uint32_t FLAG_ASYNC_COPY = 1u << 0;
 constexpr uint32_t FLAG_COPY_KERNEL = 1u << 1;  // reference: COPY_EXTEND_FLAG — force the kernel engine
 
-// Create flags: bits 0-6 NUMA node (0x7F = follow the GPU's affinity), bit 7 performance mode, bit 8 user shm fd.
+// Create flags: bits 0-6 NUMA node (0x7F = follow the GPU's affinity), bit 7 performance mode, bit 8 user shm fd, bit 9 cross-host.
 constexpr uint32_t FLAG_NUMA_MASK = 0x7F;
 constexpr uint32_t FLAG_NUMA_AUTO = 0x7F;
 constexpr uint32_t FLAG_PERFORMANCE_MODE = 1u << 7;
 constexpr uint32_t FLAG_CREATE_WITH_SHM = 1u << 8;
+// bit 9: also serve this rank's pool memory to ranks on OTHER hosts over the TCP host transport, and reach theirs the same way
+// (the environment variable MF_CROSS_HOST=1 sets it for every entity of the process).
+constexpr uint32_t FLAG_CROSS_HOST = 1u << 9;
 constexpr uint64_t INIT_FLAG_DEVICE_META = 1ull << 63;
 constexpr uint32_t FLAG_EXPORT_ENTITY = 1u << 0;
 

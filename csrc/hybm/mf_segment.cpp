@@ -32,6 +32,10 @@ static uint64_t AlignUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 std::string HostIdentity()
 {
     static std::string id = []() {
+        const char *forced = getenv("MF_HOST_IDENTITY");
+        if (forced != nullptr && forced[0] != '\0') {
+            return std::string(forced).substr(0, 39);
+        }
         std::ifstream f("/proc/sys/kernel/random/boot_id");
         std::string s;
         if (f && std::getline(f, s) && !s.empty()) {

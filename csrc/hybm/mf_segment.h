@@ -50,6 +50,12 @@ struct SliceExport {
     char fdName[48];
     char hostId[40];      // boot id: peers on another host cannot map and must not try
     uint8_t ipcHandle[64];
+    // Filled by the entity when it serves its memory over the host transport (cross-host mode): where to ask and the
+    // key of the region. Empty nic = not served over the wire.
+    char tpNic[64];
+    uint64_t tpToken;
+    uint32_t tpAccess;
+    uint32_t tpFlags;
 };
 struct EntityExport {
     uint32_t magic;
@@ -64,7 +70,7 @@ struct EntityExport {
 #pragma pack(pop)
 static_assert(sizeof(SliceExport) <= EXCHANGE_DESC_MAX, "slice export fits the exchange blob");
 
-std::string HostIdentity();  // kernel boot id (falls back to the host name)
+std::string HostIdentity();  // kernel boot id (falls back to the host name); MF_HOST_IDENTITY overrides it (tests emulate several hosts)
 
 struct SegmentOptions {
     SegmentType type{SEG_HOST_SHM};

@@ -31,6 +31,7 @@ struct AllocatedRange {
     uint32_t entityId{0};
     bool imported{false};  // true: owned by a peer and mapped here
     bool registered{false};  // true: user memory registered into the pool
+    bool remote{false};      // true: owned by a rank on another host; known here but NOT mapped, reached through the host transport
 };
 
 class VaManager {

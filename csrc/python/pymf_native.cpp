@@ -447,6 +447,8 @@ void BindNative(py::module_ &m)
         d["cpu_calls"] = st.cpuCalls;
         d["cpu_elems"] = st.cpuElems;
         d["batch_groups_last"] = st.batchGroupsLast;
+        d["remote_calls"] = st.remoteCalls;
+        d["remote_elems"] = st.remoteElems;
         return d;
     });
     n.def("xcopy", [](uint64_t dst, uint64_t src, uint64_t nbytes, int ctas, uint64_t stream) {

@@ -42,12 +42,26 @@ int ComposeTransport::RegisterMemoryRegion(const MemoryRegion &mr)
         MF_ERROR("compose transport: a region must say whether it is device or host memory");
         return BM_INVALID_PARAM;
     }
-    return (mr.flags & MR_FLAG_HBM) ? device_->RegisterMemoryRegion(mr) : host_->RegisterMemoryRegion(mr);
+    if ((mr.flags & MR_FLAG_HBM) == 0) {
+        return host_->RegisterMemoryRegion(mr);
+    }
+    int rc = device_->RegisterMemoryRegion(mr);
+    if (rc == BM_OK && serveDeviceMemory_) {
+        // Ranks on other hosts reach this device memory through the host transport's staging copier.
+        rc = host_->RegisterMemoryRegion(mr);
+        if (rc != BM_OK) {
+            device_->UnregisterMemoryRegion(mr.addr);
+        }
+    }
+    return rc;
 }
 
 int ComposeTransport::UnregisterMemoryRegion(uint64_t addr)
 {
     if (device_->QueryHasRegistered(addr, 1)) {
+        if (host_->QueryHasRegistered(addr, 1)) {
+            host_->UnregisterMemoryRegion(addr);
+        }
         return device_->UnregisterMemoryRegion(addr);
     }
     return host_->UnregisterMemoryRegion(addr);
@@ -60,7 +74,8 @@ bool ComposeTransport::QueryHasRegistered(uint64_t addr, uint64_t size)
 
 int ComposeTransport::QueryMemoryKey(uint64_t addr, MemoryKey *key)
 {
-    return device_->QueryMemoryKey(addr, key) == BM_OK ? BM_OK : host_->QueryMemoryKey(addr, key);
+    // The host transport's key carries the token a request over the wire must present; device-only regions have none.
+    return host_->QueryMemoryKey(addr, key) == BM_OK ? BM_OK : device_->QueryMemoryKey(addr, key);
 }
 
 void ComposeTransport::Split(const PrepareOptions &in, PrepareOptions *device, PrepareOptions *host)
@@ -69,8 +84,11 @@ void ComposeTransport::Split(const PrepareOptions &in, PrepareOptions *device, P
         RankInfo d, h;
         d.nic = h.nic = kv.second.nic;
         d.role = h.role = kv.second.role;
+        d.sameHost = h.sameHost = kv.second.sameHost;
         for (const auto &k : kv.second.keys) {
-            ((k.flags & MR_FLAG_HBM) ? d : h).keys.push_back(k);
+            // Device memory of a rank on this host is reached through the mapping; everything else over the wire (the
+            // owner's host transport stages its device memory).
+            (((k.flags & MR_FLAG_HBM) && kv.second.sameHost) ? d : h).keys.push_back(k);
         }
         device->ranks[kv.first] = std::move(d);
         if (!kv.second.nic.empty()) {
@@ -152,7 +170,7 @@ TransportManager *ComposeTransport::Pick(uint32_t rankId, uint64_t remoteAddr, u
     }
     for (const auto &k : it->second.keys) {
         if (k.Covers(remoteAddr, size)) {
-            return (k.flags & MR_FLAG_HBM) ? (TransportManager *)device_.get() : (TransportManager *)host_.get();
+            return ((k.flags & MR_FLAG_HBM) && it->second.sameHost) ? (TransportManager *)device_.get() : (TransportManager *)host_.get();
         }
     }
     return nullptr;

@@ -39,6 +39,12 @@ public:
     int WriteRemoteAsync(uint32_t rankId, uint64_t localAddr, uint64_t remoteAddr, uint64_t size) override;
     int Synchronize(uint32_t rankId) override;
 
+    // Device regions are also registered with the host transport, whose copier stages them for ranks on other hosts.
+    // Needs HostTcpTransport::SetDeviceCopier on Host(). Call before registering regions.
+    void ServeDeviceMemoryOverTheWire(bool on) { serveDeviceMemory_ = on; }
+    // For an owner that opened the two children itself: tells the router which rank is the local one.
+    void SetSelf(uint32_t rankId) { self_ = rankId; }
+
     // Which child would carry an operation on this remote range: TT_DEVICE_PEER, TT_HOST_TCP, or TT_COMPOSE for "nobody".
     TransportType RouteOf(uint32_t rankId, uint64_t remoteAddr, uint64_t size);
 
@@ -50,6 +56,7 @@ private:
     util::RwLock mu_;
     std::unordered_map<uint32_t, RankInfo> ranks_;
     uint32_t self_{0};
+    bool serveDeviceMemory_{false};
 };
 
 }  // namespace transport

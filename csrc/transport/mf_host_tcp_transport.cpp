@@ -244,6 +244,19 @@ void HostTcpTransport::OnRequest(net::LinkId link, const net::Frame &f)
             stats_.refused.fetch_add(1);
             MF_WARN_LIMIT("host transport: refused a " << (write ? "write" : "read") << " of 0x" << std::hex << h.size << " at 0x" << h.addr
                                                           << std::dec << " (outside a region, wrong token or access not granted)");
+        } else if ((k->flags & MR_FLAG_HBM) != 0) {
+            // Device memory: staged through the frame's own buffer by the owner's copier.
+            if (!deviceCopier_) {
+                stats_.refused.fetch_add(1);
+            } else if (write) {
+                r.result = deviceCopier_((void *)h.addr, f.body.data() + sizeof(h), h.size) == 0 ? 0 : (int16_t)BM_ERROR;
+            } else {
+                r.body.resize(h.size);
+                r.result = deviceCopier_(&r.body[0], (const void *)h.addr, h.size) == 0 ? 0 : (int16_t)BM_ERROR;
+                if (r.result != 0) {
+                    r.body.clear();
+                }
+            }
         } else if (write) {
             std::memcpy((void *)h.addr, f.body.data() + sizeof(h), h.size);
             r.result = 0;
@@ -294,10 +307,25 @@ int HostTcpTransport::ApplyRanks(const PrepareOptions &opt, bool replaceAll)
             peers_[kv.first] = p;
             continue;
         }
-        // A known rank: new keys take effect at once; a new address makes the open link stale.
+        // A known rank: a key for an address already known replaces the old one (a restarted rank serves the same pool
+        // addresses under new tokens), other keys are added; a new address makes the open link stale.
         std::lock_guard<std::mutex> lg(it->second->linkMu);
         const bool moved = it->second->info.nic != kv.second.nic;
+        std::vector<MemoryKey> keys = it->second->info.keys;
+        for (const auto &k : kv.second.keys) {
+            bool replaced = false;
+            for (auto &old : keys) {
+                if (old.addr == k.addr) {
+                    old = k;
+                    replaced = true;
+                }
+            }
+            if (!replaced) {
+                keys.push_back(k);
+            }
+        }
         it->second->info = kv.second;
+        it->second->info.keys = std::move(keys);
         it->second->ep = ep;
         if (moved) {
             it->second->stale.store(true);
@@ -541,8 +569,15 @@ int HostTcpTransport::Submit(uint32_t rankId, bool write, uint64_t localAddr, ui
         return BM_INVALID_PARAM;
     }
     if (rankId == opt_.rankId) {  // own memory: no wire
-        if (!QueryHasRegistered(remoteAddr, size)) {
+        MemoryKey own;
+        if (!QueryHasRegistered(remoteAddr, size) || QueryMemoryKey(remoteAddr, &own) != BM_OK) {
             return BM_INVALID_PARAM;
+        }
+        if ((own.flags & MR_FLAG_HBM) != 0) {
+            if (!deviceCopier_) {
+                return BM_INVALID_PARAM;
+            }
+            return write ? deviceCopier_((void *)remoteAddr, (const void *)localAddr, size) : deviceCopier_((void *)localAddr, (const void *)remoteAddr, size);
         }
         if (write) {
             std::memcpy((void *)remoteAddr, (const void *)localAddr, size);

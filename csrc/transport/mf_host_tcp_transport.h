@@ -65,6 +65,10 @@ public:
     void SetBrokenHandler(std::function<void(uint32_t rank)> cb) { onBroken_ = std::move(cb); }
     // True if a link to the rank is currently open.
     bool Linked(uint32_t rankId);
+    // Regions flagged MR_FLAG_HBM are device memory: the serving thread cannot memcpy them, it calls this instead
+    // (dst, src, bytes) -> 0 on success; one side is the region, the other an ordinary host buffer. Without a copier such
+    // regions are refused.
+    void SetDeviceCopier(std::function<int(void *dst, const void *src, size_t n)> fn) { deviceCopier_ = std::move(fn); }
 
 private:
     struct Peer {
@@ -118,6 +122,7 @@ private:
 
     HostTcpStats stats_;
     std::function<void(uint32_t)> onBroken_;
+    std::function<int(void *, const void *, size_t)> deviceCopier_;
 };
 
 }  // namespace transport

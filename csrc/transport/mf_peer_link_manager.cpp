@@ -47,15 +47,16 @@ void PeerLinkManager::NoteIdentity(uint32_t rank, hybm::Role role, const std::st
     std::lock_guard<std::mutex> g(mu_);
     PeerLink &l = links_[rank];
     const bool fresh = l.state == LINK_NONE || l.state == LINK_REMOVED || l.state == LINK_STALE;
-    const bool changed = !fresh && (l.role != role || l.hostId != hostId);
+    const std::string host = hostId.empty() && !fresh ? l.hostId : hostId;  // a caller that only knows the role keeps the host
+    const bool changed = !fresh && (l.role != role || l.hostId != host);
     if (fresh || changed) {
         l.slices = l.remoteSlices = 0;
         l.bytes = 0;
     }
     l.rank = rank;
     l.role = role;
-    l.hostId = hostId;
-    l.sameHost = hostId.empty() || hostId == hostId_;
+    l.hostId = host;
+    l.sameHost = host.empty() || host == hostId_;
     if (!RolePermitsLink(role_, role)) {
         SetState(l, LINK_REFUSED);
     } else if (fresh || changed || l.state == LINK_REFUSED) {

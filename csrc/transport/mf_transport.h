@@ -67,6 +67,7 @@ static_assert(sizeof(MemoryKey) == 32, "memory key is 32 bytes on the wire");
 struct RankInfo {
     std::string nic;
     hybm::Role role{hybm::ROLE_PEER};
+    bool sameHost{true};  // false: the rank is outside this host's NVSwitch domain, so even its device memory goes over the wire
     std::vector<MemoryKey> keys;
 };
 
