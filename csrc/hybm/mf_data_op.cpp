@@ -533,6 +533,20 @@ static bool TouchesHost(CopyDirection d)
     return s == PC_LOCAL_HOST || s == PC_GLOBAL_HOST || t == PC_LOCAL_HOST || t == PC_GLOBAL_HOST;
 }
 
+static uint64_t PeerCopyEngineMin()
+{
+    static const uint64_t v = []() -> uint64_t {
+        const char *e = getenv("MF_PEER_COPY_ENGINE_MIN_MB");
+        if (e == nullptr || e[0] == '\0') {
+            return 0;
+        }
+        char *end = nullptr;
+        unsigned long long mb = std::strtoull(e, &end, 10);
+        return (end != nullptr && *end == '\0' && mb > 0 && mb < (1ull << 30)) ? mb << 20 : 0;
+    }();
+    return v;
+}
+
 std::vector<std::shared_ptr<DataOperator>> ComposeDataOp::Candidates(CopyDirection dir, const ExtOptions &opt, uint64_t bytes, bool batch) const
 {
     uint32_t mask = allowed_;
@@ -551,6 +565,10 @@ std::vector<std::shared_ptr<DataOperator>> ComposeDataOp::Candidates(CopyDirecti
         order = {OP_COPY_ENGINE, kCpuBits};
     } else if (TouchesHost(dir) && !batch && bytes >= kCopyEngineMin) {
         order = {OP_COPY_ENGINE, OP_KERNEL_LDST, kCpuBits};  // big host legs: DMA engines saturate PCIe without SMs
+    } else if (!batch && opt.srcRank != opt.dstRank && PeerCopyEngineMin() != 0 && bytes >= PeerCopyEngineMin()) {
+        // Opt-in (MF_PEER_COPY_ENGINE_MIN_MB): large single transfers between GPUs ride the copy engine, whose packets
+        // carry about a tenth more payload over NVLink than writes issued by SMs can; the SMs stay free for compute.
+        order = {OP_COPY_ENGINE, OP_KERNEL_LDST, kCpuBits};
     } else {
         order = {OP_KERNEL_LDST, OP_COPY_ENGINE, kCpuBits};
     }
