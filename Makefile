@@ -27,7 +27,7 @@ HOST_SRCS := $(wildcard csrc/util/*.cpp csrc/net/*.cpp csrc/transport/*.cpp csrc
 CUDA_SRCS := $(wildcard csrc/kernels/*.cu)
 HOST_OBJS := $(patsubst csrc/%.cpp,$(BUILD)/%.o,$(HOST_SRCS))
 CUDA_OBJS := $(patsubst csrc/%.cu,$(BUILD)/%.cu.o,$(CUDA_SRCS))
-TEST_SRCS := $(wildcard csrc/test/*.cpp)
+TEST_SRCS := csrc/test/main.cpp
 
 CORE      := $(OUTDIR)/libmf_core.so
 PYMOD     := memfabric_hybrid_b200/_pymf$(PY_EXT)
@@ -65,6 +65,12 @@ asan: $(CUDA_OBJS)
 	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -o $(BUILD)/asan/mf_native_tests_asan \
 	    $(TEST_SRCS) $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
 
+# Mutation fuzzer of the parsers, built with the sanitizers (csrc/test/run_fuzz.sh runs it).
+fuzz: $(CUDA_OBJS)
+	@mkdir -p $(BUILD)/asan
+	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -o $(BUILD)/asan/mf_fuzz \
+	    csrc/test/fuzz_main.cpp $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
+
 # Example programs and tools that are built against the installed headers and library.
 EXAMPLES := examples/bm_perf/bm_perf examples/bm_cpp/bm_example benchmarks/store_bench
 examples: $(EXAMPLES)
@@ -78,4 +84,4 @@ examples/bm_cpp/bm_example: examples/bm_cpp/main.cpp $(CORE)
 clean:
 	rm -rf $(BUILD) $(CORE) $(PYMOD) $(TESTBIN)
 
-.PHONY: all clean asan examples
+.PHONY: all clean asan fuzz examples
