@@ -45,7 +45,7 @@ $(BUILD)/%.cu.o: csrc/%.cu $(wildcard csrc/*/*.h csrc/kernels/*.cuh include/mf/*
 
 $(CORE): $(HOST_OBJS) $(CUDA_OBJS)
 	@mkdir -p $(OUTDIR)
-	$(CXX) -shared -o $@ $^ $(LDFLAGS)
+	$(CXX) -shared -o $@.tmp $^ $(LDFLAGS) && mv -f $@.tmp $@
 
 PY_SRCS   := $(wildcard csrc/python/*.cpp)
 PY_OBJS   := $(patsubst csrc/%.cpp,$(BUILD)/%.py.o,$(PY_SRCS))
@@ -54,10 +54,10 @@ $(BUILD)/%.py.o: csrc/%.cpp $(wildcard csrc/*/*.h include/mf/*.h)
 	$(CXX) $(CXXFLAGS) -fvisibility=hidden -I$(PY_INC) -I$(PYB_INC) -c $< -o $@
 
 $(PYMOD): $(PY_OBJS) $(CORE)
-	$(CXX) -shared -o $@ $(PY_OBJS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/lib' $(LDFLAGS)
+	$(CXX) -shared -o $@.tmp $(PY_OBJS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/lib' $(LDFLAGS) && mv -f $@.tmp $@
 
 $(TESTBIN): $(TEST_SRCS) $(CORE)
-	$(CXX) $(CXXFLAGS) -o $@ $(TEST_SRCS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' $(LDFLAGS)
+	$(CXX) $(CXXFLAGS) -o $@.tmp $(TEST_SRCS) -L$(OUTDIR) -lmf_core -Wl,-rpath,'$$ORIGIN/../../$(OUTDIR)' $(LDFLAGS) && mv -f $@.tmp $@
 
 ASAN_FLAGS := -fsanitize=address,undefined -fno-omit-frame-pointer -O1
 asan: $(CUDA_OBJS)
@@ -71,6 +71,8 @@ fuzz: $(CUDA_OBJS)
 	$(CXX) $(filter-out -O2 -D_FORTIFY_SOURCE=2,$(CXXFLAGS)) $(ASAN_FLAGS) -o $(BUILD)/asan/mf_fuzz \
 	    csrc/test/fuzz_main.cpp $(HOST_SRCS) $(CUDA_OBJS) $(LDFLAGS)
 
+# Libraries and tools are linked under a temporary name and renamed into place, so a reader of the tree (a packaging step, a
+# process that has the old file mapped) never sees a half-written file.
 # Example programs and tools that are built against the installed headers and library.
 EXAMPLES := examples/bm_perf/bm_perf examples/bm_cpp/bm_example benchmarks/store_bench
 examples: $(EXAMPLES)

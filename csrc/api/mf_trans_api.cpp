@@ -308,6 +308,42 @@ public:
         std::vector<void *> src(n), dst(n);
         std::vector<uint64_t> len(n);
         uint32_t remoteType = hybm::MEM_TYPE_DEVICE;
+        uint32_t peerRank = hybm::RANK_MAX;
+        {
+            std::shared_lock<std::shared_mutex> lk(remoteMu_);
+            auto it = remotes_.find(remoteId);
+            if (it != remotes_.end()) {
+                peerRank = it->second.rank;
+            }
+        }
+        if (peerRank == hybm::RANK_MAX) {
+            int rrc = Refresh(remoteId);
+            if (rrc != MF_OK) {
+                return ret = rrc;
+            }
+            std::shared_lock<std::shared_mutex> lk(remoteMu_);
+            peerRank = remotes_[remoteId].rank;
+        }
+        if (peerRank != hybm::RANK_MAX && entity_->IsRemoteRank(peerRank)) {
+            // The peer lives on another host: nothing of it is mapped here. Every piece is a one-sided put or get through the
+            // host transport, addressed in the peer's own address space (device-side locals are staged by the entity).
+            for (uint32_t i = 0; i < n; i++) {
+                if (locals[i] == nullptr || remotes[i] == nullptr) {
+                    MF_ERROR("trans transfer: null address at #" << i);
+                    return ret = MF_INVALID_PARAM;
+                }
+                uint64_t mapped = 0;
+                ret = Resolve(remoteId, (uint64_t)remotes[i], sizes[i], &mapped, &remoteType);
+                if (ret != MF_OK) {
+                    return ret;
+                }
+                ret = MapHybmCode(entity_->RemoteUserCopy(peerRank, (uint64_t)locals[i], mapped, sizes[i], write, stream));
+                if (ret != MF_OK) {
+                    return ret;
+                }
+            }
+            return ret;
+        }
         for (uint32_t i = 0; i < n; i++) {
             if (locals[i] == nullptr || remotes[i] == nullptr) {
                 MF_ERROR("trans transfer: null address at #" << i);
@@ -486,6 +522,11 @@ private:
             r.recordAddr[(uint32_t)off] = se.gva;
         }
         r.parsedBytes = all.size();
+        if (entity_->IsRemoteRank(d.rank)) {
+            // Peer on another host: "mapping" it means handing its address and keys to the host transport and linking up.
+            int mrc = entity_->Mmap();
+            MF_CHECK_RET(mrc == hybm::BM_OK, MF_ERROR, "trans: cannot link to " << remoteId << " on another host (" << mrc << ")");
+        }
         return MF_OK;
     }
 

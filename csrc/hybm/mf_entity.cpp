@@ -229,8 +229,8 @@ int MemEntity::ServeSlice(std::string *blob)
         return BM_OK;
     }
     std::memcpy(&e, blob->data(), sizeof(e));
-    if (e.segType == SEG_USER_MEM || e.size == 0) {
-        return BM_OK;  // registered user memory has owner-local addresses: not served across hosts
+    if (e.size == 0) {
+        return BM_OK;
     }
     auto host = tp_->Host();
     if (!host->QueryHasRegistered(e.gva, e.size)) {
@@ -258,26 +258,32 @@ int MemEntity::ImportRemoteSlice(const SliceExport &e)
                  "entity: rank " << e.rank << " is on another host; cross-host mode (MF_CROSS_HOST=1) is off on this rank");
     MF_CHECK_RET(e.tpNic[0] != '\0' && e.tpToken != 0, BM_NOT_SUPPORTED,
                  "entity: rank " << e.rank << " is on another host and does not serve its memory (cross-host mode is off there)");
-    MF_CHECK_RET(e.segType == SEG_DEVICE_VMM || e.segType == SEG_HOST_SHM, BM_NOT_SUPPORTED, "entity: only pooled memory is reachable across hosts");
-    auto seg = e.segType == SEG_DEVICE_VMM ? hbm_ : dram_;
-    MF_CHECK_RET(seg != nullptr && seg->InWindow(e.gva, e.size) && seg->RankOf(e.gva) == e.rank, BM_INVALID_PARAM,
-                 "entity: slice of rank " << e.rank << " does not lie in that rank's window here (the ranks reserved different windows)");
+    const bool pooled = e.segType == SEG_DEVICE_VMM || e.segType == SEG_HOST_SHM;
+    if (pooled) {
+        auto seg = e.segType == SEG_DEVICE_VMM ? hbm_ : dram_;
+        MF_CHECK_RET(seg != nullptr && seg->InWindow(e.gva, e.size) && seg->RankOf(e.gva) == e.rank, BM_INVALID_PARAM,
+                     "entity: slice of rank " << e.rank << " does not lie in that rank's window here (the ranks reserved different windows)");
+    }
     std::lock_guard<std::mutex> g(remoteMu_);
     for (const auto &r : remoteSlices_) {
-        if (r.gva == e.gva) {
+        if (r.gva == e.gva && r.rank == e.rank) {
             return BM_OK;  // idempotent
         }
     }
-    AllocatedRange a;
-    a.gva = e.gva;
-    a.size = e.size;
-    a.memType = e.memType;
-    a.ownerRank = e.rank;
-    a.entityId = id_;
-    a.imported = true;
-    a.remote = true;
-    VaManager::Instance().AddAllocated(a);
-    remoteSlices_.push_back(RemoteSlice{e.rank, e.gva, e.size});
+    if (pooled) {
+        // Pool addresses are global: the range is entered in the VA manager so that copies classify and bounds-check it.
+        // Registered user memory is addressed in its owner's address space and is only ever named together with its rank.
+        AllocatedRange a;
+        a.gva = e.gva;
+        a.size = e.size;
+        a.memType = e.memType;
+        a.ownerRank = e.rank;
+        a.entityId = id_;
+        a.imported = true;
+        a.remote = true;
+        VaManager::Instance().AddAllocated(a);
+    }
+    remoteSlices_.push_back(RemoteSlice{e.rank, e.gva, e.size, pooled});
     transport::RankInfo &info = pendingRanks_.ranks[e.rank];
     char nic[sizeof(e.tpNic) + 1] = {0};
     std::memcpy(nic, e.tpNic, sizeof(e.tpNic));
@@ -356,6 +362,19 @@ int MemEntity::RemoteCopy(uint64_t src, uint64_t dst, uint64_t size, const ExtOp
         }
     }
     return BM_OK;
+}
+
+int MemEntity::RemoteUserCopy(uint32_t rank, uint64_t local, uint64_t remote, uint64_t size, bool write, void *stream)
+{
+    MF_CHECK_RET(tp_ != nullptr, BM_NOT_SUPPORTED, "copy: memory on another host needs cross-host mode");
+    MF_CHECK_RET(local != 0 && remote != 0 && size != 0, BM_INVALID_PARAM, "copy: null address or empty copy");
+    ExtOptions opt;
+    opt.stream = stream;
+    opt.srcRank = write ? opt_.rankId : rank;
+    opt.dstRank = write ? rank : opt_.rankId;
+    opt.srcRemote = !write;
+    opt.dstRemote = write;
+    return write ? RemoteCopy(local, remote, size, opt) : RemoteCopy(remote, local, size, opt);
 }
 
 int MemEntity::UpdateDeviceMeta()
@@ -690,7 +709,9 @@ int MemEntity::RemoveImported(uint32_t rank)
         std::lock_guard<std::mutex> g(remoteMu_);
         for (auto it = remoteSlices_.begin(); it != remoteSlices_.end();) {
             if (it->rank == rank) {
-                VaManager::Instance().RemoveAllocated(it->gva);
+                if (it->pooled) {
+                    VaManager::Instance().RemoveAllocated(it->gva);
+                }
                 it = remoteSlices_.erase(it);
             } else {
                 ++it;

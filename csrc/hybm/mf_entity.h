@@ -53,6 +53,11 @@ public:
     // Cross-host mode only (FLAG_CROSS_HOST / MF_CROSS_HOST=1): the router over the device links and the TCP host transport
     // that serves this rank's pool memory to ranks on other hosts and reaches theirs. nullptr otherwise.
     std::shared_ptr<transport::ComposeTransport> Transport() const { return tp_; }
+    // True if `rank` lives on another host (its memory was imported as remote).
+    bool IsRemoteRank(uint32_t rank) { return devTp_->Links().StateOf(rank) == transport::LINK_REMOTE; }
+    // One-sided copy between local memory and registered USER memory of a rank on another host (`remote` is an address of
+    // that rank's own address space). write: local → remote. Device-side locals are staged. Blocking.
+    int RemoteUserCopy(uint32_t rank, uint64_t local, uint64_t remote, uint64_t size, bool write, void *stream);
     int SetExtraContext(const void *ctx, uint32_t size);
     // Bit mask of DataOpType usable towards `rank`.
     uint32_t ReachTypes(uint32_t rank);
@@ -106,6 +111,7 @@ private:
         uint32_t rank;
         uint64_t gva;
         uint64_t size;
+        bool pooled;  // false: registered user memory, whose address is only meaningful on its owner (not in the VA manager)
     };
     int OpenCrossHost();
     int ServeSlice(std::string *blob);

@@ -11,7 +11,7 @@ set -euo pipefail
 ROOT="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 cd "$ROOT"
 ./build.sh
-VERSION="$(python -c 'import memfabric_hybrid_b200 as mf; print(mf.version().split()[0])' 2>/dev/null || echo 0.0.0)"
+VERSION="$(python -c 'import memfabric_hybrid_b200 as mf; print(mf.version().split()[1])' 2>/dev/null || echo 0.0.0)"
 ARCH="$(uname -m)"
 NAME="memfabric_hybrid_b200-${VERSION}-${ARCH}"
 OUT="$ROOT/output"

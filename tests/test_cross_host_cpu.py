@@ -133,3 +133,87 @@ def test_join_refuses_a_host_that_does_not_serve_its_memory():
     by_rank = {r[0]: r for r in res}
     assert by_rank[1][1] == "join=1" and ("cross-host" in by_rank[1][2] or "join callback failed" in by_rank[1][2]), res
     assert by_rank[0][1] == "copy=1", res
+
+
+def _trans_receiver(port, q_addr, q_done):
+    os.environ["MF_HOST_IDENTITY"] = "decode-host"
+    os.environ["MF_HOST_NIC"] = "127.0.0.1"
+    os.environ["MF_CROSS_HOST"] = "1"
+    import memfabric_hybrid_b200 as mf
+
+    try:
+        e = mf.TransferEngine()
+        assert e.initialize(f"tcp://127.0.0.1:{port}", "127.0.0.1:9102", "Decode", -1) == 0, mf.get_last_err_msg()
+        size = 8 << 20
+        addr = e.malloc(size)
+        assert addr != 0
+        mf.native.host_write(addr, bytes(size))
+        assert e.register_memory(addr, size) == 0, mf.get_last_err_msg()
+        q_addr.put(addr)
+        assert q_done.get(timeout=60) == "written"
+        exp = _seeded(5 << 20, 11)
+        assert mf.native.host_read(addr + 4096, exp.size) == exp.tobytes()
+        mf.native.host_write(addr + (6 << 20), b"pong" * 1024)
+        q_addr.put("ready")
+        assert q_done.get(timeout=60) == "read"
+        e.unInitialize()
+        q_addr.put("ok")
+    except Exception as ex:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q_addr.put(repr(ex))
+
+
+def _trans_sender(port, q_addr, q_done, q_res):
+    os.environ["MF_HOST_IDENTITY"] = "prefill-host"
+    os.environ["MF_HOST_NIC"] = "127.0.0.1"
+    os.environ["MF_CROSS_HOST"] = "1"
+    import memfabric_hybrid_b200 as mf
+
+    try:
+        peer_addr = q_addr.get(timeout=60)
+        assert isinstance(peer_addr, int), peer_addr
+        e = mf.TransferEngine()
+        assert e.initialize(f"tcp://127.0.0.1:{port}", "127.0.0.1:9101", "Prefill", -1) == 0, mf.get_last_err_msg()
+        data = _seeded(5 << 20, 11)
+        before = mf.native.data_op_stats()["remote_calls"]
+        # 5 blocks of 1 MiB: each crosses the transport's slice size at most once
+        locs = [data.ctypes.data + i * MiB for i in range(5)]
+        rems = [peer_addr + 4096 + i * MiB for i in range(5)]
+        assert e.batch_transfer_sync_write("127.0.0.1:9102", locs, rems, [MiB] * 5) == 0, mf.get_last_err_msg()
+        assert mf.native.data_op_stats()["remote_calls"] - before == 5
+        # outside what the peer registered: refused before anything is sent
+        assert e.transfer_sync_write("127.0.0.1:9102", data.ctypes.data, peer_addr + (8 << 20) - 10, 4096) != 0
+        q_done.put("written")
+        assert q_addr.get(timeout=60) == "ready"
+        back = np.zeros(4096, dtype=np.uint8)
+        assert e.transfer_sync_read("127.0.0.1:9102", back.ctypes.data, peer_addr + (6 << 20), 4096) == 0, mf.get_last_err_msg()
+        assert back.tobytes() == b"pong" * 1024
+        q_done.put("read")
+        assert q_addr.get(timeout=60) == "ok"
+        e.unInitialize()
+        q_res.put("ok")
+    except Exception as ex:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q_res.put(repr(ex))
+
+
+def test_transfer_engine_between_two_emulated_hosts(mf, port):
+    """Prefill on one host writes KV blocks into memory a decode process registered on another host, by the decoder's own
+    addresses, and reads a reply back: the transfer engine's sender/receiver contract over the host transport."""
+    assert mf.create_config_store(f"tcp://127.0.0.1:{port}") == 0
+    ctx = mp.get_context("spawn")
+    q_addr, q_done, q_res = ctx.Queue(), ctx.Queue(), ctx.Queue()
+    pr = ctx.Process(target=_trans_receiver, args=(port, q_addr, q_done))
+    ps = ctx.Process(target=_trans_sender, args=(port, q_addr, q_done, q_res))
+    pr.start()
+    ps.start()
+    try:
+        assert q_res.get(timeout=120) == "ok"
+    finally:
+        pr.join(30)
+        ps.join(30)
+        mf.destroy_config_store(f"tcp://127.0.0.1:{port}")
