@@ -19,7 +19,10 @@
 //               UE8M0 scale per 32 outputs, which is exactly the A operand format of the second GEMM (no separate
 //               quantisation kernel, no bf16 round trip of the intermediate).
 // BN = 256 (one accumulator of 256 TMEM columns, 4-stage ring) for large row counts; BN = 128 (two accumulators, 6-stage ring)
-// when there are few rows per expert and the kernel streams weights (more, smaller tiles balance the 148 SMs better).
+// when there are few rows per expert and the kernel streams weights (more, smaller tiles balance the 148 SMs better);
+// BN = 224 (two accumulators of 224 columns, 4-stage ring) for the plain bf16 epilogue when N is a multiple of 224: nearly
+// the operand reuse of the 256-wide tile, and the epilogue of one tile runs under the MMAs of the next, which matters when K
+// is short (the second FFN GEMM: N = 7168 = 32 x 224, K = 2048).
 // Every mbarrier wait is bounded; on expiry the CTA sets *status, all roles drain and the CTA frees its TMEM and exits.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -40,17 +43,20 @@ constexpr int kThreads = 384;
 constexpr int kEpiWarps = 8;
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfaCol = 256;  // TMEM columns [256, 260): A scale factors; [260, 260 + BN/32): B scale factors
-constexpr uint32_t kSfbCol = 260;
 constexpr uint32_t kSfOne = 0x7f7f7f7fu;  // four UE8M0 bytes of value 1.0
 
 template <int BN>
 struct Cfg {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kStages = BN == 128 ? 6 : 4;
     static constexpr int kAccBufs = BN == 256 ? 1 : 2;
-    static constexpr int kAtomsB = BN / 128;
+    static constexpr int kAtomsB = (BN + 127) / 128;
     static constexpr int kATile = BM * BK;  // bytes (fp8)
     static constexpr int kBTile = BN * BK;
+    // TMEM columns: the accumulators come first, then four columns of A scale factors, then four per 128 columns of B.
+    static constexpr uint32_t kSfaCol = kAccBufs * BN;
+    static constexpr uint32_t kSfbCol = kSfaCol + 4;
+    static_assert(kSfbCol + 4 * kAtomsB <= kTmemCols, "accumulators and scale factors must fit the 512 TMEM columns");
+    static_assert(kBTile % 1024 == 0, "stages of the B ring must stay 1024-byte aligned for the 128-byte swizzle");
 };
 
 template <int BN>
@@ -179,12 +185,22 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
             int g, mt, nt;
             decode(tile, g, mt, nt);
             const int rowBase = p.groupOffset[g] + mt * BM + lane;
-            const float *pb = p.bScale + ((size_t)g * (p.N / 128) + (size_t)nt * C::kAtomsB) * KB;
+            // Word j of atom a holds the scale of tile columns a*128 + 32*j .. +31, which lie inside ONE 128-column weight
+            // block (tiles start at multiples of 32); with BN = 224 a tile spans up to three blocks. nullptr = past the tile.
+            const float *pbw[C::kAtomsB][4];
+#pragma unroll
+            for (int a = 0; a < C::kAtomsB; a++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int cin = a * 128 + 32 * j;
+                    pbw[a][j] = cin < BN ? p.bScale + ((size_t)g * (p.N / 128) + (size_t)((nt * BN + cin) / 128)) * KB : nullptr;
+                }
+            }
             bool ok = true;
             for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
                 // Scale words of rows lane, lane+32, lane+64, lane+96 for up to four K blocks, and the weight-block scales.
                 uint32_t wa[4][4];
-                uint32_t wb[C::kAtomsB][4];
+                uint32_t wb[C::kAtomsB][4][4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const int r = rowBase + 32 * j;
@@ -212,9 +228,16 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
 #pragma unroll
                 for (int a = 0; a < C::kAtomsB; a++) {
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const float f = kb0 + k < KB ? pb[(size_t)a * KB + kb0 + k] : 1.f;
-                        wb[a][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
+                    for (int j = 0; j < 4; j++) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            if (BN % 128 == 0 && j > 0) {
+                                wb[a][j][k] = wb[a][0][k];  // the whole atom lies in one weight block
+                            } else {
+                                const float f = (pbw[a][j] != nullptr && kb0 + k < KB) ? pbw[a][j][kb0 + k] : 1.f;
+                                wb[a][j][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
+                            }
+                        }
                     }
                 }
 #pragma unroll
@@ -230,7 +253,7 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                     *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(wa[0][k], wa[1][k], wa[2][k], wa[3][k]);
 #pragma unroll
                     for (int a = 0; a < C::kAtomsB; a++) {
-                        *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(wb[a][k], wb[a][k], wb[a][k], wb[a][k]);
+                        *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(wb[a][0][k], wb[a][1][k], wb[a][2][k], wb[a][3][k]);
                     }
                     FenceProxyAsyncShared();
                     __syncwarp();
@@ -262,10 +285,10 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                         break;
                     }
                     TcFenceAfter();
-                    TmemCpSfAtom(tmemBase + kSfaCol, SmemDescSfAtom(SmemAddr(s.sfa[st])));
+                    TmemCpSfAtom(tmemBase + C::kSfaCol, SmemDescSfAtom(SmemAddr(s.sfa[st])));
 #pragma unroll
                     for (int a = 0; a < C::kAtomsB; a++) {
-                        TmemCpSfAtom(tmemBase + kSfbCol + 4 * a, SmemDescSfAtom(SmemAddr(s.sfb[st] + a * 512)));
+                        TmemCpSfAtom(tmemBase + C::kSfbCol + 4 * a, SmemDescSfAtom(SmemAddr(s.sfb[st] + a * 512)));
                     }
                     const uint64_t aDesc = SmemDescSw128(SmemAddr(s.a[st]));
                     const uint64_t bDesc = SmemDescSw128(SmemAddr(s.b[st]));
@@ -273,8 +296,8 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                     for (uint32_t k = 0; k < BK / 32; k++) {
                         // 32 fp8 elements = 32 bytes further along K inside the 128-byte swizzled row: +2 in 16-byte units. The byte of
                         // the scale-factor columns that belongs to this K step rides in the top two address bits and the descriptor.
-                        MmaMxF8(d, aDesc + (uint64_t)(k * 2), bDesc + (uint64_t)(k * 2), InstrDescMxF8(BM, BN, k), (tmemBase + kSfaCol) | (k << 30),
-                                (tmemBase + kSfbCol) | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                        MmaMxF8(d, aDesc + (uint64_t)(k * 2), bDesc + (uint64_t)(k * 2), InstrDescMxF8(BM, BN, k), (tmemBase + C::kSfaCol) | (k << 30),
+                                (tmemBase + C::kSfbCol) | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     MmaCommit(&s.empty[st]);  // the stage (operands and scale atoms) may be refilled once these operations have read it
                 }
@@ -308,6 +331,9 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
             for (int c = 0; c < NV / 32; c++) {
                 TmemLd32Issue(taddr + 32 * c, v + 32 * c);
             }
+            if (NV % 32 != 0) {
+                TmemLd16Issue(taddr + (NV / 32) * 32, v + (NV / 32) * 32);  // BN = 224: 112 columns per thread = 3 x 32 + 16
+            }
             TmemLdWait();
             TcFenceBefore();
             __syncwarp();
@@ -330,7 +356,7 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                     }
                     *reinterpret_cast<uint4 *>(o + j) = pk;
                 }
-            } else {
+            } else if (BN % 128 == 0) {
                 // Every 64 columns hold 32 gate projections followed by the 32 matching up projections.
 #pragma unroll
                 for (int q = 0; q < NV / 64; q++) {
@@ -449,18 +475,23 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
     if (a == nullptr || b == nullptr || out == nullptr || aSf == nullptr || bScale == nullptr || groupOffset == nullptr || groupCount == nullptr ||
         G < 1 || G > kMaxGroups || rowsTotal < 1 || N <= 0 || K <= 0 || N % 128 != 0 || K % BK != 0 ||
         (epi != MF_GEMM_EPI_BF16 && epi != MF_GEMM_EPI_SWIGLU && epi != MF_GEMM_EPI_SWIGLU_FP8) || (epi == MF_GEMM_EPI_SWIGLU_FP8 && outSf == nullptr) ||
-        (tileN != 0 && tileN != 128 && tileN != 256)) {
+        (tileN != 0 && tileN != 128 && tileN != 224 && tileN != 256)) {
         return MF_K_INVALID;
     }
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)out & 15) || ((uintptr_t)aSf & 15)) {
         return MF_K_INVALID;  // TMA base addresses, the 16-byte scale-word loads and the 16-byte epilogue stores need 16-byte alignment
     }
     if (tileN == 0) {
-        // Wide tiles when every SM gets at least two of them even so; otherwise more, narrower tiles balance better.
-        const long long wideTiles = (long long)((rowsTotal + BM - 1) / BM) * (N / 256);
-        tileN = (N % 256 == 0 && wideTiles >= 2LL * 148) ? 256 : 128;
+        // Wide tiles when every SM gets at least two of them even so; otherwise more, narrower tiles balance better. The plain
+        // bf16 epilogue prefers the double-buffered 224-column tile where N allows it.
+        const long long mTiles = (rowsTotal + BM - 1) / BM;
+        if (epi == MF_GEMM_EPI_BF16 && N % 224 == 0 && mTiles * (N / 224) >= 2LL * 148 && getenv("MF_GEMM_NO_224") == nullptr) {
+            tileN = 224;
+        } else {
+            tileN = (N % 256 == 0 && mTiles * (N / 256) >= 2LL * 148) ? 256 : 128;
+        }
     }
-    if (tileN == 256 && N % 256 != 0) {
+    if ((tileN == 256 && N % 256 != 0) || (tileN == 224 && (N % 224 != 0 || epi != MF_GEMM_EPI_BF16))) {
         return MF_K_INVALID;
     }
     CUtensorMap mapA, mapB;
@@ -480,5 +511,8 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
     p.K = K;
     p.mode = mode;
     p.rowsTotal = rowsTotal;
+    if (tileN == 224) {
+        return Launch<224>(mapA, mapB, p, ctas, (cudaStream_t)stream);
+    }
     return tileN == 256 ? Launch<256>(mapA, mapB, p, ctas, (cudaStream_t)stream) : Launch<128>(mapA, mapB, p, ctas, (cudaStream_t)stream);
 }

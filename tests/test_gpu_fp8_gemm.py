@@ -101,10 +101,16 @@ def test_grouped_gemm_swiglu_epilogue(big_counts):
 # ---------------------------------------------------------------------------------------------- block-scaled tensor-core path (UE8M0 scales)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
-@pytest.mark.parametrize("counts,N,K", [([128], 256, 128), ([128], 256, 512), ([1], 256, 384), ([200, 0, 37, 128], 256, 1024),
-                                        ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048), ([700, 256, 1], 512, 1024),
-                                        ([1000, 130, 257, 640], 768, 2048)])
+def _mx_cases():
+    base = [([128], 256, 128), ([128], 256, 512), ([1], 256, 384), ([200, 0, 37, 128], 256, 1024), ([5, 17, 300, 64, 1, 129, 0, 255], 512, 2048),
+            ([700, 256, 1], 512, 1024), ([1000, 130, 257, 640], 768, 2048)]
+    cases = [(c, n, k, t) for (c, n, k) in base for t in (128, 256)]
+    # 224-column tiles (two accumulators, a tile spans up to three 128-column weight blocks): N must be a multiple of 896
+    cases += [([128], 896, 128, 224), ([1, 300, 0, 129], 896, 1024, 224), ([700, 256, 1, 64], 1792, 2048, 224), ([513], 1792, 384, 0)]
+    return cases
+
+
+@pytest.mark.parametrize("counts,N,K,tile_n", _mx_cases())
 def test_grouped_gemm_mx_matches_reference(counts, N, K, tile_n):
     import torch
 
