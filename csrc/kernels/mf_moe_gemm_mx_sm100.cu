@@ -485,7 +485,11 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
         // Wide tiles when every SM gets at least two of them even so; otherwise more, narrower tiles balance better. The plain
         // bf16 epilogue prefers the double-buffered 224-column tile where N allows it.
         const long long mTiles = (rowsTotal + BM - 1) / BM;
-        if (epi == MF_GEMM_EPI_BF16 && N % 224 == 0 && mTiles * (N / 224) >= 2LL * 148 && getenv("MF_GEMM_NO_224") == nullptr) {
+        static const bool auto224 = []() {
+            const char *e = getenv("MF_GEMM_TILE224");
+            return e != nullptr && e[0] == '1';
+        }();
+        if (auto224 && epi == MF_GEMM_EPI_BF16 && N % 224 == 0 && mTiles * (N / 224) >= 2LL * 148) {
             tileN = 224;
         } else {
             tileN = (N % 256 == 0 && mTiles * (N / 256) >= 2LL * 148) ? 256 : 128;
