@@ -164,24 +164,55 @@ __device__ __forceinline__ void Fail(const mf_allreduce_args_t &a, int code)
     }
 }
 
+// Epoch of this call: the kernel argument, or (argument 0) one more than the device-resident count of finished calls. Every CTA
+// of the launch reads the same value: the count only moves when the LAST CTA of a launch retires (FinishEpoch).
+__device__ __forceinline__ uint64_t ResolveEpoch(const mf_allreduce_args_t &a, uint64_t epochArg)
+{
+    if (epochArg != 0 || a.epochState == nullptr) {
+        return epochArg;
+    }
+    return *(volatile unsigned long long *)a.epochState + 1;
+}
+
+// Called by every CTA on every way out of the kernel (after its last use of the epoch).
+__device__ __forceinline__ void FinishEpoch(const mf_allreduce_args_t &a, uint64_t epochArg, uint64_t epoch)
+{
+    if (epochArg != 0 || a.epochState == nullptr) {
+        return;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned long long done = atomicAdd(a.epochState + 1, 1ull);
+        if (done == (unsigned long long)gridDim.x - 1) {
+            a.epochState[1] = 0;
+            *(volatile unsigned long long *)a.epochState = epoch;
+            __threadfence();
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ one-shot
 
 template <int VPT, bool TAIL>
 __global__ void __launch_bounds__(kThreads, 1)
-mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epoch,
+mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epochArg,
                                     uint64_t timeoutNs)
 {
     const mf_allreduce_args_t a = args[blockIdx.y];
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     const int vecsPerRow = H / 8;
+    const uint64_t epoch = ResolveEpoch(a, epochArg);
     if (mf_check_bounds_enabled(m) && !mf_shm_in_own_window(m, a.x, (uint64_t)T * H * 2)) {
         Fail(a, MF_DEV_ERR_BOUNDS);  // peers would read my x at this offset of their own heaps: it must be heap memory
+        FinishEpoch(a, epochArg, epoch);
         return;
     }
     // Peers' x is complete once their CTA of the same index has arrived here.
     int rc = mf_barrier_cta(m, channel, blockIdx.x, 2 * epoch - 1, timeoutNs);
     if (rc != MF_DEV_OK) {
         Fail(a, rc);
+        FinishEpoch(a, epochArg, epoch);
         return;
     }
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
@@ -216,6 +247,7 @@ mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args
             Fail(a, rc);
         }
     }
+    FinishEpoch(a, epochArg, epoch);
 }
 
 // ------------------------------------------------------------------------------------------------ two-shot / NVLS
@@ -223,7 +255,7 @@ mf_allreduce_rmsnorm_oneshot_kernel(const mf_allreduce_args_t *__restrict__ args
 // RC: compile-time upper bound of the rank count (2, 4 or 8; 0 = any) so that the peer vectors of a trip live in registers.
 template <bool NVLS, int VPT, int RC>
 __global__ void __launch_bounds__(kThreads, 1)
-mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epoch,
+mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args, int T, int H, float eps, uint32_t channel, uint64_t epochArg,
                                     uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
@@ -231,9 +263,11 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     const uint32_t R = m->rankCount, me = m->rankId;
     const int vecsPerRow = H / 8;
+    const uint64_t epoch = ResolveEpoch(a, epochArg);
     __shared__ int abortFlag;
     if (mf_check_bounds_enabled(m) && !(mf_shm_in_own_window(m, a.x, (uint64_t)T * H * 2) && mf_shm_in_own_window(m, a.residualOut, (uint64_t)T * H * 2))) {
         Fail(a, MF_DEV_ERR_BOUNDS);  // every CTA of every rank decides alike from the same arguments: nobody waits for anybody
+        FinishEpoch(a, epochArg, epoch);
         return;
     }
 
@@ -348,6 +382,7 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
     }
     __syncthreads();
     if (abortFlag != 0) {
+        FinishEpoch(a, epochArg, epoch);
         return;
     }
     // Phase 2: normalise every row from the (now complete) local copy of the new residual.
@@ -363,6 +398,7 @@ mf_allreduce_rmsnorm_twoshot_kernel(const mf_allreduce_args_t *__restrict__ args
         }
         NormAndStore<VPT>(acc, vecsPerRow, (const char *)a.weight, (char *)a.out + rowOff, H, eps);
     }
+    FinishEpoch(a, epochArg, epoch);
 }
 
 template <int VPT>
@@ -441,8 +477,8 @@ extern "C" int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nE
                                       uint32_t channel, uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream)
 {
     if (argsDev == nullptr || nEmulatedRanks < 1 || rankCount < 1 || rankCount > (int)MF_SIGNAL_MAX_RANKS || T <= 0 || H <= 0 || H % 8 != 0 ||
-        H > kThreads * kMaxVpt * 8 || channel >= MF_SIGNAL_CHANNELS || epoch == 0) {
-        return MF_K_INVALID;
+        H > kThreads * kMaxVpt * 8 || channel >= MF_SIGNAL_CHANNELS) {
+        return MF_K_INVALID;  // epoch 0 = device-resident epoch (args->epochState), see the header
     }
     if (timeoutNs == 0) {
         timeoutNs = 2000000000ull;

@@ -57,7 +57,10 @@ typedef struct {
     void *residualOut;     // [T, H] bf16: residual + sum_r x_r (may be NULL for one-shot)
     void *out;             // [T, H] bf16: RMSNorm(residualOut) * weight
     int *status;           // device int, zero before launch; receives MF_DEV_ERR_* | peer << 8 on a bounded-wait expiry
-    void *reserved;
+    // Device-resident epoch (optional): two 64-bit words, [0] = epoch of the last finished call, [1] = 0. With `epoch` 0 the
+    // kernel takes epochState[0] + 1 as its epoch and the last CTA to finish stores it back, so the same launch can be
+    // replayed from a CUDA graph (kernel arguments are frozen there, the epoch must still grow with every call).
+    unsigned long long *epochState;
 } mf_allreduce_args_t;
 
 // MF_AR_ONESHOT_NOTAIL: one-shot without the closing cross-rank barrier. Only legal when the caller alternates between two x
@@ -67,7 +70,9 @@ enum { MF_AR_AUTO = 0, MF_AR_ONESHOT = 1, MF_AR_TWOSHOT = 2, MF_AR_NVLS = 3, MF_
 
 // argsDev: device array of nEmulatedRanks blocks (1 in production; R when a test runs all ranks of a fake heap on one GPU
 // as slices of one cooperative launch). rankCount must equal meta->rankCount. epoch: strictly increasing per (heap,
-// channel), identical on all ranks (mf_shm_next_epoch). H: multiple of 8, at most 16384. timeoutNs 0 = 2 s.
+// channel), identical on all ranks (mf_shm_next_epoch); 0 = take it from args->epochState (every rank must then do so, the
+// states must have been initialised to the same value, at least the channel's last host-side epoch, and the channel must not
+// be used with host-side epochs any more). H: multiple of 8, at most 16384. timeoutNs 0 = 2 s.
 int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRanks, int rankCount, int T, int H, float eps, int algo,
                            uint32_t channel, uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 

@@ -21,7 +21,8 @@ void BindOps(py::module_ &m)
     ops.attr("ALLREDUCE_ARGS_BYTES") = (int)sizeof(mf_allreduce_args_t);
 
     // Packs one argument block (to be copied to device memory by the caller).
-    ops.def("pack_allreduce_args", [](uint64_t meta, uint64_t x, uint64_t residual, uint64_t weight, uint64_t residualOut, uint64_t out, uint64_t status) {
+    ops.def("pack_allreduce_args", [](uint64_t meta, uint64_t x, uint64_t residual, uint64_t weight, uint64_t residualOut, uint64_t out, uint64_t status,
+                                       uint64_t epochState) {
         mf_allreduce_args_t a{};
         a.meta = (const void *)meta;
         a.x = (const void *)x;
@@ -30,8 +31,10 @@ void BindOps(py::module_ &m)
         a.residualOut = (void *)residualOut;
         a.out = (void *)out;
         a.status = (int *)status;
+        a.epochState = (unsigned long long *)epochState;
         return py::bytes((const char *)&a, sizeof(a));
-    });
+    }, py::arg("meta"), py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("residual_out"), py::arg("out"), py::arg("status"),
+       py::arg("epoch_state") = 0);
     ops.attr("GEMM_EPI_BF16") = (int)MF_GEMM_EPI_BF16;
     ops.attr("GEMM_EPI_SWIGLU") = (int)MF_GEMM_EPI_SWIGLU;
     ops.attr("GEMM_EPI_SWIGLU_FP8") = (int)MF_GEMM_EPI_SWIGLU_FP8;

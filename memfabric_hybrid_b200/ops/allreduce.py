@@ -11,6 +11,11 @@ when every peer has long passed the opening barrier of the call in between. Fetc
 
 `out = RMSNorm(residual + sum_r x_r) * weight`, `new_residual = residual + sum_r x_r`, both bf16 [T, hidden]. The kernel
 (csrc/kernels/mf_allreduce.cu) picks one-shot / two-shot / NVLS by size unless `algo` is given.
+
+CUDA graphs: with `device_epochs=True` the epoch that orders the cross-rank flags lives in device memory and is advanced by the
+kernel itself, so calls may be captured into a graph and replayed (a decode step is typically one graph). Every rank must
+use the same setting, the op then owns its signal channel, and with two input buffers a captured sequence must contain an
+even number of calls (the buffers alternate per call, a replay must start on the buffer the capture started on).
 """
 from __future__ import annotations
 
@@ -38,7 +43,8 @@ def reference(xs, residual, weight, eps: float):
 
 
 class AllReduceRMSNorm:
-    def __init__(self, heap, max_tokens: int, hidden: int, eps: float = 1e-6, channel: int = 0, timeout_ns: int = 0, double_buffer: bool = True):
+    def __init__(self, heap, max_tokens: int, hidden: int, eps: float = 1e-6, channel: int = 0, timeout_ns: int = 0, double_buffer: bool = True,
+                 device_epochs: bool = False):
         import torch
 
         if hidden % 8 != 0 or hidden > 16384:
@@ -59,6 +65,12 @@ class AllReduceRMSNorm:
         self._args = [torch.empty(_ops.ALLREDUCE_ARGS_BYTES, dtype=torch.uint8, device=dev) for _ in range(2)]
         self._args_key = [None, None]
         self.launches = 0
+        self.device_epochs = device_epochs
+        self._epoch_state = None
+        if device_epochs:
+            # [0] = epoch of the last finished call, [1] = CTAs of the running call that have retired. Starts at the channel's
+            # current host-side epoch (the same number on every rank), so that flags left by earlier host-epoch calls are stale.
+            self._epoch_state = torch.tensor([heap.next_epoch(channel), 0], dtype=torch.int64, device=dev)
 
     @property
     def x(self):
@@ -72,7 +84,8 @@ class AllReduceRMSNorm:
         key = (residual.data_ptr() if residual is not None else 0, weight.data_ptr())
         if key != self._args_key[c]:
             blob = _ops.pack_allreduce_args(self.heap.meta_ptr, self._xs[c].data_ptr(), key[0], key[1], self.residual_out.data_ptr(),
-                                            self.out.data_ptr(), self.status.data_ptr())
+                                            self.out.data_ptr(), self.status.data_ptr(),
+                                            self._epoch_state.data_ptr() if self._epoch_state is not None else 0)
             self._args[c].copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8), non_blocking=False)
             self._args_key[c] = key
         return self._args[c].data_ptr()
@@ -99,7 +112,7 @@ class AllReduceRMSNorm:
             raise RuntimeError("the NVLS algorithm needs a heap created with nvls=True on a platform with multicast")
         args = self._pack(residual, weight)
         s = stream or torch.cuda.current_stream()
-        epoch = self.heap.next_epoch(self.channel)
+        epoch = 0 if self.device_epochs else self.heap.next_epoch(self.channel)
         rc = _ops.allreduce_rmsnorm(args, 1, self.heap.world, tokens, self.hidden, self.eps, a, self.channel, epoch, self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"allreduce_rmsnorm launch failed ({rc})")
@@ -111,6 +124,39 @@ class AllReduceRMSNorm:
     def check_status(self) -> int:
         """Synchronises and returns the device status word (0 = fine, else MF_DEV_ERR_* | peer << 8)."""
         return int(self.status.item())
+
+
+class EmulatedAllReduce:
+    """All ranks of an EmulatedHeap as ONE cooperative launch with device-resident epochs: `launch()` may be called any number
+    of times and captured into a CUDA graph (the epochs advance on the device). Inputs are read from the heap at `xs_off` of
+    every rank, outputs land in `outs[r]`."""
+
+    def __init__(self, eheap, xs_off: int, res_out_off: int, residuals, weight, tokens: int, hidden: int, eps: float, algo: str, channel: int = 1):
+        import torch
+
+        self.eheap, self.tokens, self.hidden, self.eps, self.algo, self.channel = eheap, tokens, hidden, eps, ALGOS[algo], channel
+        world = eheap.world
+        self.outs = [torch.zeros(tokens, hidden, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        self.status = torch.zeros(world, dtype=torch.int32, device="cuda")
+        self.epoch_state = torch.zeros(world, 2, dtype=torch.int64, device="cuda")
+        self.epoch_state[:, 0] = eheap.next_epoch(channel)
+        blob = b""
+        for r in range(world):
+            rk = eheap.ranks[r]
+            blob += _ops.pack_allreduce_args(rk.meta_ptr, rk.addr(xs_off), residuals[r].data_ptr() if residuals is not None else 0, weight.data_ptr(),
+                                             rk.addr(res_out_off), self.outs[r].data_ptr(), self.status.data_ptr() + 4 * r,
+                                             self.epoch_state.data_ptr() + 16 * r)
+        self.args = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
+        self._keep = (residuals, weight)
+
+    def launch(self, stream=None):
+        import torch
+
+        s = stream or torch.cuda.current_stream()
+        rc = _ops.allreduce_rmsnorm(self.args.data_ptr(), self.eheap.world, self.eheap.world, self.tokens, self.hidden, self.eps, self.algo,
+                                    self.channel, 0, 0, 0, s.cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"allreduce_rmsnorm launch failed ({rc})")
 
 
 def emulated_allreduce(eheap, xs_off: int, res_out_off: int, residuals, weight, tokens: int, hidden: int, eps: float, algo: str,

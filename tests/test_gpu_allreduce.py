@@ -160,3 +160,117 @@ def test_real_ranks_one_per_gpu():
     for p in ps:
         p.join(timeout=60)
     assert res == [(r, "ok") for r in range(world)], res
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+def test_emulated_ranks_replayed_from_a_cuda_graph(algo):
+    """Device-resident epochs: the launch is captured once and replayed with new inputs; the flags must order every replay
+    (a frozen epoch would let a replay run through on the flags of the previous one and read half-written inputs)."""
+    import torch
+
+    from memfabric_hybrid_b200.ops.allreduce import EmulatedAllReduce, reference
+    from memfabric_hybrid_b200.parallel.heap import EmulatedHeap
+
+    world, T, H, eps = 4, 24, 4096, 1e-6
+    xs, res, w = _make_inputs(world, T, H, 77)
+    heap = EmulatedHeap(world, 2 * T * H * 2 + 8192)
+    x_off, r_off = heap.alloc(T * H * 2), heap.alloc(T * H * 2)
+    op = EmulatedAllReduce(heap, x_off, r_off, [res] * world, w, T, H, eps, algo)
+    for r in range(world):
+        heap.tensor(r, x_off, (T, H), torch.bfloat16).copy_(xs[r])
+    op.launch()  # plain launch first (also warms the function up before capture)
+    torch.cuda.synchronize()
+    ref_out, _ = reference(xs, res, w, eps)
+    torch.testing.assert_close(op.outs[0].float(), ref_out, atol=2e-2, rtol=2e-2)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            op.launch(stream=side)
+            op.launch(stream=side)
+    torch.cuda.synchronize()
+    first = int(op.epoch_state[0, 0])
+    for it in range(3):
+        xs2, _, _ = _make_inputs(world, T, H, 500 + it)
+        for r in range(world):
+            heap.tensor(r, x_off, (T, H), torch.bfloat16).copy_(xs2[r])
+        graph.replay()
+        torch.cuda.synchronize()
+        assert op.status.cpu().tolist() == [0] * world
+        ref_out, _ = reference(xs2, res, w, eps)
+        for r in range(world):
+            torch.testing.assert_close(op.outs[r].float(), ref_out, atol=2e-2, rtol=2e-2)
+    # every rank counted every call: one plain launch, then three replays of two
+    assert op.epoch_state[:, 0].cpu().tolist() == [first + 6] * world and op.epoch_state[:, 1].cpu().tolist() == [0] * world
+
+
+def _graph_rank(rank, world, port, q):
+    try:
+        import torch
+
+        from memfabric_hybrid_b200.ops.allreduce import AllReduceRMSNorm, reference
+        from memfabric_hybrid_b200.parallel.heap import SymmetricHeap
+
+        torch.cuda.set_device(rank)
+        heap = SymmetricHeap(rank, world, rank, 64 << 20, store_url=f"tcp://127.0.0.1:{port}")
+        T, H = 8, 8192
+        ar = AllReduceRMSNorm(heap, T, H, device_epochs=True)
+        xs, res, w = _make_inputs(world, T, H, 99)
+        bufs = [ar.x]
+        ar.x.copy_(xs[rank])
+        torch.cuda.synchronize()
+        heap.barrier()
+        ar(T, res, w)  # warm-up calls outside the graph: argument blocks are uploaded, both input buffers seen
+        bufs.append(ar.x)
+        ar.x.copy_(xs[rank])
+        torch.cuda.synchronize()
+        heap.barrier()
+        ar(T, res, w)
+        torch.cuda.synchronize()
+        heap.barrier()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        outs = []
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(2):
+                    o, _h = ar(T, res, w, stream=side)
+                    outs.append(o.clone())
+        for it in range(3):
+            xs2, _, _ = _make_inputs(world, T, H, 1000 + it)
+            for b in bufs:
+                b.copy_(xs2[rank])
+            torch.cuda.synchronize()
+            heap.barrier()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert ar.check_status() == 0
+            ref_out, _ = reference(xs2, res, w, 1e-6)
+            for o in outs:
+                torch.testing.assert_close(o.float(), ref_out, atol=2e-2, rtol=2e-2)
+            heap.barrier()
+        heap.close()
+        q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(e)))
+
+
+def test_real_ranks_replay_a_captured_graph():
+    import torch
+
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    ps = [ctx.Process(target=_graph_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in ps)
+    for p in ps:
+        p.join(timeout=60)
+    assert res == [(r, "ok") for r in range(world)], res
