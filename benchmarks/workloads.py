@@ -57,6 +57,33 @@ def timed_us(fn, iters: int, warmup: int = 3, stream=None) -> float:
 # ---------------------------------------------------------------------------------------------- all-reduce + residual + RMSNorm
 
 
+def _graph_us(call, prepare, iters: int, calls_per_graph: int = 10, check=None) -> float:
+    """Microseconds per call when `calls_per_graph` calls are captured into one CUDA graph and the graph is replayed `iters`
+    times. call(stream) issues one call on the capture stream; prepare() runs before capture (fills inputs)."""
+    import torch
+
+    prepare()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            call(side)  # warm-up outside the graph: argument blocks uploaded, both input buffers seen
+    torch.cuda.synchronize()
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(calls_per_graph):
+                call(side)
+    torch.cuda.synchronize()
+    barrier()
+    graph.replay()  # one replay on its own first: a replay that cannot complete must not be repeated iters times
+    torch.cuda.synchronize()
+    if check is not None and check() != 0:
+        raise RuntimeError(f"status {check()} after the first replay")
+    return timed_us(graph.replay, iters) / calls_per_graph
+
+
 def allreduce_sizes(heap, sizes: List[int], hidden: int = 8192, iters: int = 20, baselines: bool = True) -> List[Dict]:
     """Fused all-reduce + residual add + RMSNorm (bf16, eps 1e-6) for each x size in bytes, every algorithm that applies,
     against NCCL all-reduce + separate add and norm kernels and against NCCL all-reduce alone."""
@@ -69,6 +96,11 @@ def allreduce_sizes(heap, sizes: List[int], hidden: int = 8192, iters: int = 20,
     H = hidden
     max_T = max(1, max(sizes) // (H * 2))
     ar = AllReduceRMSNorm(heap, max_T, H, eps=1e-6)
+    # Small inputs are also timed as a replayed CUDA graph (ten calls per graph), which is how a decode step runs them: the
+    # launch overhead of the host loop disappears from the figure. Needs the device-resident epochs and its own signal channel.
+    graph_max = 4 << 20
+    small_T = max([max(1, n // (H * 2)) for n in sizes if n <= graph_max], default=0)
+    ar_g = AllReduceRMSNorm(heap, small_T, H, eps=1e-6, channel=1, device_epochs=True, timeout_ns=200_000_000) if small_T else None
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     gc = torch.Generator(device="cuda").manual_seed(7)  # residual and weight are replicated across tensor-parallel ranks
     w = (1.0 + 0.1 * torch.randn(H, generator=gc, device="cuda")).to(torch.bfloat16)
@@ -88,6 +120,12 @@ def allreduce_sizes(heap, sizes: List[int], hidden: int = 8192, iters: int = 20,
             row[algo + "_us"] = round(timed_us(lambda: ar(T, res, w, algo=algo), it), 2)
         row["auto_us"] = round(timed_us(lambda: ar(T, res, w), it), 2)
         row["status"] = ar.check_status()
+        if ar_g is not None and nbytes <= graph_max:
+            try:
+                row["auto_graph_us"] = round(_graph_us(lambda s: ar_g(T, res, w, stream=s), lambda: [b[:T].copy_(x) for b in ar_g._xs], it,
+                                                       check=ar_g.check_status), 2)
+            except Exception as e:  # noqa: BLE001
+                row["graph_error"] = repr(e)[:160]
         best = min(row[a + "_us"] for a in algos)
         if baselines:
             xb = x.clone()
@@ -104,6 +142,11 @@ def allreduce_sizes(heap, sizes: List[int], hidden: int = 8192, iters: int = 20,
             if d is not None:
                 xb2 = x.clone()
                 row["nccl_allreduce_only_us"] = round(timed_us(lambda: d.all_reduce(xb2), it), 2)
+                if nbytes <= graph_max:
+                    try:
+                        row["nccl_allreduce_only_graph_us"] = round(_graph_us(lambda s: d.all_reduce(xb2), lambda: None, it), 2)
+                    except Exception as e:  # noqa: BLE001 - a library that refuses capture must not take the row down
+                        row["nccl_graph_error"] = repr(e)[:120]
             row["speedup_vs_nccl_unfused"] = round(row["nccl_unfused_us"] / best, 2)
         if world > 1:
             link_bytes = row["bytes"] * (1.0 if "nvls" in algos else 2.0 * (world - 1) / world)
