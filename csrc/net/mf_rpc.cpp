@@ -15,6 +15,7 @@
 #include <sys/epoll.h>
 #include <sys/eventfd.h>
 #include <sys/socket.h>
+#include <sys/uio.h>
 #include <unistd.h>
 #include <vector>
 
@@ -188,6 +189,7 @@ struct RpcServer::Conn {
     LinkId id{0};
     bool hello{false};
     bool dead{false};
+    Frame frame;  // the frame being delivered (I/O thread only)
     std::string in;
     std::deque<std::string> out;  // guarded by RpcServer::mu_
     size_t outOff{0};
@@ -335,6 +337,67 @@ int RpcServer::Send(LinkId link, const Frame &f)
     return SendBytesLocked(c, std::move(bytes));
 }
 
+int RpcServer::SendWithPayload(LinkId link, const Frame &f, const void *payload, size_t payloadLen)
+{
+    if (payloadLen > kMaxBodyLen) {
+        return -1;
+    }
+    WireHeader h{kWireMagic, f.type, f.result, (uint32_t)payloadLen, f.seq};
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = conns_.find(link);
+    if (it == conns_.end() || it->second->dead) {
+        return -1;
+    }
+    Conn &c = *it->second;
+    if (c.tls || !c.out.empty()) {
+        // Encrypted links need one plaintext; a link with a backlog must keep its order: both take the copying path.
+        std::string bytes;
+        bytes.reserve(sizeof(h) + payloadLen);
+        bytes.append((const char *)&h, sizeof(h));
+        bytes.append((const char *)payload, payloadLen);
+        if (c.tls) {
+            std::string wire;
+            if (c.tls->Encrypt(bytes.data(), bytes.size(), &wire) != 0) {
+                return -1;
+            }
+            bytes.swap(wire);
+        }
+        return SendBytesLocked(c, std::move(bytes));
+    }
+    iovec iov[2] = {{&h, sizeof(h)}, {const_cast<void *>(payload), payloadLen}};
+    size_t idx = 0;
+    while (idx < 2) {
+        msghdr mh{};
+        mh.msg_iov = iov + idx;
+        mh.msg_iovlen = 2 - idx;
+        ssize_t n = ::sendmsg(c.fd, &mh, MSG_NOSIGNAL | MSG_DONTWAIT);
+        if (n < 0 && errno == EINTR) {
+            continue;
+        }
+        if (n <= 0) {
+            break;  // EAGAIN or error: the rest is queued and the I/O thread finishes or drops it
+        }
+        size_t adv = (size_t)n;
+        while (adv > 0 && idx < 2) {
+            const size_t take = adv < iov[idx].iov_len ? adv : iov[idx].iov_len;
+            iov[idx].iov_base = (char *)iov[idx].iov_base + take;
+            iov[idx].iov_len -= take;
+            adv -= take;
+            if (iov[idx].iov_len == 0) {
+                idx++;
+            }
+        }
+    }
+    if (idx == 2) {
+        return 0;
+    }
+    std::string rest;
+    for (size_t i = idx; i < 2; i++) {
+        rest.append((const char *)iov[i].iov_base, iov[i].iov_len);
+    }
+    return SendBytesLocked(c, std::move(rest));
+}
+
 int RpcServer::SendBytesLocked(Conn &c, std::string bytes)
 {
     size_t off = 0;
@@ -461,9 +524,10 @@ void RpcServer::OnReadable(const std::shared_ptr<Conn> &c)
         ssize_t n = ::recv(c->fd, buf, sizeof(buf), 0);
         if (n > 0) {
             sink.append(buf, (size_t)n);
-            if ((size_t)n < sizeof(buf)) {
-                break;
+            if (sink.size() >= (8u << 20)) {
+                break;  // hand what has arrived to the parser before reading on (the socket is level-triggered)
             }
+            // A short read does not mean the socket is empty (a bulk sender delivers segment by segment): read until EAGAIN.
         } else if (n == 0) {
             eof = true;
             break;
@@ -510,7 +574,7 @@ void RpcServer::OnReadable(const std::shared_ptr<Conn> &c)
         if (c->in.size() - pos < sizeof(h) + h.bodyLen) {
             break;
         }
-        Frame f;
+        Frame &f = c->frame;  // one per link, so that a stream of large frames reuses one buffer instead of allocating afresh
         f.type = h.type;
         f.result = h.result;
         f.seq = h.seq;
@@ -843,21 +907,66 @@ void RpcClient::FailAll()
     }
 }
 
-int RpcClient::SendFrame(uint16_t type, uint32_t seq, const std::string &body)
+int RpcClient::SendFrame(uint16_t type, uint32_t seq, const std::string &body) { return SendParts(type, seq, body.data(), body.size(), nullptr, 0); }
+
+int RpcClient::SendParts(uint16_t type, uint32_t seq, const void *head, size_t headLen, const void *payload, size_t payloadLen)
 {
-    Frame f;
-    f.type = type;
-    f.seq = seq;
-    f.body = body;
-    std::string bytes = Encode(f);
+    if (headLen + payloadLen > kMaxBodyLen) {
+        return -1;
+    }
+    WireHeader h{kWireMagic, type, 0, (uint32_t)(headLen + payloadLen), seq};
     std::lock_guard<std::mutex> g(sendMu_);
     if (!connected_.load() || fd_ < 0) {
         return -1;
     }
-    return IoWrite(bytes.data(), bytes.size()) ? 0 : -1;
+    if (tls_) {
+        // The record layer needs one contiguous plaintext anyway.
+        std::string bytes;
+        bytes.reserve(sizeof(h) + headLen + payloadLen);
+        bytes.append((const char *)&h, sizeof(h));
+        bytes.append((const char *)head, headLen);
+        bytes.append((const char *)payload, payloadLen);
+        return IoWrite(bytes.data(), bytes.size()) ? 0 : -1;
+    }
+    // Plain TCP: wire header, head and payload leave from where they lie.
+    iovec iov[3] = {{&h, sizeof(h)}, {const_cast<void *>(head), headLen}, {const_cast<void *>(payload), payloadLen}};
+    size_t idx = 0, left = sizeof(h) + headLen + payloadLen;
+    while (left > 0) {
+        while (idx < 3 && iov[idx].iov_len == 0) {
+            idx++;
+        }
+        msghdr mh{};
+        mh.msg_iov = iov + idx;
+        mh.msg_iovlen = 3 - idx;
+        ssize_t n = ::sendmsg(fd_, &mh, MSG_NOSIGNAL);
+        if (n < 0 && errno == EINTR) {
+            continue;
+        }
+        if (n <= 0) {
+            return -1;
+        }
+        left -= (size_t)n;
+        size_t adv = (size_t)n;
+        while (adv > 0 && idx < 3) {
+            const size_t take = adv < iov[idx].iov_len ? adv : iov[idx].iov_len;
+            iov[idx].iov_base = (char *)iov[idx].iov_base + take;
+            iov[idx].iov_len -= take;
+            adv -= take;
+            if (iov[idx].iov_len == 0) {
+                idx++;
+            }
+        }
+    }
+    return 0;
 }
 
 int RpcClient::Call(uint16_t type, const std::string &body, Frame *reply, int64_t timeoutMs)
+{
+    return CallGather(type, body.data(), body.size(), nullptr, 0, nullptr, 0, reply, timeoutMs);
+}
+
+int RpcClient::CallGather(uint16_t type, const void *head, size_t headLen, const void *payload, size_t payloadLen, void *sink, size_t sinkLen,
+                          Frame *reply, int64_t timeoutMs)
 {
     if (!connected_.load()) {
         return RPC_IO_ERROR;
@@ -867,11 +976,13 @@ int RpcClient::Call(uint16_t type, const std::string &body, Frame *reply, int64_
         seq = nextSeq_.fetch_add(1);
     }
     auto p = std::make_shared<Pending>();
+    p->sink = sink;
+    p->sinkLen = sinkLen;
     {
         std::lock_guard<std::mutex> g(mu_);
         pending_[seq] = p;
     }
-    if (SendFrame(type, seq, body) != 0) {
+    if (SendParts(type, seq, head, headLen, payload, payloadLen) != 0) {
         std::lock_guard<std::mutex> g(mu_);
         pending_.erase(seq);
         return RPC_IO_ERROR;
@@ -880,6 +991,7 @@ int RpcClient::Call(uint16_t type, const std::string &body, Frame *reply, int64_
     if (timeoutMs < 0) {
         p->cv.wait(lk, [&]() { return p->done; });
     } else if (!p->cv.wait_for(lk, std::chrono::milliseconds(timeoutMs), [&]() { return p->done; })) {
+        p->abandoned = true;  // under p->mu: the reader fills a sink only while holding it, so it is not in the sink now
         lk.unlock();
         std::lock_guard<std::mutex> g(mu_);
         pending_.erase(seq);
@@ -934,9 +1046,30 @@ void RpcClient::ReaderLoop()
         f.type = h.type;
         f.result = h.result;
         f.seq = h.seq;
-        f.body.resize(h.bodyLen);
-        if (h.bodyLen > 0 && !IoRead(&f.body[0], h.bodyLen)) {
-            break;
+        // A caller that handed in a buffer of exactly the body's size gets the body read straight into it.
+        std::shared_ptr<Pending> direct;
+        if (h.bodyLen > 0 && h.result == 0 && h.type != MSG_GOODBYE) {
+            std::lock_guard<std::mutex> g(mu_);
+            auto it = pending_.find(h.seq);
+            if (it != pending_.end() && it->second->sink != nullptr && it->second->sinkLen == h.bodyLen && !it->second->persist) {
+                direct = it->second;
+            }
+        }
+        bool filled = false;
+        if (direct) {
+            std::lock_guard<std::mutex> g(direct->mu);  // the caller cannot time out and leave while its buffer is being written
+            if (!direct->abandoned) {
+                if (!IoRead(direct->sink, h.bodyLen)) {
+                    break;
+                }
+                filled = true;
+            }
+        }
+        if (!filled) {
+            f.body.resize(h.bodyLen);
+            if (h.bodyLen > 0 && !IoRead(&f.body[0], h.bodyLen)) {
+                break;
+            }
         }
         if (f.type == MSG_GOODBYE) {
             goodbye_.store(true);  // the close that follows is the end of the job, not a failure

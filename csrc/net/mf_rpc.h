@@ -92,6 +92,9 @@ public:
     bool Running() const { return running_.load(); }
     // Thread-safe. Returns 0 when queued/sent, -1 if the link is gone.
     int Send(LinkId link, const Frame &f);
+    // A frame whose body is `payload` (f.body is ignored): on a plain link the bytes go to the socket from where they lie and
+    // only what the socket does not take at once is copied into the queue. The payload must stay valid during the call only.
+    int SendWithPayload(LinkId link, const Frame &f, const void *payload, size_t payloadLen);
     void CloseLink(LinkId link);
     size_t LinkCount();
 
@@ -138,6 +141,13 @@ public:
     void SetBrokenHandler(BrokenCb cb) { onBroken_ = std::move(cb); }
     // Blocking request. timeoutMs < 0 waits until the link breaks. Returns RPC_OK and fills reply, RPC_IO_ERROR or RPC_TIMEOUT.
     int Call(uint16_t type, const std::string &body, Frame *reply, int64_t timeoutMs);
+    // The same request with its body given as two pieces that are sent from where they lie (no intermediate copy), and,
+    // optionally, a buffer that receives the reply's body in place: if the reply carries exactly sinkLen bytes and result 0
+    // they are read from the socket straight into `sink` and reply->body stays empty; any other reply arrives in reply->body.
+    // Used by the bulk data path; `sink` must stay valid until the call returns (it does: a call that times out waits for a
+    // body that is being received at that moment).
+    int CallGather(uint16_t type, const void *head, size_t headLen, const void *payload, size_t payloadLen, void *sink, size_t sinkLen,
+                   Frame *reply, int64_t timeoutMs);
     // Sends a request whose replies (possibly many) are delivered to cb on the reader thread until Cancel(seq).
     // Returns the sequence number, or 0 on failure.
     uint32_t CallPersistent(uint16_t type, const std::string &body, PersistCb cb);
@@ -149,10 +159,14 @@ private:
         std::condition_variable cv;
         bool done{false};
         bool failed{false};
+        bool abandoned{false};  // the caller gave up: its sink must not be written any more
+        void *sink{nullptr};
+        size_t sinkLen{0};
         Frame reply;
         PersistCb persist;
     };
     int SendFrame(uint16_t type, uint32_t seq, const std::string &body);
+    int SendParts(uint16_t type, uint32_t seq, const void *head, size_t headLen, const void *payload, size_t payloadLen);
     void ReaderLoop();
     void FailAll();
     bool IoWrite(const void *p, size_t n);  // caller holds sendMu_ (or is the only thread: during Connect)

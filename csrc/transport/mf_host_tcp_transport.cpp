@@ -261,8 +261,11 @@ void HostTcpTransport::OnRequest(net::LinkId link, const net::Frame &f)
             std::memcpy((void *)h.addr, f.body.data() + sizeof(h), h.size);
             r.result = 0;
         } else {
-            r.body.assign((const char *)h.addr, h.size);
+            // The reply's body is the region itself: it goes to the socket from where it lies, still under the read lock.
             r.result = 0;
+            stats_.bytesServed.fetch_add(h.size);
+            server_.SendWithPayload(link, r, (const void *)h.addr, h.size);
+            return;
         }
     }
     if (r.result == 0) {
@@ -497,14 +500,10 @@ int HostTcpTransport::RunSliceOnce(const Slice &s)
         return BM_ERROR;
     }
     OneSidedHeader h{s.token, s.remote, s.size};
-    std::string body;
-    body.reserve(sizeof(h) + (s.write ? s.size : 0));
-    body.assign((const char *)&h, sizeof(h));
-    if (s.write) {
-        body.append((const char *)s.local, s.size);
-    }
     net::Frame reply;
-    int rc = link->Call(s.write ? kMsgWrite : kMsgRead, body, &reply, opt_.opTimeoutMs);
+    // A write's payload leaves from the caller's memory, a read's data arrives in it: no staging copy on this side.
+    int rc = s.write ? link->CallGather(kMsgWrite, &h, sizeof(h), (const void *)s.local, s.size, nullptr, 0, &reply, opt_.opTimeoutMs)
+                     : link->CallGather(kMsgRead, &h, sizeof(h), nullptr, 0, (void *)s.local, s.size, &reply, opt_.opTimeoutMs);
     if (rc == net::RPC_TIMEOUT) {
         return BM_TIMEOUT;
     }
@@ -515,10 +514,12 @@ int HostTcpTransport::RunSliceOnce(const Slice &s)
         return BM_INVALID_PARAM;  // the owner refused: retrying cannot help
     }
     if (!s.write) {
-        if (reply.body.size() != s.size) {
-            return BM_ERROR;
+        if (!reply.body.empty()) {  // not delivered in place (TLS session data interleaved, or an odd size): copy it over
+            if (reply.body.size() != s.size) {
+                return BM_ERROR;
+            }
+            std::memcpy((void *)s.local, reply.body.data(), s.size);
         }
-        std::memcpy((void *)s.local, reply.body.data(), s.size);
         stats_.bytesRead.fetch_add(s.size);
     } else {
         stats_.bytesWritten.fetch_add(s.size);
