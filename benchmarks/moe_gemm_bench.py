@@ -24,7 +24,9 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--tile-n", type=int, default=0, help="0 = let the launcher choose, 128 or 256")
+    ap.add_argument("--tile-n", type=int, default=0, help="0 = let the launcher choose; 128, 224 (bf16 epilogue only) or 256")
+    ap.add_argument("--cases", default="", help="comma list of case names to run (default: all)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the cuBLAS comparison")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     dev = "cuda"
@@ -33,6 +35,8 @@ def main():
              ("ffn1_prefill", 1024, 4096, 7168, "swiglu"), ("ffn2_prefill", 1024, 7168, 2048, "bf16")]
     if args.small:
         G, cases = 8, [("ffn1_small", 256, 4096, 7168, "swiglu")]
+    if args.cases:
+        cases = [c for c in cases if c[0] in args.cases.split(",")]
     rows_out = []
     stream = torch.cuda.current_stream()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -95,11 +99,11 @@ def main():
                     y = torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]
             return y
 
-        for _ in range(2):
+        for _ in range(0 if args.no_baseline else 2):
             base()
         torch.cuda.synchronize()
-        bt = []
-        for _ in range(max(3, args.iters // 2)):
+        bt = [0.0] if args.no_baseline else []
+        for _ in range(0 if args.no_baseline else max(3, args.iters // 2)):
             flush.fill_(1)
             a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a_ev.record(stream)
@@ -114,7 +118,7 @@ def main():
         err = float((got - ref[:counts[0]]).abs().max() / (ref[:counts[0]].abs().max() + 1e-9))
         weight_bytes = G * N * K
         row = {"case": name, "G": G, "rows_per_expert": per, "N": N, "K": K, "mode": mode, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
-               "weight_GBps": round(weight_bytes / ms / 1e6, 1), "cublas_bf16_ms": round(bms, 4), "speedup": round(bms / ms, 2),
+               "weight_GBps": round(weight_bytes / ms / 1e6, 1), "cublas_bf16_ms": round(bms, 4), "speedup": round(bms / ms, 2) if bms else None,
                "rel_err": round(err, 5), "status": int(status)}
         rows_out.append(row)
         print(json.dumps(row), flush=True)
