@@ -29,10 +29,10 @@ constexpr size_t kPdlMaxBytes = 32 * 1024;
 __global__ void __launch_bounds__(kThreads, 2)
 mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src, size_t n, size_t tileBytes)
 {
-    // Programmatic dependent launch: when the host sets the stream-serialisation attribute (small copies only), the next
-    // kernel of the stream may be scheduled while this one runs, and this kernel may have been scheduled while its
+    // Programmatic dependent launch: when the host sets the stream-serialisation attribute (copies up to kPdlMaxBytes: beyond it the overlap measured no gain), the
+    // next kernel of the stream may be scheduled while this one runs, and this kernel may have been scheduled while its
     // predecessor ran; the wait returns once the predecessor has completed and its writes are visible, so stream order
-    // is kept and only the launch latency between back-to-back small copies is hidden. Without the attribute both
+    // is kept and only the launch latency between back-to-back copies is hidden. Without the attribute both
     // instructions do nothing.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -51,9 +51,9 @@ mf_xcopy_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict
 }
 
 // ---------------------------------------------------------------------------------------------- bulk-copy (TMA) variant
-// For large copies whose two addresses are congruent modulo 16: each CTA streams 32 KiB tiles global → shared → global with
-// the bulk asynchronous copy engine of the SM (cp.async.bulk, no tensor map, no multicast), six tiles deep. One thread issues
-// loads, one thread issues stores; mbarriers hand tiles over. The SM's load/store units and register file stay out of the
+// For large copies whose two addresses are congruent modulo 16: each CTA streams tiles global → shared → global with the bulk
+// asynchronous copy engine of the SM (cp.async.bulk, no tensor map, no multicast) through a ring of shared-memory stages. One
+// thread issues loads, one thread issues stores; mbarriers hand tiles over. The SM's load/store units and register file stay out of the
 // data path, so the copy runs at what the memory system and NVLink deliver. Waits are bounded like everywhere else.
 // Default pipeline shapes, picked from a sweep of tile x stages x stores in flight x walk order x CTAs per SM on local HBM
 // copies (a shallow pipeline interleaves DRAM reads and writes more regularly than a deep one: 6 stages with 3 stores in
