@@ -1056,16 +1056,58 @@ void RpcClient::ReaderLoop()
             }
         }
         bool filled = false;
-        if (direct) {
-            std::lock_guard<std::mutex> g(direct->mu);  // the caller cannot time out and leave while its buffer is being written
-            if (!direct->abandoned) {
-                if (!IoRead(direct->sink, h.bodyLen)) {
+        if (direct && !tls_) {
+            // The caller's buffer is written only while the caller's mutex is held, and the mutex is held only while bytes
+            // that have already arrived are copied out of the socket: a caller whose wait runs out is never kept waiting by a
+            // peer that stalls in the middle of a body. If the caller has left, the rest goes to a scratch buffer.
+            size_t got = 0;
+            std::string scratch;
+            bool broken = false;
+            while (got < h.bodyLen && !broken) {
+                pollfd pfd{fd_, POLLIN, 0};
+                int pr = ::poll(&pfd, 1, 200);
+                if (pr < 0 && errno != EINTR) {
+                    broken = true;
                     break;
                 }
-                filled = true;
+                if (pr <= 0) {
+                    if (closing_.load()) {
+                        broken = true;
+                    }
+                    continue;
+                }
+                std::lock_guard<std::mutex> g(direct->mu);
+                char *dstp = nullptr;
+                if (!direct->abandoned && scratch.empty()) {
+                    dstp = (char *)direct->sink + got;
+                } else {
+                    if (scratch.empty()) {
+                        scratch.resize(h.bodyLen);  // what was already delivered in place is lost with the caller: nobody reads it
+                    }
+                    dstp = &scratch[got];
+                }
+                while (got < h.bodyLen) {  // take everything that has arrived; none of these calls blocks
+                    ssize_t n = ::recv(fd_, dstp, h.bodyLen - got, MSG_DONTWAIT);
+                    if (n > 0) {
+                        got += (size_t)n;
+                        dstp += n;
+                    } else {
+                        if (n == 0 || (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) {
+                            broken = true;
+                        }
+                        break;
+                    }
+                }
+            }
+            if (broken) {
+                break;
+            }
+            filled = scratch.empty();
+            if (!filled) {
+                f.body.swap(scratch);
             }
         }
-        if (!filled) {
+        if (!filled && f.body.size() != h.bodyLen) {
             f.body.resize(h.bodyLen);
             if (h.bodyLen > 0 && !IoRead(&f.body[0], h.bodyLen)) {
                 break;

@@ -144,8 +144,8 @@ public:
     // The same request with its body given as two pieces that are sent from where they lie (no intermediate copy), and,
     // optionally, a buffer that receives the reply's body in place: if the reply carries exactly sinkLen bytes and result 0
     // they are read from the socket straight into `sink` and reply->body stays empty; any other reply arrives in reply->body.
-    // Used by the bulk data path; `sink` must stay valid until the call returns (it does: a call that times out waits for a
-    // body that is being received at that moment).
+    // Used by the bulk data path; `sink` must stay valid until the call returns. On TLS links the reply always arrives in
+    // reply->body.
     int CallGather(uint16_t type, const void *head, size_t headLen, const void *payload, size_t payloadLen, void *sink, size_t sinkLen,
                    Frame *reply, int64_t timeoutMs);
     // Sends a request whose replies (possibly many) are delivered to cb on the reader thread until Cancel(seq).

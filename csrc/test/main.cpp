@@ -2,6 +2,10 @@
 // two-rank Big Memory run over a loopback config store — the shape of the reference's gtest suite
 // (test/ut/testcase/smem/smem_bm_test.cpp:209-416, acc_config_store_test.cpp:68-462). Build: `make`; sanitised: `make asan`.
 // Usage: mf_native_tests [filter-substring]. Exit code = number of failed cases.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
+#include <chrono>
 #include <sys/wait.h>
 #include <unistd.h>
 
@@ -175,6 +179,95 @@ static bool TestUtilLayer()
     EXPECT(rw.TryLockWrite());
     EXPECT(!rw.TryLockRead());
     rw.Unlock();
+    return ok;
+}
+
+// A peer that answers a bulk read with the frame header and half of the body and then goes quiet: the caller's wait must end
+// at its own limit (not when the peer feels like continuing), the half-filled buffer is simply abandoned, and when the rest
+// arrives later it is swallowed without touching the caller's memory.
+static bool TestStalledReplyBody()
+{
+    bool ok = true;
+    int lfd = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    EXPECT(::bind(lfd, (sockaddr *)&sa, sizeof(sa)) == 0 && ::listen(lfd, 1) == 0);
+    socklen_t sl = sizeof(sa);
+    getsockname(lfd, (sockaddr *)&sa, &sl);
+    const uint16_t port = ntohs(sa.sin_port);
+    constexpr uint32_t kBody = 1u << 20;
+    std::atomic<int> phase{0};
+    std::thread srv([&]() {
+        int fd = ::accept(lfd, nullptr, nullptr);
+        auto readn = [&](void *p, size_t n) {
+            size_t got = 0;
+            while (got < n) {
+                ssize_t r = ::recv(fd, (char *)p + got, n - got, 0);
+                if (r <= 0) {
+                    return false;
+                }
+                got += (size_t)r;
+            }
+            return true;
+        };
+        net::WireHeader h{};
+        char hello[sizeof(net::HelloBody)];
+        if (!readn(&h, sizeof(h)) || !readn(hello, sizeof(hello))) {
+            ::close(fd);
+            return;
+        }
+        net::WireHeader ack{net::kWireMagic, net::MSG_HELLO_ACK, 0, 0, h.seq};
+        ::send(fd, &ack, sizeof(ack), MSG_NOSIGNAL);
+        // the request: header + 24-byte body
+        char req[24];
+        if (!readn(&h, sizeof(h)) || h.bodyLen != sizeof(req) || !readn(req, sizeof(req))) {
+            ::close(fd);
+            return;
+        }
+        std::string body(kBody, 'Z');
+        net::WireHeader rh{net::kWireMagic, h.type, 0, kBody, h.seq};
+        ::send(fd, &rh, sizeof(rh), MSG_NOSIGNAL);
+        ::send(fd, body.data(), kBody / 2, MSG_NOSIGNAL);
+        phase.store(1);
+        while (phase.load() < 2) {
+            usleep(10 * 1000);  // stalled
+        }
+        ::send(fd, body.data() + kBody / 2, kBody / 2, MSG_NOSIGNAL);
+        phase.store(3);
+        char dummy;
+        ::recv(fd, &dummy, 1, 0);  // until the client closes
+        ::close(fd);
+    });
+    {
+        net::RpcClient c;
+        net::Endpoint to{"127.0.0.1", port, false};
+        EXPECT(c.Connect(to, 1, 3, 100) == 0);
+        std::vector<char> sink(kBody, 'a');
+        char head[24] = {0};
+        net::Frame reply;
+        auto t0 = std::chrono::steady_clock::now();
+        int rc = c.CallGather(0x0201, head, sizeof(head), nullptr, 0, sink.data(), sink.size(), &reply, 400);
+        double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        EXPECT(rc == net::RPC_TIMEOUT);
+        EXPECT(ms >= 350 && ms < 2000);
+        EXPECT(phase.load() == 1);
+        std::fill(sink.begin(), sink.end(), 'b');  // the caller reuses its memory
+        phase.store(2);
+        while (phase.load() < 3) {
+            usleep(10 * 1000);
+        }
+        usleep(300 * 1000);  // the late half has been read by now: into a scratch buffer, not into `sink`
+        bool untouched = true;
+        for (char ch : sink) {
+            untouched = untouched && ch == 'b';
+        }
+        EXPECT(untouched);
+        EXPECT(c.Connected());
+        c.Close();
+    }
+    srv.join();
+    ::close(lfd);
     return ok;
 }
 
@@ -391,6 +484,7 @@ int main(int argc, char **argv)
     std::vector<Case> cases = {
         {"codec", TestCodec},
         {"util_layer", TestUtilLayer},
+        {"rpc_stalled_reply_body", TestStalledReplyBody},
         {"va_manager_and_range_pool", TestVaAndPool},
         {"store_and_group_engine", TestStoreAndGroup},
         {"hybm_single_rank_host_pool", TestHybmSingleRankHostPool},
