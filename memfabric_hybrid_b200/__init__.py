@@ -32,7 +32,27 @@ TransferEngine = getattr(_pymf, "TransferEngine", None)
 TransferOpcode = getattr(_pymf, "TransferOpcode", None)
 TransDataOpType = getattr(_pymf, "TransDataOpType", None)
 
+
+
+def get_include_path() -> str:
+    """Directory of the public C / CUDA headers (`mf/*.h`, `mf/device/*.cuh`): the package's own copy when installed from a
+    release, the repository's `include/` when run from a source tree."""
+    import os
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    packaged = os.path.join(here, "include")
+    return packaged if os.path.isdir(packaged) else os.path.join(os.path.dirname(here), "include")
+
+
+def get_lib_path() -> str:
+    """Directory that holds libmf_core.so."""
+    import os
+
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
+
+
 __all__ = [
+    "get_include_path", "get_lib_path",
     "initialize", "uninitialize", "set_log_level", "set_extern_logger", "get_last_err_msg",
     "get_and_clear_last_err_msg", "set_conf_store_tls", "set_conf_store_tls_key", "create_config_store",
     "destroy_config_store", "version", "bm", "shm", "native", "TransferEngine", "TransferOpcode",

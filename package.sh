@@ -20,7 +20,8 @@ rm -rf "$STAGE"
 mkdir -p "$STAGE/lib" "$STAGE/include" "$STAGE/python" "$STAGE/examples" "$STAGE/benchmarks"
 cp memfabric_hybrid_b200/lib/libmf_core.so "$STAGE/lib/"
 cp -r include/mf "$STAGE/include/"
-rsync -a --exclude '__pycache__' memfabric_hybrid_b200 "$STAGE/python/" 2>/dev/null || cp -r memfabric_hybrid_b200 "$STAGE/python/"
+rsync -a --exclude '__pycache__' memfabric_hybrid_b200 memfabric_hybrid mf_adapter "$STAGE/python/" 2>/dev/null || cp -r memfabric_hybrid_b200 memfabric_hybrid mf_adapter "$STAGE/python/"
+cp -r include/mf "$STAGE/python/memfabric_hybrid_b200/include" 2>/dev/null || { mkdir -p "$STAGE/python/memfabric_hybrid_b200/include"; cp -r include/mf "$STAGE/python/memfabric_hybrid_b200/include/"; }
 cp -r examples/. "$STAGE/examples/"
 cp benchmarks/*.py benchmarks/*.cpp "$STAGE/benchmarks/"
 [ -x benchmarks/store_bench ] && cp benchmarks/store_bench "$STAGE/benchmarks/"

@@ -22,7 +22,7 @@ setup(
     name="memfabric_hybrid_b200",
     version="1.0.0",
     description="Blackwell-native memory fabric: pooled HBM/DRAM over a global virtual address space, xcopy, fused collectives",
-    packages=find_packages(include=["memfabric_hybrid_b200", "memfabric_hybrid_b200.*"]),
+    packages=find_packages(include=["memfabric_hybrid_b200", "memfabric_hybrid_b200.*", "memfabric_hybrid", "mf_adapter"]),
     package_data={"memfabric_hybrid_b200": ["lib/*.so", "*.so"]},
     include_package_data=True,
     cmdclass={"build_py": BuildNative},

@@ -145,3 +145,20 @@ def test_logger_hook_and_last_error(mf):
     assert mf.set_extern_logger(None) == 0
     assert mf.set_conf_store_tls(False) == 0 and mf.set_conf_store_tls(True, "x") != 0
     assert mf.version().startswith("memfabric-b200")
+
+
+def test_reference_package_names_resolve():
+    """Programs written against the reference import `memfabric_hybrid` (or the transfer-only `mf_adapter`)."""
+    import memfabric_hybrid as ref_name
+    import memfabric_hybrid_b200 as mf
+    import mf_adapter
+
+    for name in ("bm", "shm", "TransferEngine", "TransferOpcode", "create_config_store", "initialize", "uninitialize", "set_log_level",
+                 "set_extern_logger", "get_last_err_msg", "set_conf_store_tls", "set_conf_store_tls_key", "get_and_clear_last_err_msg",
+                 "get_include_path", "get_lib_path"):
+        assert getattr(ref_name, name) is getattr(mf, name), name
+    assert mf_adapter.TransferEngine is mf.TransferEngine and mf_adapter.create_config_store is mf.create_config_store
+    import os
+
+    assert os.path.isfile(os.path.join(mf.get_include_path(), "mf", "mf_bm.h"))
+    assert os.path.isfile(os.path.join(mf.get_lib_path(), "libmf_core.so"))
