@@ -95,10 +95,15 @@ int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, con
 // mantissa bits are ignored (only the exponent is used). Epilogues: MF_GEMM_EPI_BF16 (out bf16 [rowsTotal, N]),
 // MF_GEMM_EPI_SWIGLU (out bf16 [rowsTotal, N/2]) and MF_GEMM_EPI_SWIGLU_FP8: out e4m3 [rowsTotal, N/2] plus outSf
 // [rowsTotal, N/64] UE8M0 bytes, one per 32 outputs, i.e. exactly the a / aSf operands of a following GEMM with K = N/2.
-// tileN: 0 = pick from the sizes, 128 or 256 (256 needs N % 256 == 0). a, b, out and aSf must be 16-byte aligned.
+// tileN: 0 = pick from the sizes; 128, 256 (N % 256 == 0), 224 (N % 224 == 0, bf16 epilogue only: two accumulators), or 512 =
+// the two-SM kernel (256 x 256 tiles computed by pairs of CTAs with cta_group::2, N % 256 == 0). a, b, out and aSf must be
+// 16-byte aligned.
 int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
                              const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
                              int *status, int ctas, mf_stream_t stream);
+int mf_k_moe_grouped_gemm_mx_2sm(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
+                                 const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas,
+                                 mf_stream_t stream);
 
 // ------------------------------------------------------------------------------------------------ MoE dispatch / combine (K5a, K5c)
 

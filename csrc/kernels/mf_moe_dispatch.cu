@@ -289,7 +289,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 3)
 mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int K, int EL, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
@@ -353,26 +353,48 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
             }
         }
         char *dst = reinterpret_cast<char *>(mf_shm_peer(m, a.retY, src)) + ((size_t)meta.y * K + k) * H * 2;
+        // The lane's four vectors of the chunk are loaded together for every addend, so that four 16-byte loads per lane are
+        // in flight (the rows of a group lie far apart: latency, not bandwidth, would pace a one-at-a-time loop).
         const int vEnd = min(vecs, (ch + 1) * 128);
-        for (int v = ch * 128 + lane; v < vEnd; v += 32) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int i = 0; i < n; i++) {
-                const uint4 raw = mf_ld16(reinterpret_cast<const char *>(a.y) + (size_t)rowOf[i] * H * 2 + (size_t)v * 16);
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+        const int v0 = ch * 128 + lane;
+        float acc[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                acc[j][q] = 0.f;
+            }
+        }
+        for (int i = 0; i < n; i++) {
+            const char *rowp = reinterpret_cast<const char *>(a.y) + (size_t)rowOf[i] * H * 2;
+            uint4 raw[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                raw[j] = v0 + 32 * j < vEnd ? mf_ld16(rowp + (size_t)(v0 + 32 * j) * 16) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            const float w = wOf[i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[j]);
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     float2 f = __bfloat1622float2(h[q]);
-                    acc[2 * q] = fmaf(wOf[i], f.x, acc[2 * q]);
-                    acc[2 * q + 1] = fmaf(wOf[i], f.y, acc[2 * q + 1]);
+                    acc[j][2 * q] = fmaf(w, f.x, acc[j][2 * q]);
+                    acc[j][2 * q + 1] = fmaf(w, f.y, acc[j][2 * q + 1]);
                 }
             }
-            uint4 pk;
-            __nv_bfloat162 *hp = reinterpret_cast<__nv_bfloat162 *>(&pk);
+        }
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                hp[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+        for (int j = 0; j < 4; j++) {
+            if (v0 + 32 * j < vEnd) {
+                uint4 pk;
+                __nv_bfloat162 *hp = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    hp[q] = __floats2bfloat162_rn(acc[j][2 * q], acc[j][2 * q + 1]);
+                }
+                mf_st16(dst + (size_t)(v0 + 32 * j) * 16, pk);
             }
-            mf_st16(dst + (size_t)v * 16, pk);
         }
     }
     __threadfence_system();
@@ -409,28 +431,49 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
                 leaders |= 1u << k;
             }
         }
-        for (int v = lane; v < vecs; v += 32) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        // Four vectors per lane and trip, loaded together for every partial sum (same reason as above).
+        for (int vb = lane; vb < vecs; vb += 128) {
+            float acc[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    acc[j][q] = 0.f;
+                }
+            }
             for (int k = 0; k < K; k++) {
                 if ((leaders >> k & 1u) == 0) {
                     continue;
                 }
-                const uint4 raw = mf_ld16_coherent(base + (size_t)k * H * 2 + (size_t)v * 16);
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                const char *rowp = base + (size_t)k * H * 2;
+                uint4 raw[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float2 f = __bfloat1622float2(h[i]);
-                    acc[2 * i] += f.x;
-                    acc[2 * i + 1] += f.y;
+                for (int j = 0; j < 4; j++) {
+                    raw[j] = vb + 32 * j < vecs ? mf_ld16_coherent(rowp + (size_t)(vb + 32 * j) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[j]);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float2 f = __bfloat1622float2(h[i]);
+                        acc[j][2 * i] += f.x;
+                        acc[j][2 * i + 1] += f.y;
+                    }
                 }
             }
-            uint4 pk;
-            __nv_bfloat162 *hp = reinterpret_cast<__nv_bfloat162 *>(&pk);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                hp[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            for (int j = 0; j < 4; j++) {
+                if (vb + 32 * j < vecs) {
+                    uint4 pk;
+                    __nv_bfloat162 *hp = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        hp[i] = __floats2bfloat162_rn(acc[j][2 * i], acc[j][2 * i + 1]);
+                    }
+                    mf_st16(o + (size_t)(vb + 32 * j) * 16, pk);
+                }
             }
-            mf_st16(o + (size_t)v * 16, pk);
         }
     }
 }

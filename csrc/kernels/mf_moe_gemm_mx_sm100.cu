@@ -490,6 +490,9 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
                                         int *status, int ctas, mf_stream_t stream)
 {
     const int epi = mode & 15;
+    if (tileN == 512) {
+        return mf_k_moe_grouped_gemm_mx_2sm(a, aSf, b, bScale, out, outSf, groupOffset, groupCount, G, rowsTotal, N, K, mode, status, ctas, stream);
+    }
     if (a == nullptr || b == nullptr || out == nullptr || aSf == nullptr || bScale == nullptr || groupOffset == nullptr || groupCount == nullptr ||
         G < 1 || G > kMaxGroups || rowsTotal < 1 || N <= 0 || K <= 0 || N % 128 != 0 || K % BK != 0 ||
         (epi != MF_GEMM_EPI_BF16 && epi != MF_GEMM_EPI_SWIGLU && epi != MF_GEMM_EPI_SWIGLU_FP8) || (epi == MF_GEMM_EPI_SWIGLU_FP8 && outSf == nullptr) ||

@@ -107,6 +107,9 @@ def _mx_cases():
     cases = [(c, n, k, t) for (c, n, k) in base for t in (128, 256)]
     # 224-column tiles (two accumulators, a tile spans up to three 128-column weight blocks): N must be a multiple of 896
     cases += [([128], 896, 128, 224), ([1, 300, 0, 129], 896, 1024, 224), ([700, 256, 1, 64], 1792, 2048, 224)]
+    # the two-SM kernel (tile_n 512 = 256 x 256 tiles by CTA pairs): row counts around the 128- and 256-row boundaries
+    cases += [([256], 256, 128, 512), ([128], 256, 512, 512), ([1], 256, 384, 512), ([200, 0, 37, 128, 257], 512, 1024, 512),
+              ([1000, 130, 257, 640], 768, 2048, 512)]
     return cases
 
 
