@@ -512,13 +512,7 @@ extern "C" int mf_k_moe_grouped_gemm_mx_2sm(const void *a, const uint32_t *aSf, 
     if (sms < 2) {
         return MF_K_LAUNCH_FAILED;
     }
-    int grid = ctas > 0 && ctas < sms ? ctas : sms;
-    grid &= ~1;
-    if (grid < 2) {
-        return MF_K_INVALID;
-    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = (cudaStream_t)stream;
@@ -529,6 +523,27 @@ extern "C" int mf_k_moe_grouped_gemm_mx_2sm(const void *a, const uint32_t *aSf, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // The kernel is persistent with a static tile walk: every pair must be resident from the start, or the pairs of a second
+    // wave would only begin when a first-wave pair has finished ALL its tiles. Not every SM can be paired (a pair needs two
+    // free SMs of one cluster-scheduling group), so the number of pairs that fit at once is asked for, not assumed.
+    static int maxPairs = 0;
+    if (maxPairs == 0) {
+        cfg.gridDim = dim3((unsigned)(sms & ~1));
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, mf_moe_grouped_gemm_mx2_kernel, &cfg) != cudaSuccess || n < 1) {
+            (void)cudaGetLastError();
+            return MF_K_LAUNCH_FAILED;
+        }
+        maxPairs = n;
+    }
+    int pairsWanted = (ctas > 0 && ctas < sms ? ctas : sms) / 2;
+    if (pairsWanted > maxPairs) {
+        pairsWanted = maxPairs;
+    }
+    if (pairsWanted < 1) {
+        return MF_K_INVALID;
+    }
+    cfg.gridDim = dim3((unsigned)(2 * pairsWanted));
     if (cudaLaunchKernelEx(&cfg, mf_moe_grouped_gemm_mx2_kernel, mapA, mapB, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return MF_K_LAUNCH_FAILED;

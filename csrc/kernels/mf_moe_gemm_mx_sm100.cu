@@ -83,7 +83,6 @@ struct MxParams {
     const int *groupCount;
     int *status;
     int G, N, K, mode, rowsTotal;
-    int l2Ahead;  // weight tiles are asked into L2 this many K blocks before their load into shared memory (0 = off)
 };
 
 __device__ __forceinline__ float Silu(float x) { return x / (1.f + __expf(-x)); }
@@ -167,25 +166,8 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                 decode(tile, g, mt, nt);
                 const int rowA = p.groupOffset[g] + mt * BM;
                 const int rowB = g * p.N + nt * BN;
-                // Where this CTA's NEXT tile reads its weights: the prefetch runs across the tile boundary.
-                int rowBNext = -1;
-                if (p.l2Ahead > 0 && tile + (int)gridDim.x < totalTiles) {
-                    int g2, mt2, nt2;
-                    decode(tile + (int)gridDim.x, g2, mt2, nt2);
-                    rowBNext = g2 * p.N + nt2 * BN;
-                }
                 for (int kb = 0; kb < KB; kb++, it++) {
                     const uint32_t st = it % C::kStages, ph = (it / C::kStages) & 1;
-                    if (p.l2Ahead > 0) {
-                        // The ring holds kStages K blocks; the weights of the block l2Ahead further on are pulled into L2 now, so
-                        // that its load into shared memory (issued when a stage frees up) does not wait for DRAM.
-                        const int kbAhead = kb + p.l2Ahead;
-                        if (kbAhead < KB) {
-                            TmaPrefetchL2(&tmapB, kbAhead * BK, rowB);
-                        } else if (rowBNext >= 0 && kbAhead - KB < KB) {
-                            TmaPrefetchL2(&tmapB, (kbAhead - KB) * BK, rowBNext);
-                        }
-                    }
                     if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
                         break;
                     }
@@ -540,12 +522,6 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
     p.K = K;
     p.mode = mode;
     p.rowsTotal = rowsTotal;
-    static const int l2Ahead = []() {
-        const char *e = getenv("MF_GEMM_L2_AHEAD");
-        const int v = e != nullptr ? atoi(e) : 0;
-        return v < 0 ? 0 : (v > 64 ? 64 : v);
-    }();
-    p.l2Ahead = l2Ahead;
     if (tileN == 224) {
         return Launch<224>(mapA, mapB, p, ctas, (cudaStream_t)stream);
     }

@@ -83,13 +83,6 @@ __device__ __forceinline__ void TmaLoad2D(void *smemDst, const CUtensorMap *m, u
                  : "memory");
 }
 
-// Asks for the same tile to be brought into L2 only (no shared memory, no completion): a later TmaLoad2D of it then finds it
-// there instead of waiting for DRAM. Same alignment rule for c0.
-__device__ __forceinline__ void TmaPrefetchL2(const CUtensorMap *m, int c0, int c1)
-{
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"((uint64_t)m), "r"(c0), "r"(c1) : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------- TMEM
 // Allocates `cols` (power of two, >= 32) TMEM columns; the base address is written to *smemSlot. Whole warp must call.
 __device__ __forceinline__ void TmemAlloc(uint32_t *smemSlot, uint32_t cols)
