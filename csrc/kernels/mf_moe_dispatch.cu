@@ -65,6 +65,13 @@ __device__ __forceinline__ int ReadAbort(int *status, int *smemFlag)
     return v;
 }
 
+// Meta words are written by other GPUs during this kernel: read them past the non-coherent path.
+__device__ __forceinline__ int4 mf_ld_meta(const int4 *p)
+{
+    const uint4 u = mf_ld16_coherent(p);
+    return make_int4((int)u.x, (int)u.y, (int)u.z, (int)u.w);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
 {
@@ -241,9 +248,13 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
                 }
             }
             const bool leader = mySlot >= 0 && before % (MF_MOE_MAX_SIBLINGS + 1) == 0;
+            // Only the leader of a (token, owner) group carries the payload over the link; the owner copies it into the
+            // followers' rows after everything has landed (phase (e)). A token routed to several experts of one rank crosses
+            // NVLink once.
+            const uint32_t leadMask = __ballot_sync(0xffffffffu, leader);
             for (int k = 0; k < K; k++) {
                 const int slot = __shfl_sync(0xffffffffu, mySlot, k);
-                if (slot < 0) {
+                if (slot < 0 || (leadMask >> k & 1u) == 0) {
                     continue;
                 }
                 const uint32_t d = (uint32_t)__shfl_sync(0xffffffffu, myOwner, k);
@@ -285,6 +296,44 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
         for (int e = threadIdx.x; e < E; e += kThreads) {
             a.localCnt[e] = 0;
             a.cursor[e] = 0;
+        }
+    }
+    // ---- (e) every leader row that arrived here is copied into the rows of its followers (local memory only)
+    grid.sync();
+    if (dead || ReadAbort(a.status, &abortFlag) != 0) {
+        return;
+    }
+    {
+        const int warpsTotal = gridDim.x * kWarps;
+        const int rowsHere = min(starts[me * EL + EL - 1] + ((totals[me * EL + EL - 1] + 127) & ~127), a.cap);
+        const unsigned char *rx = reinterpret_cast<const unsigned char *>(a.recvX);
+        for (int r = blockIdx.x * kWarps + warp; r < rowsHere; r += warpsTotal) {
+            int el = 0;
+            while (el + 1 < EL && starts[me * EL + el + 1] <= r) {
+                el++;
+            }
+            if (r - starts[me * EL + el] >= totals[me * EL + el]) {
+                continue;  // padding row: whatever it holds is from an earlier call
+            }
+            const int4 meta = mf_ld_meta(a.recvMeta + r);
+            const int nsib = (meta.z >> 8) & 0xff;
+            if ((meta.z & MF_MOE_META_FOLLOWER) != 0 || nsib == 0 || nsib > MF_MOE_MAX_SIBLINGS) {
+                continue;
+            }
+            const int2 *sd = a.recvSib + (size_t)r * MF_MOE_MAX_SIBLINGS;
+            for (int i = 0; i < nsib; i++) {
+                const int fr = sd[i].x;
+                if (fr < 0 || fr >= rowsHere || fr == r) {
+                    continue;
+                }
+                unsigned char *dx = reinterpret_cast<unsigned char *>(a.recvX) + (size_t)fr * H;
+                for (int v = lane; v < H / 16; v += 32) {
+                    mf_st16(dx + (size_t)v * 16, mf_ld16_coherent(rx + (size_t)r * H + (size_t)v * 16));
+                }
+                for (int v = lane; v < nblk; v += 32) {
+                    a.recvSf[(size_t)fr * nblk + v] = ((volatile uint32_t *)a.recvSf)[(size_t)r * nblk + v];
+                }
+            }
         }
     }
 }
