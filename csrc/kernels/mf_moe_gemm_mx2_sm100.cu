@@ -226,76 +226,98 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ scale-factor producer (both CTAs)
+        // One work item (tile, group of up to four K blocks) of lookahead: see the one-SM kernel.
         const uint32_t leaderFull0 = MapToCta(SmemAddr(&s.full[0]), 0);
-        uint32_t it = 0;
+        struct SfWords {
+            uint32_t wa[4][4];
+            uint32_t wb[2][4];
+        };
         const bool vec = (KB & 3) == 0;
-        for (int tile = pairId; tile < totalTiles && *abortFlag == 0; tile += pairs) {
+        auto fetch = [&](int tile, int kb0, SfWords &w) {
             int g, mt, nt;
             decode(tile, g, mt, nt);
             const int rowBase = p.groupOffset[g] + mt * 2 * BM + (int)cta * BM + lane;
-            const float *pb = p.bScale + ((size_t)g * (p.N / 128) + (size_t)nt * 2) * KB;
-            bool ok = true;
-            for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
-                uint32_t wa[4][4];
-                uint32_t wb[2][4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int r = rowBase + 32 * j;
-                    if (r < p.rowsTotal) {
-                        const uint32_t *src = p.aSf + (size_t)r * KB + kb0;
-                        if (vec) {
-                            const uint4 q = *reinterpret_cast<const uint4 *>(src);
-                            wa[j][0] = q.x;
-                            wa[j][1] = q.y;
-                            wa[j][2] = q.z;
-                            wa[j][3] = q.w;
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                wa[j][k] = kb0 + k < KB ? src[k] : kSfOne;
-                            }
-                        }
+            for (int j = 0; j < 4; j++) {
+                const int r = rowBase + 32 * j;
+                if (r < p.rowsTotal) {
+                    const uint32_t *src = p.aSf + (size_t)r * KB + kb0;
+                    if (vec) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(src);
+                        w.wa[j][0] = q.x;
+                        w.wa[j][1] = q.y;
+                        w.wa[j][2] = q.z;
+                        w.wa[j][3] = q.w;
                     } else {
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            wa[j][k] = kSfOne;
+                            w.wa[j][k] = kb0 + k < KB ? src[k] : kSfOne;
                         }
                     }
-                }
-#pragma unroll
-                for (int a = 0; a < 2; a++) {
+                } else {
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
-                        const float f = kb0 + k < KB ? pb[(size_t)a * KB + kb0 + k] : 1.f;
-                        wb[a][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
+                        w.wa[j][k] = kSfOne;
                     }
                 }
+            }
+            const float *pb = p.bScale + ((size_t)g * (p.N / 128) + (size_t)nt * 2) * KB;
+#pragma unroll
+            for (int a = 0; a < 2; a++) {
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
-                    if (kb0 + k >= KB) {
-                        break;
-                    }
-                    const uint32_t st = it % kStages, ph = (it / kStages) & 1;
-                    if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
-                        ok = false;
-                        break;
-                    }
-                    *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(wa[0][k], wa[1][k], wa[2][k], wa[3][k]);
-#pragma unroll
-                    for (int a = 0; a < 2; a++) {
-                        *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(wb[a][k], wb[a][k], wb[a][k], wb[a][k]);
-                    }
-                    FenceProxyAsyncShared();
-                    __syncwarp();
-                    if (lane == 0) {
-                        RemoteArrive(leaderFull0 + st * (uint32_t)sizeof(uint64_t));  // also the way the leader arrives on its own barrier
-                    }
-                    it++;
+                    const float f = kb0 + k < KB ? pb[(size_t)a * KB + kb0 + k] : 1.f;
+                    w.wb[a][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
                 }
+            }
+        };
+        uint32_t it = 0;
+        int tile = pairId, kb0 = 0;
+        SfWords cur, nxt;
+        bool have = tile < totalTiles;
+        if (have) {
+            fetch(tile, kb0, cur);
+        }
+        while (have && *abortFlag == 0) {
+            int tileN = tile, kbN = kb0 + 4;
+            if (kbN >= KB) {
+                tileN = tile + pairs;
+                kbN = 0;
+            }
+            const bool haveNext = tileN < totalTiles;
+            if (haveNext) {
+                fetch(tileN, kbN, nxt);
+            }
+            bool ok = true;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (kb0 + k >= KB) {
+                    break;
+                }
+                const uint32_t st = it % kStages, ph = (it / kStages) & 1;
+                if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
+                    ok = false;
+                    break;
+                }
+                *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(cur.wa[0][k], cur.wa[1][k], cur.wa[2][k], cur.wa[3][k]);
+#pragma unroll
+                for (int a = 0; a < 2; a++) {
+                    *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(cur.wb[a][k], cur.wb[a][k], cur.wb[a][k], cur.wb[a][k]);
+                }
+                FenceProxyAsyncShared();
+                __syncwarp();
+                if (lane == 0) {
+                    RemoteArrive(leaderFull0 + st * (uint32_t)sizeof(uint64_t));  // also the way the leader arrives on its own barrier
+                }
+                it++;
             }
             if (!ok) {
                 break;
             }
+            cur = nxt;
+            tile = tileN;
+            kb0 = kbN;
+            have = haveNext;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)

@@ -50,6 +50,7 @@ struct Cfg {
     static constexpr int kStages = BN == 128 ? 6 : 4;
     static constexpr int kAccBufs = BN == 256 ? 1 : 2;
     static constexpr int kAtomsB = (BN + 127) / 128;
+    static constexpr int kSfbWords = BN % 128 == 0 ? 1 : 4;  // distinct weight-scale words per 128-column atom
     static constexpr int kATile = BM * BK;  // bytes (fp8)
     static constexpr int kBTile = BN * BK;
     // TMEM columns: the accumulators come first, then four columns of A scale factors, then four per 128 columns of B.
@@ -179,93 +180,107 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ scale-factor producer
-        uint32_t it = 0;
+        // Work item = (tile, group of up to four K blocks). The scale words of item i+1 are requested from global memory before
+        // item i is laid out, so their latency (the A scales are read once and come from DRAM) is hidden behind the stage
+        // hand-shakes instead of being paid once per group on the path that feeds the MMAs.
+        struct SfWords {
+            uint32_t wa[4][4];
+            uint32_t wb[C::kAtomsB][C::kSfbWords][4];
+        };
         const bool vec = (KB & 3) == 0;
-        for (int tile = blockIdx.x; tile < totalTiles && *abortFlag == 0; tile += gridDim.x) {
+        auto fetch = [&](int tile, int kb0, SfWords &w) {
             int g, mt, nt;
             decode(tile, g, mt, nt);
             const int rowBase = p.groupOffset[g] + mt * BM + lane;
-            // Word j of atom a holds the scale of tile columns a*128 + 32*j .. +31, which lie inside ONE 128-column weight
-            // block (tiles start at multiples of 32); with BN = 224 a tile spans up to three blocks. nullptr = past the tile.
-            const float *pbw[C::kAtomsB][4];
 #pragma unroll
-            for (int a = 0; a < C::kAtomsB; a++) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int cin = a * 128 + 32 * j;
-                    pbw[a][j] = cin < BN ? p.bScale + ((size_t)g * (p.N / 128) + (size_t)((nt * BN + cin) / 128)) * KB : nullptr;
-                }
-            }
-            bool ok = true;
-            for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
-                // Scale words of rows lane, lane+32, lane+64, lane+96 for up to four K blocks, and the weight-block scales.
-                uint32_t wa[4][4];
-                uint32_t wb[C::kAtomsB][4][4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int r = rowBase + 32 * j;
-                    if (r < p.rowsTotal) {
-                        const uint32_t *src = p.aSf + (size_t)r * KB + kb0;
-                        if (vec) {
-                            const uint4 q = *reinterpret_cast<const uint4 *>(src);
-                            wa[j][0] = q.x;
-                            wa[j][1] = q.y;
-                            wa[j][2] = q.z;
-                            wa[j][3] = q.w;
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                wa[j][k] = kb0 + k < KB ? src[k] : kSfOne;
-                            }
-                        }
+            for (int j = 0; j < 4; j++) {
+                const int r = rowBase + 32 * j;
+                if (r < p.rowsTotal) {
+                    const uint32_t *src = p.aSf + (size_t)r * KB + kb0;
+                    if (vec) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(src);
+                        w.wa[j][0] = q.x;
+                        w.wa[j][1] = q.y;
+                        w.wa[j][2] = q.z;
+                        w.wa[j][3] = q.w;
                     } else {
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            wa[j][k] = kSfOne;
+                            w.wa[j][k] = kb0 + k < KB ? src[k] : kSfOne;
                         }
                     }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        w.wa[j][k] = kSfOne;
+                    }
                 }
+            }
+            // Word j of atom a holds the scale of tile columns a*128 + 32*j .. +31, which lie inside ONE 128-column weight
+            // block (tiles start at multiples of 32); with BN = 224 a tile spans up to three blocks.
+#pragma unroll
+            for (int a = 0; a < C::kAtomsB; a++) {
+#pragma unroll
+                for (int j = 0; j < C::kSfbWords; j++) {
+                    const int cin = a * 128 + 32 * j;
+                    const float *pb = p.bScale + ((size_t)g * (p.N / 128) + (size_t)((nt * BN + cin) / 128)) * KB;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float f = (cin < BN && kb0 + k < KB) ? pb[kb0 + k] : 1.f;
+                        w.wb[a][j][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
+                    }
+                }
+            }
+        };
+        uint32_t it = 0;
+        int tile = blockIdx.x, kb0 = 0;
+        SfWords cur, nxt;
+        bool have = tile < totalTiles;
+        if (have) {
+            fetch(tile, kb0, cur);
+        }
+        while (have && *abortFlag == 0) {
+            int tileN = tile, kbN = kb0 + 4;
+            if (kbN >= KB) {
+                tileN = tile + (int)gridDim.x;
+                kbN = 0;
+            }
+            const bool haveNext = tileN < totalTiles;
+            if (haveNext) {
+                fetch(tileN, kbN, nxt);
+            }
+            bool ok = true;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (kb0 + k >= KB) {
+                    break;
+                }
+                const uint32_t st = it % C::kStages, ph = (it / C::kStages) & 1;
+                if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
+                    ok = false;
+                    break;
+                }
+                *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(cur.wa[0][k], cur.wa[1][k], cur.wa[2][k], cur.wa[3][k]);
 #pragma unroll
                 for (int a = 0; a < C::kAtomsB; a++) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            if (BN % 128 == 0 && j > 0) {
-                                wb[a][j][k] = wb[a][0][k];  // the whole atom lies in one weight block
-                            } else {
-                                const float f = (pbw[a][j] != nullptr && kb0 + k < KB) ? pbw[a][j][kb0 + k] : 1.f;
-                                wb[a][j][k] = ((__float_as_uint(f) >> 23) & 0xffu) * 0x01010101u;
-                            }
-                        }
-                    }
+                    // with one word per atom (the atom lies in one weight block) all four lanes-of-32 groups share it
+                    *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) =
+                        make_uint4(cur.wb[a][0][k], cur.wb[a][1 % C::kSfbWords][k], cur.wb[a][2 % C::kSfbWords][k], cur.wb[a][3 % C::kSfbWords][k]);
                 }
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    if (kb0 + k >= KB) {
-                        break;
-                    }
-                    const uint32_t st = it % C::kStages, ph = (it / C::kStages) & 1;
-                    if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
-                        ok = false;
-                        break;
-                    }
-                    *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(wa[0][k], wa[1][k], wa[2][k], wa[3][k]);
-#pragma unroll
-                    for (int a = 0; a < C::kAtomsB; a++) {
-                        *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(wb[a][0][k], wb[a][1][k], wb[a][2][k], wb[a][3][k]);
-                    }
-                    FenceProxyAsyncShared();
-                    __syncwarp();
-                    if (lane == 0) {
-                        MbarArrive(&s.full[st]);
-                    }
-                    it++;
+                FenceProxyAsyncShared();
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&s.full[st]);
                 }
+                it++;
             }
             if (!ok) {
                 break;
             }
+            cur = nxt;
+            tile = tileN;
+            kb0 = kbN;
+            have = haveNext;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
