@@ -276,6 +276,15 @@ def moe_layer(heap, token_list: List[int], hidden: int = 7168, experts_per_rank:
         layer.experts()
         row["combine_us"] = round(timed_us(lambda: (layer.dispatch(x, idx, w), layer.combine(T)), it) - row["dispatch_us"], 1)
         row["status"] = layer.check_status()
+        # Arrival mode: no closing barrier in dispatch, the first GEMM starts each tile when its rows have landed. Only the whole
+        # layer is timed in this mode (two dispatches must be separated by a consumer that waited for every tile).
+        plain = layer(x, idx, w).clone()
+        layer.overlap = True
+        row["fused_total_overlap_us"] = round(timed_us(lambda: layer(x, idx, w), it), 1)
+        row["overlap_max_abs_diff"] = float((layer(x, idx, w).float() - plain.float()).abs().max())
+        row["overlap_status"] = layer.check_status()
+        barrier()
+        layer.overlap = False
         flops = 2.0 * T * K * (H * 2 * I + I * H)
         row["gemm_tflops_fp8"] = round(flops / (row["experts_us"] * 1e-6) / 1e12, 1)
         if world > 1:

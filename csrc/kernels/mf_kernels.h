@@ -101,6 +101,15 @@ int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, con
 int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
                              const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
                              int *status, int ctas, mf_stream_t stream);
+// The same kernel driven by arrival counters: tile (group g, rows [off + 128 m, +128)) starts when arrive[(off + 128 m) / 128]
+// has reached the number of valid rows of the tile (an acquire load of system scope, so what other GPUs stored into those
+// rows before counting them is visible to the loads of the tile). waitNs bounds every such wait (0 = 2 s); on expiry *status
+// becomes MF_K_GEMM_ARRIVAL_EXPIRED and the kernel drains and returns. A non-zero *status at launch (a failed dispatch) turns
+// the waits off. tileN 512 is not available here.
+enum { MF_K_GEMM_PIPELINE_EXPIRED = 3, MF_K_GEMM_ARRIVAL_EXPIRED = 4 };
+int mf_k_moe_grouped_gemm_mx_gated(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
+                                   const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
+                                   const int *arrive, uint64_t waitNs, int *status, int ctas, mf_stream_t stream);
 int mf_k_moe_grouped_gemm_mx_2sm(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
                                  const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int *status, int ctas,
                                  mf_stream_t stream);
@@ -113,7 +122,8 @@ typedef struct {
     const void *x;        // [T, H] bf16 tokens of this rank
     const int *topkIdx;   // [T, K] global expert ids
     const float *topkW;   // [T, K] renormalised routing weights
-    int *cnt;             // heap: [R][E] pair counts, row s written by rank s on every rank
+    int *cnt;             // heap: [R][E] pair counts, row s written by rank s on every rank ([2][R][E] when `arrive` is set:
+                          // calls alternate between the halves, since no closing barrier separates them)
     void *recvX;          // heap: [cap][H] e4m3
     uint32_t *recvSf;     // heap: [cap][H/128] scale words: the UE8M0 exponent byte of the 1x128 block, four times
     int4 *recvMeta;       // heap: [cap] {source rank, token, k | siblings << 8 | MF_MOE_META_FOLLOWER, weight bits}
@@ -124,6 +134,9 @@ typedef struct {
     int *expertCount;     // out: [E/R] valid rows of each local expert
     int *sendSlot;        // out (optional): [T, K] row each pair was written to on its owner
     int *status;          // device int, zero before launch
+    int *arrive;          // heap, optional: [cap / 128] rows landed in each 128-row tile of the receive buffer (arrival mode: no
+                          // closing barrier; the consumer waits per tile, see mf_k_moe_grouped_gemm_mx_gated). Between two
+                          // dispatches in this mode a consumer must have waited for every tile of the first.
     int T;
     int cap;
 } mf_moe_dispatch_args_t;

@@ -12,6 +12,10 @@
 //           published never points past the buffer.
 //           A token whose top-k holds several experts of the same owner tells that owner, in the record of the first of
 //           them (the "leader"), where its sibling rows are.
+//           Arrival mode (args.arrive set): instead of (d) every row that has landed is counted, with release semantics, in a
+//           counter of its 128-row tile on the owner; the kernel ends without a closing barrier and the grouped GEMM that
+//           follows starts each tile when the counter of that tile is complete (mf_k_moe_grouped_gemm_mx_gated), so an owner
+//           computes on what has arrived while slower senders are still pushing. Every pair carries its payload in this mode.
 // combine   each expert owner reduces the sibling rows of a token with their routing weights (fp32) and pushes ONE row
 //           per (token, owner) back to the source rank's landing zone [token][k of the leader][hidden]; after a barrier the
 //           source adds the partial sums of the owners in fixed k order (fp32, deterministic) and writes bf16. A top-8
@@ -89,7 +93,8 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     const size_t stagePerWarp = (size_t)H + (size_t)nblk * 4;
     __shared__ int abortFlag;
     if (mf_check_bounds_enabled(m) &&
-        !(mf_shm_in_own_window(m, a.cnt, (uint64_t)R * E * 4) && mf_shm_in_own_window(m, a.recvX, (uint64_t)a.cap * H) &&
+        !(mf_shm_in_own_window(m, a.cnt, (uint64_t)(a.arrive != nullptr ? 2 : 1) * R * E * 4) &&
+          (a.arrive == nullptr || mf_shm_in_own_window(m, a.arrive, (uint64_t)(a.cap / 128) * 4)) && mf_shm_in_own_window(m, a.recvX, (uint64_t)a.cap * H) &&
           mf_shm_in_own_window(m, a.recvSf, (uint64_t)a.cap * nblk * 4) && mf_shm_in_own_window(m, a.recvMeta, (uint64_t)a.cap * 16) &&
           mf_shm_in_own_window(m, a.recvSib, (uint64_t)a.cap * MF_MOE_MAX_SIBLINGS * 8))) {
         FailD(a.status, MF_DEV_ERR_BOUNDS);  // the receive buffers are addressed by offset on every owner: they must be heap memory
@@ -97,6 +102,14 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     }
 
     // ---- (a) histogram of my pairs per global expert
+    const bool arrival = a.arrive != nullptr;
+    const int *myCnt = a.cnt + (arrival ? (size_t)(epoch & 1) * R * E : 0);
+    if (arrival) {
+        // My tile counters start from zero before anybody is told (by the barrier below) that it may send.
+        for (int i = blockIdx.x * kThreads + threadIdx.x; i < a.cap / 128; i += gridDim.x * kThreads) {
+            a.arrive[i] = 0;
+        }
+    }
     const int pairs = a.T * K;
     for (int i = blockIdx.x * kThreads + threadIdx.x; i < pairs; i += gridDim.x * kThreads) {
         const int e = a.topkIdx[i];
@@ -109,7 +122,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     if (blockIdx.x == 0) {
         for (int i = threadIdx.x; i < E * R; i += kThreads) {
             const int r = i / E, e = i % E;
-            int *peerCnt = mf_shm_peer(m, a.cnt, (uint32_t)r);
+            int *peerCnt = mf_shm_peer(m, const_cast<int *>(myCnt), (uint32_t)r);
             peerCnt[me * E + e] = ((volatile int *)a.localCnt)[e];
         }
         // Nobody sends before every rank is inside this call (its receive buffers are free) and has published its counts.
@@ -127,7 +140,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
         for (int e = threadIdx.x; e < E; e += kThreads) {
             int tot = 0, before = 0;
             for (int s = 0; s < R; s++) {
-                const int c = ((volatile int *)a.cnt)[s * E + e];
+                const int c = ((volatile const int *)myCnt)[s * E + e];
                 tot += c;
                 before += s < me ? c : 0;
             }
@@ -254,7 +267,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
             const uint32_t leadMask = __ballot_sync(0xffffffffu, leader);
             for (int k = 0; k < K; k++) {
                 const int slot = __shfl_sync(0xffffffffu, mySlot, k);
-                if (slot < 0 || (leadMask >> k & 1u) == 0) {
+                if (slot < 0 || (!arrival && (leadMask >> k & 1u) == 0)) {
                     continue;
                 }
                 const uint32_t d = (uint32_t)__shfl_sync(0xffffffffu, myOwner, k);
@@ -279,6 +292,14 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
                     }
                 }
             }
+            if (arrival) {
+                // Everything this warp stored for the token is visible system-wide before any of its rows is counted.
+                __threadfence_system();
+                __syncwarp();
+                if (mySlot >= 0) {
+                    atomicAdd_system(mf_shm_peer(m, a.arrive, (uint32_t)myOwner) + (mySlot >> 7), 1);
+                }
+            }
             __syncwarp();
         }
     }
@@ -286,7 +307,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
     __threadfence_system();
     grid.sync();
     if (blockIdx.x == 0) {
-        if (!dead) {
+        if (!dead && !arrival) {
             int rc = mf_barrier_cta(m, channel, 0, 2 * epoch, timeoutNs);
             if (rc != MF_DEV_OK) {
                 FailD(a.status, rc);
@@ -297,6 +318,9 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
             a.localCnt[e] = 0;
             a.cursor[e] = 0;
         }
+    }
+    if (arrival) {
+        return;  // the consumers of the receive buffer wait on the tile counters
     }
     // ---- (e) every leader row that arrived here is copied into the rows of its followers (local memory only)
     grid.sync();
@@ -321,17 +345,36 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
                 continue;
             }
             const int2 *sd = a.recvSib + (size_t)r * MF_MOE_MAX_SIBLINGS;
+            int rowsOf[MF_MOE_MAX_SIBLINGS];
+            int nf = 0;
             for (int i = 0; i < nsib; i++) {
                 const int fr = sd[i].x;
-                if (fr < 0 || fr >= rowsHere || fr == r) {
-                    continue;
+                if (fr >= 0 && fr < rowsHere && fr != r) {
+                    rowsOf[nf++] = fr;
                 }
-                unsigned char *dx = reinterpret_cast<unsigned char *>(a.recvX) + (size_t)fr * H;
-                for (int v = lane; v < H / 16; v += 32) {
-                    mf_st16(dx + (size_t)v * 16, mf_ld16_coherent(rx + (size_t)r * H + (size_t)v * 16));
+            }
+            // The leader's row is read once, four vectors per lane at a time, and stored to every follower.
+            const unsigned char *srcRow = rx + (size_t)r * H;
+            for (int vb = lane; vb < H / 16; vb += 128) {
+                uint4 raw[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    raw[j] = vb + 32 * j < H / 16 ? mf_ld16_coherent(srcRow + (size_t)(vb + 32 * j) * 16) : make_uint4(0u, 0u, 0u, 0u);
                 }
-                for (int v = lane; v < nblk; v += 32) {
-                    a.recvSf[(size_t)fr * nblk + v] = ((volatile uint32_t *)a.recvSf)[(size_t)r * nblk + v];
+                for (int i = 0; i < nf; i++) {
+                    unsigned char *dx = reinterpret_cast<unsigned char *>(a.recvX) + (size_t)rowsOf[i] * H;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if (vb + 32 * j < H / 16) {
+                            mf_st16(dx + (size_t)(vb + 32 * j) * 16, raw[j]);
+                        }
+                    }
+                }
+            }
+            for (int v = lane; v < nblk; v += 32) {
+                const uint32_t w = ((volatile uint32_t *)a.recvSf)[(size_t)r * nblk + v];
+                for (int i = 0; i < nf; i++) {
+                    a.recvSf[(size_t)rowsOf[i] * nblk + v] = w;
                 }
             }
         }

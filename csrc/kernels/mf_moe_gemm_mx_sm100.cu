@@ -24,6 +24,10 @@
 // the operand reuse of the 256-wide tile, and the epilogue of one tile runs under the MMAs of the next, which matters when K
 // is short (the second FFN GEMM: N = 7168 = 32 x 224, K = 2048).
 // Every mbarrier wait is bounded; on expiry the CTA sets *status, all roles drain and the CTA frees its TMEM and exits.
+// Gated form (mf_k_moe_grouped_gemm_mx_gated): the rows of A are being stored by other GPUs (the MoE dispatch of the peers)
+// while this kernel runs. The two warps that read A — the TMA producer and the scale-factor producer — start a tile only when
+// the arrival counter of its 128 rows is complete (acquire load of system scope, then a proxy fence before the TMA reads);
+// the scale-factor producer looks one tile ahead without blocking so that a tile that is late does not stall the one in flight.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -71,7 +75,8 @@ struct SharedStorage {
     uint64_t tmemFull[2];
     uint64_t tmemEmpty[2];
     uint32_t tmemBase;
-    int abortFlag;
+    int abortFlag;  // 0 running, 1 a pipeline wait expired, 2 an arrival wait expired
+    int gated;
     int tilePrefix[kMaxGroups + 1];
 };
 
@@ -84,7 +89,41 @@ struct MxParams {
     const int *groupCount;
     int *status;
     int G, N, K, mode, rowsTotal;
+    const int *arrive;  // optional: rows landed per 128-row tile of A
+    uint64_t waitNs;
 };
+
+__device__ __forceinline__ int LdAcquireSys(const int *p)
+{
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Spins until *ctr >= need; what the senders stored before they counted their rows is visible afterwards. Bounded: on expiry
+// the CTA-wide abort flag is raised and every role drains.
+__device__ __forceinline__ bool ArrivalWait(const int *ctr, int need, volatile int *abortFlag, uint64_t limitNs)
+{
+    if (LdAcquireSys(ctr) >= need) {
+        return true;
+    }
+    const uint64_t t0 = GlobalTimerNs();
+    for (uint32_t i = 0; i < (1u << 24); i++) {
+        if (LdAcquireSys(ctr) >= need) {
+            return true;
+        }
+        if ((i & 15u) == 15u) {
+            if (*abortFlag != 0) {
+                return false;
+            }
+            if (GlobalTimerNs() - t0 > limitNs) {
+                break;
+            }
+        }
+    }
+    *abortFlag = 2;
+    return false;
+}
 
 __device__ __forceinline__ float Silu(float x) { return x / (1.f + __expf(-x)); }
 
@@ -119,6 +158,7 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
             MbarInit(&s.tmemEmpty[i], kEpiWarps);
         }
         s.abortFlag = 0;
+        s.gated = p.arrive != nullptr && (p.status == nullptr || *(volatile int *)p.status == 0) ? 1 : 0;
         MbarInitFence();
         TmaPrefetchDesc(&tmapA);
         TmaPrefetchDesc(&tmapB);
@@ -141,6 +181,7 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
     const uint32_t tmemBase = s.tmemBase;
     const int totalTiles = s.tilePrefix[p.G];
     volatile int *abortFlag = &s.abortFlag;
+    const bool gated = s.gated != 0;
 
     auto decode = [&](int tile, int &g, int &mt, int &nt) {
         int lo = 0, hi = p.G;  // last group whose first tile is <= tile (empty groups share a prefix value: take the last)
@@ -162,11 +203,19 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
+            int lastGate = -1;
             for (int tile = blockIdx.x; tile < totalTiles && *abortFlag == 0; tile += gridDim.x) {
                 int g, mt, nt;
                 decode(tile, g, mt, nt);
                 const int rowA = p.groupOffset[g] + mt * BM;
                 const int rowB = g * p.N + nt * BN;
+                if (gated && (rowA >> 7) != lastGate) {
+                    if (!ArrivalWait(p.arrive + (rowA >> 7), min(BM, p.groupCount[g] - mt * BM), abortFlag, p.waitNs)) {
+                        break;
+                    }
+                    FenceProxyAsyncGlobal();  // the rows were stored through the generic proxy (by other GPUs); TMA reads them
+                    lastGate = rowA >> 7;
+                }
                 for (int kb = 0; kb < KB; kb++, it++) {
                     const uint32_t st = it % C::kStages, ph = (it / C::kStages) & 1;
                     if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
@@ -232,12 +281,31 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                 }
             }
         };
+        // Have the 128 rows of the tile landed? Lane 0 asks (waiting if `block`), the warp shares the answer.
+        auto gate = [&](int tile, bool block) -> bool {
+            int ok = 1;
+            if (lane == 0) {
+                int g, mt, nt;
+                decode(tile, g, mt, nt);
+                const int row0 = p.groupOffset[g] + mt * BM;
+                const int need = min(BM, p.groupCount[g] - mt * BM);
+                const int *ctr = p.arrive + (row0 >> 7);
+                ok = block ? (ArrivalWait(ctr, need, abortFlag, p.waitNs) ? 1 : 0) : (LdAcquireSys(ctr) >= need ? 1 : 0);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
         uint32_t it = 0;
         int tile = blockIdx.x, kb0 = 0;
         SfWords cur, nxt;
         bool have = tile < totalTiles;
         if (have) {
-            fetch(tile, kb0, cur);
+            if (gated && !gate(tile, true)) {
+                have = false;
+            } else {
+                fetch(tile, kb0, cur);
+            }
         }
         while (have && *abortFlag == 0) {
             int tileN = tile, kbN = kb0 + 4;
@@ -246,8 +314,10 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                 kbN = 0;
             }
             const bool haveNext = tileN < totalTiles;
-            if (haveNext) {
+            bool fetched = false;
+            if (haveNext && (!gated || kbN != 0 || gate(tileN, false))) {
                 fetch(tileN, kbN, nxt);
+                fetched = true;
             }
             bool ok = true;
 #pragma unroll
@@ -276,6 +346,12 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
             }
             if (!ok) {
                 break;
+            }
+            if (haveNext && !fetched) {
+                if (!gate(tileN, true)) {
+                    break;
+                }
+                fetch(tileN, kbN, nxt);
             }
             cur = nxt;
             tile = tileN;
@@ -419,7 +495,7 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
     TcFenceBefore();
     __syncthreads();
     if (s.abortFlag != 0 && threadIdx.x == 0 && p.status != nullptr) {
-        atomicCAS(p.status, 0, 3 /* pipeline wait expired */);
+        atomicCAS(p.status, 0, s.abortFlag == 2 ? MF_K_GEMM_ARRIVAL_EXPIRED : MF_K_GEMM_PIPELINE_EXPIRED);
     }
     if (warp == 3) {
         TcFenceAfter();
@@ -480,14 +556,15 @@ int Launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const MxParams &p, 
     return cudaGetLastError() == cudaSuccess ? MF_K_OK : MF_K_LAUNCH_FAILED;
 }
 
-}  // namespace
-
-extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
-                                        const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
-                                        int *status, int ctas, mf_stream_t stream)
+int GemmMx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf, const int *groupOffset,
+           const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN, const int *arrive, uint64_t waitNs, int *status, int ctas,
+           mf_stream_t stream)
 {
     const int epi = mode & 15;
     if (tileN == 512) {
+        if (arrive != nullptr) {
+            return MF_K_INVALID;
+        }
         return mf_k_moe_grouped_gemm_mx_2sm(a, aSf, b, bScale, out, outSf, groupOffset, groupCount, G, rowsTotal, N, K, mode, status, ctas, stream);
     }
     if (a == nullptr || b == nullptr || out == nullptr || aSf == nullptr || bScale == nullptr || groupOffset == nullptr || groupCount == nullptr ||
@@ -537,8 +614,30 @@ extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, cons
     p.K = K;
     p.mode = mode;
     p.rowsTotal = rowsTotal;
+    p.arrive = arrive;
+    // Shorter than the 2 s limit of the pipeline waits, so that a tile that never arrives is reported as such.
+    p.waitNs = (waitNs == 0 || waitNs > 1500000000ull) ? 1500000000ull : waitNs;
     if (tileN == 224) {
         return Launch<224>(mapA, mapB, p, ctas, (cudaStream_t)stream);
     }
     return tileN == 256 ? Launch<256>(mapA, mapB, p, ctas, (cudaStream_t)stream) : Launch<128>(mapA, mapB, p, ctas, (cudaStream_t)stream);
+}
+
+}  // namespace
+
+extern "C" int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
+                                        const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
+                                        int *status, int ctas, mf_stream_t stream)
+{
+    return GemmMx(a, aSf, b, bScale, out, outSf, groupOffset, groupCount, G, rowsTotal, N, K, mode, tileN, nullptr, 0, status, ctas, stream);
+}
+
+extern "C" int mf_k_moe_grouped_gemm_mx_gated(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
+                                              const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
+                                              const int *arrive, uint64_t waitNs, int *status, int ctas, mf_stream_t stream)
+{
+    if (arrive == nullptr) {
+        return MF_K_INVALID;
+    }
+    return GemmMx(a, aSf, b, bScale, out, outSf, groupOffset, groupCount, G, rowsTotal, N, K, mode, tileN, arrive, waitNs, status, ctas, stream);
 }

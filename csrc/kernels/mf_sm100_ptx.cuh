@@ -203,6 +203,8 @@ __device__ __forceinline__ void TmemCpSfAtom(uint32_t taddr, uint64_t smemDesc)
 }
 // Generic-proxy writes to shared memory (ordinary stores) become visible to the async proxy (tcgen05.cp, TMA) after this fence.
 __device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Orders global-memory accesses of the generic proxy (an acquire load that saw another agent's stores) before TMA reads.
+__device__ __forceinline__ void FenceProxyAsyncGlobal() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 // Instruction descriptor for kind::mxf8f6f4.block_scale, E4M3 x E4M3 (A/B format 0 at [7,10) and [10,13)), both operands K-major,
 // UE8M0 scale factors (bit 23), N >> 3 at [17,23), M >> 4 at [24,29), byte selectors of the scale-factor columns: B at [4,6), A at

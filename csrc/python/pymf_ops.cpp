@@ -41,13 +41,20 @@ void BindOps(py::module_ &m)
     ops.attr("MOE_MAX_SIBLINGS") = (int)MF_MOE_MAX_SIBLINGS;
     ops.def("moe_grouped_gemm_mx", [](uint64_t a, uint64_t aSf, uint64_t b, uint64_t bScale, uint64_t out, uint64_t outSf, uint64_t groupOffset,
                                       uint64_t groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN, uint64_t status, int ctas,
-                                      uint64_t stream) {
+                                      uint64_t stream, uint64_t arrive, uint64_t waitNs) {
+        if (arrive != 0) {
+            return mf_k_moe_grouped_gemm_mx_gated((const void *)a, (const uint32_t *)aSf, (const void *)b, (const float *)bScale, (void *)out,
+                                                  (void *)outSf, (const int *)groupOffset, (const int *)groupCount, G, rowsTotal, N, K, mode, tileN,
+                                                  (const int *)arrive, waitNs, (int *)status, ctas, (mf_stream_t)stream);
+        }
         return mf_k_moe_grouped_gemm_mx((const void *)a, (const uint32_t *)aSf, (const void *)b, (const float *)bScale, (void *)out, (void *)outSf,
                                         (const int *)groupOffset, (const int *)groupCount, G, rowsTotal, N, K, mode, tileN, (int *)status, ctas,
                                         (mf_stream_t)stream);
     }, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_scale"), py::arg("out"), py::arg("out_sf"), py::arg("group_offset"),
             py::arg("group_count"), py::arg("G"), py::arg("rows_total"), py::arg("N"), py::arg("K"), py::arg("mode"), py::arg("tile_n") = 0,
-            py::arg("status") = 0, py::arg("ctas") = 0, py::arg("stream") = 0);
+            py::arg("status") = 0, py::arg("ctas") = 0, py::arg("stream") = 0, py::arg("arrive") = 0, py::arg("wait_ns") = 0);
+    ops.attr("GEMM_ARRIVAL_EXPIRED") = (int)MF_K_GEMM_ARRIVAL_EXPIRED;
+    ops.attr("GEMM_PIPELINE_EXPIRED") = (int)MF_K_GEMM_PIPELINE_EXPIRED;
     ops.def("moe_grouped_gemm", [](uint64_t a, uint64_t aScale, uint64_t b, uint64_t bScale, uint64_t out, uint64_t groupOffset, uint64_t groupCount,
                                    int G, int rowsTotal, int N, int K, int mode, uint64_t status, int ctas, uint64_t stream) {
         return mf_k_moe_grouped_gemm((const void *)a, (const float *)aScale, (const void *)b, (const float *)bScale, (void *)out,
@@ -61,8 +68,9 @@ void BindOps(py::module_ &m)
     ops.attr("MOE_COMBINE_ARGS_BYTES") = (int)sizeof(mf_moe_combine_args_t);
     ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvSf,
                                          uint64_t recvMeta, uint64_t recvSib, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
-                                         uint64_t sendSlot, uint64_t status, int T, int cap) {
+                                         uint64_t sendSlot, uint64_t status, int T, int cap, uint64_t arrive) {
         mf_moe_dispatch_args_t a{};
+        a.arrive = (int *)arrive;
         a.meta = (const void *)meta;
         a.x = (const void *)x;
         a.topkIdx = (const int *)topkIdx;
@@ -81,7 +89,9 @@ void BindOps(py::module_ &m)
         a.T = T;
         a.cap = cap;
         return py::bytes((const char *)&a, sizeof(a));
-    });
+    }, py::arg("meta"), py::arg("x"), py::arg("topk_idx"), py::arg("topk_w"), py::arg("cnt"), py::arg("recv_x"), py::arg("recv_sf"), py::arg("recv_meta"),
+            py::arg("recv_sib"), py::arg("local_cnt"), py::arg("cursor"), py::arg("expert_offset"), py::arg("expert_count"), py::arg("send_slot"),
+            py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("arrive") = 0);
     ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t recvSib, uint64_t expertOffset, uint64_t expertCount,
                                         uint64_t retY, uint64_t topkIdx, uint64_t out, uint64_t status, int T, int cap, int retRows) {
         mf_moe_combine_args_t a{};

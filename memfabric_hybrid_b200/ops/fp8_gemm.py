@@ -180,13 +180,16 @@ def quant_weight_mx_torch(w):
 
 
 def grouped_gemm_mx(a_q, a_sf, b_q, b_scale, group_offset, group_count, mode: str = "bf16", out=None, out_sf=None, status=None, tile_n: int = 0,
-                    ctas: int = 0, stream=None):
+                    ctas: int = 0, stream=None, arrive=None, wait_ns: int = 0):
     """out[rows of group g] = dequant(a)[rows] @ dequant(b[g]).T on the block-scaled tensor-core path.
 
     a_q [R, K] e4m3; a_sf uint8 [R, K/32] (or int32 [R, K/128]); b_q [G, N, K] e4m3; b_scale fp32 powers of two [G, N/128, K/128];
     group_offset int32 [G+1] (starts are multiples of 128), group_count int32 [G], both on the device.
     mode "bf16": out bf16 [R, N]. "swiglu": out bf16 [R, N/2]. "swiglu_fp8": returns (out e4m3 [R, N/2], out_sf uint8 [R, N/64]),
-    quantised per (row, 32 columns) — the a_q / a_sf of the next GEMM."""
+    quantised per (row, 32 columns) — the a_q / a_sf of the next GEMM.
+    arrive (int32 [R / 128], optional): rows of `a_q` are still being stored by other GPUs; a tile starts when the counter of
+    its 128 rows has reached the tile's valid rows (each wait bounded by wait_ns, at most 1.5 s; on expiry `status` becomes
+    GEMM_ARRIVAL_EXPIRED)."""
     import torch
 
     R, K = a_q.shape
@@ -205,7 +208,8 @@ def grouped_gemm_mx(a_q, a_sf, b_q, b_scale, group_offset, group_count, mode: st
     s = stream or torch.cuda.current_stream()
     rc = _ops.moe_grouped_gemm_mx(a_q.data_ptr(), a_sf.data_ptr(), b_q.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
                                   out_sf.data_ptr() if out_sf is not None else 0, group_offset.data_ptr(), group_count.data_ptr(), G, R, N, K, epi,
-                                  tile_n, status.data_ptr() if status is not None else 0, ctas, s.cuda_stream)
+                                  tile_n, status.data_ptr() if status is not None else 0, ctas, s.cuda_stream,
+                                  arrive.data_ptr() if arrive is not None else 0, wait_ns)
     if rc != 0:
         raise RuntimeError(f"moe_grouped_gemm_mx launch failed ({rc})")
     return (out, out_sf) if mode == "swiglu_fp8" else out

@@ -9,6 +9,11 @@ experts that share an owner, then the weighted top-k sum at the source).
 `w13` holds this rank's experts' gate/up projections in the interleaved layout of ops.fp8_gemm.interleave_gate_up,
 `w2` the down projections; both e4m3 with 128x128 power-of-two block scales (ops.fp8_gemm.quant_weight_mx_torch). `route()` turns router logits into (idx, renormalised w).
 
+With ``overlap=True`` dispatch ends without its closing barrier: every row that lands is counted in a per-tile arrival counter
+on the owner and the first GEMM starts each 128-row tile when its counter is complete, so an owner computes on what has arrived
+while slower senders are still pushing (every pair then carries its payload over the link; without it a token crosses once per
+owner and the owner replicates it).
+
 ``EmulatedMoE`` drives the same kernels for all ranks of an ``EmulatedHeap`` on one GPU (dispatch and combine each as one
 cooperative launch over all ranks; the per-rank GEMMs in between are ordinary launches) — this is how the multi-rank logic
 is tested without several GPUs.
@@ -52,13 +57,16 @@ class _RankState:
         self.heap = heap
         self.cap = cap
         nblk = hidden // 128
-        self.cnt_off = alloc(R * n_experts * 4)
+        self.cnt_off = alloc(2 * R * n_experts * 4)  # two halves: calls in arrival mode alternate between them
         self.recv_x_off = alloc(cap * hidden, 1024)
         self.recv_s_off = alloc(cap * nblk * 4)
         self.recv_m_off = alloc(cap * 16)
         self.recv_sib_off = alloc(cap * _ops.MOE_MAX_SIBLINGS * 8)
         self.ret_y_off = alloc(max_tokens * topk * hidden * 2)
-        self.cnt = heap.tensor(self.cnt_off, (R, n_experts), torch.int32)
+        self.arrive_off = alloc(cap // 128 * 4)
+        self.arrive = heap.tensor(self.arrive_off, (cap // 128,), torch.int32)
+        self.arrive.zero_()
+        self.cnt = heap.tensor(self.cnt_off, (2, R, n_experts), torch.int32)
         self.recv_x = heap.tensor(self.recv_x_off, (cap, hidden), torch.uint8).view(torch.float8_e4m3fn)
         self.recv_s = heap.tensor(self.recv_s_off, (cap, nblk), torch.int32)  # four UE8M0 bytes per 128-column block
         self.recv_m = heap.tensor(self.recv_m_off, (cap, 4), torch.int32)
@@ -86,12 +94,14 @@ class _MoEBase:
         self.hidden, self.n_experts, self.topk, self.inter, self.world = hidden, n_experts, topk, inter, world
         self.el = n_experts // world
         self.launches = 0
+        self.overlap = False
+        self.wait_ns = 0
 
     def _experts(self, st: _RankState, w13_q, w13_s, w2_q, w2_s, stream=None):
         """The expert FFN of one rank on what dispatch delivered: GEMM1 (+SwiGLU, + 1x32 quantisation) → GEMM2."""
         rows = st.cap
         F.grouped_gemm_mx(st.recv_x, st.recv_s, w13_q, w13_s, st.expert_offset, st.expert_count, mode="swiglu_fp8", out=st.h1_q, out_sf=st.h1_sf,
-                          status=st.status, stream=stream)
+                          status=st.status, stream=stream, arrive=st.arrive if self.overlap else None, wait_ns=self.wait_ns)
         F.grouped_gemm_mx(st.h1_q, st.h1_sf, w2_q, w2_s, st.expert_offset, st.expert_count, mode="bf16", out=st.y, status=st.status, stream=stream)
         self.launches += 2
         return rows
@@ -101,11 +111,12 @@ class FusedMoE(_MoEBase):
     """One rank of an expert-parallel MoE layer on a real SymmetricHeap."""
 
     def __init__(self, heap, max_tokens: int, hidden: int, n_experts: int, topk: int, inter: int, w13_q, w13_s, w2_q, w2_s,
-                 capacity_factor: float = 2.0, timeout_ns: int = 0):
+                 capacity_factor: float = 2.0, timeout_ns: int = 0, overlap: bool = False):
         import torch
 
         super().__init__(hidden, n_experts, topk, inter, heap.world)
         self.heap, self.max_tokens, self.timeout_ns = heap, max_tokens, timeout_ns
+        self.overlap, self.wait_ns = overlap, min(timeout_ns, 1_500_000_000)
         self.w13_q, self.w13_s, self.w2_q, self.w2_s = w13_q, w13_s, w2_q, w2_s
         cap = capacity_rows(max_tokens, topk, heap.world, self.el, capacity_factor)
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -119,13 +130,14 @@ class FusedMoE(_MoEBase):
     def _pack(self, x, idx, w, T):
         import torch
 
-        key = (x.data_ptr(), idx.data_ptr(), w.data_ptr(), T)
+        key = (x.data_ptr(), idx.data_ptr(), w.data_ptr(), T, self.overlap)
         if key == self._key:
             return
         st, h = self.st, self.heap
         d = _ops.pack_moe_dispatch_args(h.meta_ptr, x.data_ptr(), idx.data_ptr(), w.data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(), st.recv_s.data_ptr(),
                                         st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(), st.expert_offset.data_ptr(),
-                                        st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap)
+                                        st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap,
+                                        st.arrive.data_ptr() if self.overlap else 0)
         c = _ops.pack_moe_combine_args(h.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
                                        st.expert_count.data_ptr(), st.ret_y.data_ptr(), idx.data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T,
                                        st.cap, st.max_rows_ret)
@@ -174,11 +186,13 @@ class FusedMoE(_MoEBase):
 class EmulatedMoE(_MoEBase):
     """All ranks of an EmulatedHeap on one GPU. weights: per-rank lists of (w13_q, w13_s, w2_q, w2_s)."""
 
-    def __init__(self, eheap, max_tokens, hidden, n_experts, topk, inter, weights: List[tuple], capacity_factor: float = 8.0):
+    def __init__(self, eheap, max_tokens, hidden, n_experts, topk, inter, weights: List[tuple], capacity_factor: float = 8.0,
+                 overlap: bool = False):
         import torch
 
         super().__init__(hidden, n_experts, topk, inter, eheap.world)
         self.eheap, self.max_tokens, self.weights = eheap, max_tokens, weights
+        self.overlap = overlap
         cap = capacity_rows(max_tokens, topk, eheap.world, self.el, capacity_factor)
         # one set of symmetric offsets, shared by every emulated rank
         offs = {}
@@ -207,7 +221,8 @@ class EmulatedMoE(_MoEBase):
             st, rk = self.states[r], self.eheap.ranks[r]
             d += _ops.pack_moe_dispatch_args(rk.meta_ptr, xs[r].data_ptr(), idxs[r].data_ptr(), ws[r].data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(),
                                              st.recv_s.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(),
-                                             st.expert_offset.data_ptr(), st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap)
+                                             st.expert_offset.data_ptr(), st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap,
+                                             st.arrive.data_ptr() if self.overlap else 0)
             c += _ops.pack_moe_combine_args(rk.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
                                             st.expert_count.data_ptr(), st.ret_y.data_ptr(), idxs[r].data_ptr(), st.out.data_ptr(), st.status.data_ptr(),
                                             T, st.cap, st.max_rows_ret)

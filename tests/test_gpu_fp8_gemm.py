@@ -183,3 +183,53 @@ def test_grouped_gemm_mx_swiglu_and_fused_quant(counts, tile_n):
         err = (got - ref_q[sl]).abs()
         assert float(err.max()) <= 0.13 * float(exp.abs().max()) + 1e-6
         assert float(err.mean()) <= 5e-3 * float(exp.abs().max())
+
+
+def _arrival_counters(offs, cnts, rows, device):
+    import torch
+
+    arrive = torch.zeros(rows // 128, dtype=torch.int32, device=device)
+    for off, n in zip(offs.tolist(), cnts.tolist()):
+        for mt in range((n + 127) // 128):
+            arrive[off // 128 + mt] = min(128, n - 128 * mt)
+    return arrive
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gated_gemm_runs_on_complete_counters_and_gives_up_on_a_missing_tile(tile_n):
+    """The GEMM whose tiles wait for arrival counters: complete counters → the ordinary result; one tile whose counter stays
+    short → every wait is bounded, the status word names the arrival wait and the context stays usable."""
+    import torch
+
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+    from memfabric_hybrid_b200._loader import _pymf
+
+    dev = "cuda"
+    counts, N, K = [300, 0, 129, 64], 512, 1024
+    offs, cnts, rows = _groups(counts, dev)
+    g = torch.Generator(device=dev).manual_seed(77)
+    a_q, a_sf = F.quant_act_mx_torch(torch.randn(rows, K, generator=g, device=dev))
+    w_q, w_s = F.quant_weight_mx_torch(torch.randn(len(counts), N, K, generator=g, device=dev) * 0.05)
+    arrive = _arrival_counters(offs, cnts, rows, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, status=status, tile_n=tile_n, arrive=arrive, wait_ns=200_000_000)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    ref = F.grouped_gemm_mx_reference(a_q, a_sf, w_q, w_s, offs, cnts)
+    for off, n in zip(offs.tolist(), cnts.tolist()):
+        if n:
+            exp = ref[off:off + n]
+            assert bool(((out[off:off + n].float() - exp).abs() <= 2e-2 * exp.abs().amax(dim=1, keepdim=True) + 1e-6).all())
+    # nothing ever completes the second tile of the first group
+    arrive[1] -= 1
+    F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, status=status, tile_n=tile_n, arrive=arrive, wait_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert int(status) == _pymf.ops.GEMM_ARRIVAL_EXPIRED
+    assert float((torch.ones(4, device=dev) + 1).sum()) == 8.0  # the context is alive
+    # a status that is already set (a failed dispatch) turns the waits off: the call returns at once
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, status=status, tile_n=tile_n, arrive=arrive, wait_ns=1_000_000_000)
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 100.0

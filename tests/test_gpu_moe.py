@@ -58,7 +58,8 @@ def _check(outs, refs):
 
 @pytest.mark.parametrize("world,T,hidden,n_experts,topk,inter", [(2, 8, 512, 8, 2, 256), (4, 33, 1024, 16, 4, 256), (8, 16, 7168, 64, 8, 256),
                                                                  (4, 200, 512, 8, 2, 128)])
-def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter):
+@pytest.mark.parametrize("overlap", [False, True])
+def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter, overlap):
     import torch
 
     from memfabric_hybrid_b200.ops.moe import EmulatedMoE, moe_reference
@@ -69,7 +70,7 @@ def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter)
     cap_rows = T * topk * world + (n_experts // world) * 128
     heap_bytes = world * n_experts * 4 + cap_rows * (hidden + hidden // 128 * 4 + 16 + 56) + T * topk * hidden * 2 + (1 << 20)
     heap = EmulatedHeap(world, heap_bytes)
-    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world))
+    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world), overlap=overlap)
     outs, status = layer(xs, idxs, ws)
     assert status == [0] * world
     refs = moe_reference(xs, idxs, ws, weights, n_experts, inter)
@@ -77,6 +78,14 @@ def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter)
     # receive-side bookkeeping: every pair arrived exactly once
     total = sum(int(st.expert_count.sum()) for st in layer.states)
     assert total == world * T * topk
+    if overlap:
+        # arrival mode: the counter of every 128-row tile of the receive buffer holds exactly the valid rows of that tile
+        for st in layer.states:
+            want = torch.zeros_like(st.arrive)
+            for off, n in zip(st.expert_offset.tolist(), st.expert_count.tolist()):
+                for mt in range((n + 127) // 128):
+                    want[off // 128 + mt] = min(128, n - 128 * mt)
+            assert torch.equal(st.arrive, want)
     # a second call on the same heap (epochs advance, scratch counters were left clean)
     xs2, idxs2, ws2 = _inputs(world, T, hidden, n_experts, topk, 6)
     outs2, status2 = layer(xs2, idxs2, ws2)
@@ -167,7 +176,7 @@ def test_missing_rank_times_out_with_status():
     assert float((torch.ones(4, device="cuda") + 1).sum()) == 8.0  # the context is alive
 
 
-def _real_rank(rank, world, port, q):
+def _real_rank(rank, world, port, q, overlap=False):
     try:
         import torch
 
@@ -179,8 +188,8 @@ def _real_rank(rank, world, port, q):
         heap = SymmetricHeap(rank, world, rank, 256 << 20, store_url=f"tcp://127.0.0.1:{port}")
         weights = _weights(world, n_experts, hidden, inter, 21)  # same seed everywhere: every rank can build the oracle
         xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 22)
-        layer = FusedMoE(heap, T, hidden, n_experts, topk, inter, *weights[rank], capacity_factor=float(world))
-        for it in range(2):
+        layer = FusedMoE(heap, T, hidden, n_experts, topk, inter, *weights[rank], capacity_factor=float(world), overlap=overlap)
+        for it in range(3 if overlap else 2):
             out = layer(xs[rank], idxs[rank], ws[rank])
             torch.cuda.synchronize()
             assert layer.check_status() == 0
@@ -196,7 +205,8 @@ def _real_rank(rank, world, port, q):
         q.put((rank, repr(e)))
 
 
-def test_real_ranks_one_per_gpu():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_real_ranks_one_per_gpu(overlap):
     import torch
 
     world = min(torch.cuda.device_count(), 8)
@@ -205,7 +215,7 @@ def test_real_ranks_one_per_gpu():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    ps = [ctx.Process(target=_real_rank, args=(r, world, port, q)) for r in range(world)]
+    ps = [ctx.Process(target=_real_rank, args=(r, world, port, q, overlap)) for r in range(world)]
     for p in ps:
         p.start()
     res = sorted(q.get(timeout=300) for _ in ps)
