@@ -139,6 +139,9 @@ typedef struct {
                           // dispatches in this mode a consumer must have waited for every tile of the first.
     int T;
     int cap;
+    int dedupMinPairs;    // pairs per rank (average over the ranks) from which a token crosses the link once per owner and the owner
+                          // replicates it; 0 = the built-in threshold. The same value on every rank.
+    int reserved;
 } mf_moe_dispatch_args_t;
 
 // A token with several experts on one owner: the pair with the lowest k is the leader, the others are followers.

@@ -68,9 +68,10 @@ void BindOps(py::module_ &m)
     ops.attr("MOE_COMBINE_ARGS_BYTES") = (int)sizeof(mf_moe_combine_args_t);
     ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvSf,
                                          uint64_t recvMeta, uint64_t recvSib, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
-                                         uint64_t sendSlot, uint64_t status, int T, int cap, uint64_t arrive) {
+                                         uint64_t sendSlot, uint64_t status, int T, int cap, uint64_t arrive, int dedupMinPairs) {
         mf_moe_dispatch_args_t a{};
         a.arrive = (int *)arrive;
+        a.dedupMinPairs = dedupMinPairs;
         a.meta = (const void *)meta;
         a.x = (const void *)x;
         a.topkIdx = (const int *)topkIdx;
@@ -91,7 +92,7 @@ void BindOps(py::module_ &m)
         return py::bytes((const char *)&a, sizeof(a));
     }, py::arg("meta"), py::arg("x"), py::arg("topk_idx"), py::arg("topk_w"), py::arg("cnt"), py::arg("recv_x"), py::arg("recv_sf"), py::arg("recv_meta"),
             py::arg("recv_sib"), py::arg("local_cnt"), py::arg("cursor"), py::arg("expert_offset"), py::arg("expert_count"), py::arg("send_slot"),
-            py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("arrive") = 0);
+            py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("arrive") = 0, py::arg("dedup_min_pairs") = 0);
     ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t recvSib, uint64_t expertOffset, uint64_t expertCount,
                                         uint64_t retY, uint64_t topkIdx, uint64_t out, uint64_t status, int T, int cap, int retRows) {
         mf_moe_combine_args_t a{};

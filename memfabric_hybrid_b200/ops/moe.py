@@ -96,6 +96,8 @@ class _MoEBase:
         self.launches = 0
         self.overlap = False
         self.wait_ns = 0
+        # Pairs per rank from which a token crosses the link once per owner and is replicated there (0 = the kernel's threshold).
+        self.dedup_min_pairs = 0
 
     def _experts(self, st: _RankState, w13_q, w13_s, w2_q, w2_s, stream=None):
         """The expert FFN of one rank on what dispatch delivered: GEMM1 (+SwiGLU, + 1x32 quantisation) → GEMM2."""
@@ -130,14 +132,14 @@ class FusedMoE(_MoEBase):
     def _pack(self, x, idx, w, T):
         import torch
 
-        key = (x.data_ptr(), idx.data_ptr(), w.data_ptr(), T, self.overlap)
+        key = (x.data_ptr(), idx.data_ptr(), w.data_ptr(), T, self.overlap, self.dedup_min_pairs)
         if key == self._key:
             return
         st, h = self.st, self.heap
         d = _ops.pack_moe_dispatch_args(h.meta_ptr, x.data_ptr(), idx.data_ptr(), w.data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(), st.recv_s.data_ptr(),
                                         st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(), st.expert_offset.data_ptr(),
                                         st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap,
-                                        st.arrive.data_ptr() if self.overlap else 0)
+                                        st.arrive.data_ptr() if self.overlap else 0, self.dedup_min_pairs)
         c = _ops.pack_moe_combine_args(h.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
                                        st.expert_count.data_ptr(), st.ret_y.data_ptr(), idx.data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T,
                                        st.cap, st.max_rows_ret)
@@ -222,7 +224,7 @@ class EmulatedMoE(_MoEBase):
             d += _ops.pack_moe_dispatch_args(rk.meta_ptr, xs[r].data_ptr(), idxs[r].data_ptr(), ws[r].data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(),
                                              st.recv_s.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(),
                                              st.expert_offset.data_ptr(), st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap,
-                                             st.arrive.data_ptr() if self.overlap else 0)
+                                             st.arrive.data_ptr() if self.overlap else 0, self.dedup_min_pairs)
             c += _ops.pack_moe_combine_args(rk.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
                                             st.expert_count.data_ptr(), st.ret_y.data_ptr(), idxs[r].data_ptr(), st.out.data_ptr(), st.status.data_ptr(),
                                             T, st.cap, st.max_rows_ret)

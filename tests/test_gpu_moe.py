@@ -58,7 +58,7 @@ def _check(outs, refs):
 
 @pytest.mark.parametrize("world,T,hidden,n_experts,topk,inter", [(2, 8, 512, 8, 2, 256), (4, 33, 1024, 16, 4, 256), (8, 16, 7168, 64, 8, 256),
                                                                  (4, 200, 512, 8, 2, 128)])
-@pytest.mark.parametrize("overlap", [False, True])
+@pytest.mark.parametrize("overlap", [False, True, "dedup"])
 def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter, overlap):
     import torch
 
@@ -70,7 +70,9 @@ def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter,
     cap_rows = T * topk * world + (n_experts // world) * 128
     heap_bytes = world * n_experts * 4 + cap_rows * (hidden + hidden // 128 * 4 + 16 + 56) + T * topk * hidden * 2 + (1 << 20)
     heap = EmulatedHeap(world, heap_bytes)
-    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world), overlap=overlap)
+    layer = EmulatedMoE(heap, T, hidden, n_experts, topk, inter, weights, capacity_factor=float(world), overlap=overlap is True)
+    if overlap == "dedup":
+        layer.dedup_min_pairs = 1  # a token crosses once per owner and is replicated there, whatever the size of the call
     outs, status = layer(xs, idxs, ws)
     assert status == [0] * world
     refs = moe_reference(xs, idxs, ws, weights, n_experts, inter)
@@ -78,7 +80,7 @@ def test_emulated_layer_matches_oracle(world, T, hidden, n_experts, topk, inter,
     # receive-side bookkeeping: every pair arrived exactly once
     total = sum(int(st.expert_count.sum()) for st in layer.states)
     assert total == world * T * topk
-    if overlap:
+    if overlap is True:
         # arrival mode: the counter of every 128-row tile of the receive buffer holds exactly the valid rows of that tile
         for st in layer.states:
             want = torch.zeros_like(st.arrive)
@@ -142,8 +144,10 @@ def test_receive_buffer_overflow_is_reported_and_contained():
     _check(outs, moe_reference(xs, bal_idx, bal_w, weights, n_experts, inter))
 
 
-def test_tokens_with_several_experts_on_one_owner():
-    """top-k larger than the rank count forces every token to have sibling experts on one owner (owner-side reduction)."""
+@pytest.mark.parametrize("dedup_min_pairs", [0, 1])
+def test_tokens_with_several_experts_on_one_owner(dedup_min_pairs):
+    """top-k larger than the rank count forces every token to have sibling experts on one owner (owner-side reduction), with
+    every pair carrying its payload (0: small call) and with one payload per (token, owner) replicated by the owner (1)."""
     import torch
 
     from memfabric_hybrid_b200.ops.moe import EmulatedMoE, moe_reference
@@ -188,7 +192,9 @@ def _real_rank(rank, world, port, q, overlap=False):
         heap = SymmetricHeap(rank, world, rank, 256 << 20, store_url=f"tcp://127.0.0.1:{port}")
         weights = _weights(world, n_experts, hidden, inter, 21)  # same seed everywhere: every rank can build the oracle
         xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 22)
-        layer = FusedMoE(heap, T, hidden, n_experts, topk, inter, *weights[rank], capacity_factor=float(world), overlap=overlap)
+        layer = FusedMoE(heap, T, hidden, n_experts, topk, inter, *weights[rank], capacity_factor=float(world), overlap=overlap is True)
+        if overlap == "dedup":
+            layer.dedup_min_pairs = 1
         for it in range(3 if overlap else 2):
             out = layer(xs[rank], idxs[rank], ws[rank])
             torch.cuda.synchronize()
@@ -205,7 +211,7 @@ def _real_rank(rank, world, port, q, overlap=False):
         q.put((rank, repr(e)))
 
 
-@pytest.mark.parametrize("overlap", [False, True])
+@pytest.mark.parametrize("overlap", [False, True, "dedup"])
 def test_real_ranks_one_per_gpu(overlap):
     import torch
 
