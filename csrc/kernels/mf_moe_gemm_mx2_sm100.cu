@@ -34,18 +34,23 @@ constexpr int kThreads = 384;
 constexpr int kEpiWarps = 8;
 constexpr int kMaxGroups = 256;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfaCol = 256;  // [0, 256) accumulator, [256, 260) A scale factors, [260, 268) weight scale factors
-constexpr uint32_t kSfbCol = 260;
+constexpr uint32_t kSfaCol = 256;  // [0, 256) accumulator, [256, 260) A scale factors, [260, 268) weight scale factors,
+constexpr uint32_t kSfbCol = 260;  // [268, 280) a second set of both: K blocks alternate
+constexpr uint32_t kSfSetCols = 12;
 constexpr uint32_t kSfOne = 0x7f7f7f7fu;
+constexpr int kSfGroup = 4;             // K blocks whose scale atoms are produced and released together
+constexpr int kSfSlots = 2 * kSfGroup;  // two groups: one being consumed, one being filled
 constexpr int kTileBytes = BM * BK;
 
 struct SharedStorage2 {
     alignas(1024) unsigned char a[kStages][kTileBytes];
     alignas(1024) unsigned char b[kStages][kTileBytes];
-    alignas(128) unsigned char sfa[kStages][512];
-    alignas(128) unsigned char sfb[kStages][1024];
-    uint64_t full[kStages];   // used in the leader: TMA bytes of both CTAs + both scale-factor warps
+    alignas(128) unsigned char sfa[kSfSlots][512];
+    alignas(128) unsigned char sfb[kSfSlots][1024];
+    uint64_t full[kStages];   // used in the leader: TMA bytes of both CTAs
     uint64_t empty[kStages];  // one copy per CTA, released together by the commit
+    uint64_t sfFull[2];       // used in the leader: the scale-factor warps of both CTAs
+    uint64_t sfEmpty[2];      // one copy per CTA, released together by the commit
     uint64_t tmemFull;        // one copy per CTA
     uint64_t tmemEmpty;       // used in the leader: epilogue warps of both CTAs
     uint32_t tmemBase;
@@ -62,6 +67,7 @@ struct Mx2Params {
     const int *groupCount;
     int *status;
     int G, N, K, mode, rowsTotal;
+    int wideStores;  // out is 32-byte aligned: the epilogue stores whole sectors
 };
 
 __device__ __forceinline__ float Silu(float x) { return x / (1.f + __expf(-x)); }
@@ -149,8 +155,12 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; i++) {
-            MbarInit(&s.full[i], 3);  // the leader's TMA thread (with the byte count of both CTAs) + both scale-factor warps
+            MbarInit(&s.full[i], 1);  // the leader's TMA thread, with the byte count of both CTAs
             MbarInit(&s.empty[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            MbarInit(&s.sfFull[i], 2);
+            MbarInit(&s.sfEmpty[i], 1);
         }
         MbarInit(&s.tmemFull, 1);
         MbarInit(&s.tmemEmpty, 2 * kEpiWarps);
@@ -226,8 +236,9 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ scale-factor producer (both CTAs)
-        // One work item (tile, group of up to four K blocks) of lookahead: see the one-SM kernel.
-        const uint32_t leaderFull0 = MapToCta(SmemAddr(&s.full[0]), 0);
+        // One work item (tile, group of up to four K blocks) of lookahead, and a ring of two such groups of atoms with one
+        // hand-shake per group, apart from the operand ring: see the one-SM kernel.
+        const uint32_t leaderSfFull0 = MapToCta(SmemAddr(&s.sfFull[0]), 0);
         struct SfWords {
             uint32_t wa[4][4];
             uint32_t wb[2][4];
@@ -288,26 +299,25 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
             if (haveNext) {
                 fetch(tileN, kbN, nxt);
             }
-            bool ok = true;
+            const uint32_t buf = it & 1, ph = (it >> 1) & 1;
+            const bool ok = MbarWaitBounded(&s.sfEmpty[buf], ph ^ 1, abortFlag);
+            if (ok) {
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if (kb0 + k >= KB) {
-                    break;
-                }
-                const uint32_t st = it % kStages, ph = (it / kStages) & 1;
-                if (!MbarWaitBounded(&s.empty[st], ph ^ 1, abortFlag)) {
-                    ok = false;
-                    break;
-                }
-                *reinterpret_cast<uint4 *>(s.sfa[st] + lane * 16) = make_uint4(cur.wa[0][k], cur.wa[1][k], cur.wa[2][k], cur.wa[3][k]);
+                for (int k = 0; k < kSfGroup; k++) {
+                    if (kb0 + k >= KB) {
+                        break;
+                    }
+                    const uint32_t slot = buf * kSfGroup + k;
+                    *reinterpret_cast<uint4 *>(s.sfa[slot] + lane * 16) = make_uint4(cur.wa[0][k], cur.wa[1][k], cur.wa[2][k], cur.wa[3][k]);
 #pragma unroll
-                for (int a = 0; a < 2; a++) {
-                    *reinterpret_cast<uint4 *>(s.sfb[st] + a * 512 + lane * 16) = make_uint4(cur.wb[a][k], cur.wb[a][k], cur.wb[a][k], cur.wb[a][k]);
+                    for (int a = 0; a < 2; a++) {
+                        *reinterpret_cast<uint4 *>(s.sfb[slot] + a * 512 + lane * 16) = make_uint4(cur.wb[a][k], cur.wb[a][k], cur.wb[a][k], cur.wb[a][k]);
+                    }
                 }
                 FenceProxyAsyncShared();
                 __syncwarp();
                 if (lane == 0) {
-                    RemoteArrive(leaderFull0 + st * (uint32_t)sizeof(uint64_t));  // also the way the leader arrives on its own barrier
+                    RemoteArrive(leaderSfFull0 + buf * (uint32_t)sizeof(uint64_t));  // also the way the leader arrives on its own barrier
                 }
                 it++;
             }
@@ -322,7 +332,7 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0 && cta == 0) {
-            uint32_t it = 0, tl = 0;
+            uint32_t it = 0, tl = 0, sg = 0;
             for (int tile = pairId; tile < totalTiles && *abortFlag == 0; tile += pairs, tl++) {
                 if (!MbarWaitBounded(&s.tmemEmpty, (tl & 1) ^ 1, abortFlag)) {
                     break;
@@ -331,22 +341,32 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                 bool ok = true;
                 for (int kb = 0; kb < KB; kb++, it++) {
                     const uint32_t st = it % kStages, ph = (it / kStages) & 1;
+                    const uint32_t sbuf = sg & 1, slot = sbuf * kSfGroup + (kb % kSfGroup);
+                    if (kb % kSfGroup == 0 && !MbarWaitBounded(&s.sfFull[sbuf], (sg >> 1) & 1, abortFlag)) {
+                        ok = false;
+                        break;
+                    }
                     if (!MbarWaitBounded(&s.full[st], ph, abortFlag)) {
                         ok = false;
                         break;
                     }
                     TcFenceAfter();
-                    TmemCpSfAtomPair(tmemBase + kSfaCol, SmemDescSfAtom(SmemAddr(s.sfa[st])));
-                    TmemCpSfAtomPair(tmemBase + kSfbCol, SmemDescSfAtom(SmemAddr(s.sfb[st])));
-                    TmemCpSfAtomPair(tmemBase + kSfbCol + 4, SmemDescSfAtom(SmemAddr(s.sfb[st] + 512)));
+                    const uint32_t sfa = tmemBase + kSfaCol + (kb & 1) * kSfSetCols, sfb = tmemBase + kSfbCol + (kb & 1) * kSfSetCols;
+                    TmemCpSfAtomPair(sfa, SmemDescSfAtom(SmemAddr(s.sfa[slot])));
+                    TmemCpSfAtomPair(sfb, SmemDescSfAtom(SmemAddr(s.sfb[slot])));
+                    TmemCpSfAtomPair(sfb + 4, SmemDescSfAtom(SmemAddr(s.sfb[slot] + 512)));
                     const uint64_t aDesc = SmemDescSw128(SmemAddr(s.a[st]));
                     const uint64_t bDesc = SmemDescSw128(SmemAddr(s.b[st]));
 #pragma unroll
                     for (uint32_t k = 0; k < BK / 32; k++) {
-                        MmaMxF8Pair(d, aDesc + (uint64_t)(k * 2), bDesc + (uint64_t)(k * 2), InstrDescMxF8(2 * BM, BN, k), (tmemBase + kSfaCol) | (k << 30),
-                                    (tmemBase + kSfbCol) | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                        MmaMxF8Pair(d, aDesc + (uint64_t)(k * 2), bDesc + (uint64_t)(k * 2), InstrDescMxF8(2 * BM, BN, k), sfa | (k << 30), sfb | (k << 30),
+                                    (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     MmaCommitPair(&s.empty[st]);
+                    if (kb % kSfGroup == kSfGroup - 1 || kb == KB - 1) {
+                        MmaCommitPair(&s.sfEmpty[sbuf]);
+                        sg++;
+                    }
                 }
                 if (!ok) {
                     break;
@@ -391,15 +411,30 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
             const int colBase = nt * BN + half * NV;
             if (epi == MF_GEMM_EPI_BF16) {
                 __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + (size_t)row * p.N + colBase;
+                // Whole 32-byte sectors per store when the output allows it: half the store instructions, and no sector is
+                // written in two pieces (the stores of a warp go to 32 different rows).
+                if (p.wideStores) {
 #pragma unroll
-                for (int j = 0; j < NV; j += 8) {
-                    uint4 pk;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+                    for (int j = 0; j < NV; j += 16) {
+                        uint32_t pk[8];
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                        for (int q = 0; q < 8; q++) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                            pk[q] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        StGlobal32B(o + j, pk);
                     }
-                    *reinterpret_cast<uint4 *>(o + j) = pk;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NV; j += 8) {
+                        uint4 pk;
+                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                        }
+                        *reinterpret_cast<uint4 *>(o + j) = pk;
+                    }
                 }
             } else {
 #pragma unroll
@@ -428,15 +463,26 @@ mf_moe_grouped_gemm_mx2_kernel(const __grid_constant__ CUtensorMap tmapA, const 
                         const uint32_t e = Ue8m0Ceil(amax * (1.f / 448.f));
                         const float inv = __uint_as_float((254u - e) << 23);
                         unsigned char *o = reinterpret_cast<unsigned char *>(p.out) + (size_t)row * (p.N / 2) + hcol;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 16) {
-                            uint4 pk;
-                            unsigned short *ps = reinterpret_cast<unsigned short *>(&pk);
+                        if (p.wideStores) {
+                            uint32_t pk[8];
 #pragma unroll
                             for (int t = 0; t < 8; t++) {
-                                ps[t] = __nv_cvt_float2_to_fp8x2(make_float2(h[j + 2 * t] * inv, h[j + 2 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * t] * inv, h[4 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * t + 2] * inv, h[4 * t + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                                pk[t] = lo | (hi << 16);
                             }
-                            *reinterpret_cast<uint4 *>(o + j) = pk;
+                            StGlobal32B(o, pk);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 16) {
+                                uint4 pk;
+                                unsigned short *ps = reinterpret_cast<unsigned short *>(&pk);
+#pragma unroll
+                                for (int t = 0; t < 8; t++) {
+                                    ps[t] = __nv_cvt_float2_to_fp8x2(make_float2(h[j + 2 * t] * inv, h[j + 2 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                }
+                                *reinterpret_cast<uint4 *>(o + j) = pk;
+                            }
                         }
                         p.outSf[(size_t)row * (p.N / 64) + hcol / 32] = (unsigned char)e;
                     }
@@ -521,6 +567,7 @@ extern "C" int mf_k_moe_grouped_gemm_mx_2sm(const void *a, const uint32_t *aSf, 
     p.K = K;
     p.mode = mode;
     p.rowsTotal = rowsTotal;
+    p.wideStores = ((uintptr_t)out & 31) == 0 ? 1 : 0;
     static bool attrSet = false;
     const size_t smem = sizeof(SharedStorage2) + 1024;
     if (!attrSet) {

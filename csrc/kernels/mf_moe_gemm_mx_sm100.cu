@@ -91,6 +91,7 @@ struct MxParams {
     int G, N, K, mode, rowsTotal;
     const int *arrive;  // optional: rows landed per 128-row tile of A
     uint64_t waitNs;
+    int wideStores;  // out is 32-byte aligned: the epilogue stores whole sectors
 };
 
 __device__ __forceinline__ int LdAcquireSys(const int *p)
@@ -437,15 +438,30 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
             const int colBase = nt * BN + half * NV;
             if (epi == MF_GEMM_EPI_BF16) {
                 __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + (size_t)row * p.N + colBase;
+                // Whole 32-byte sectors per store when the output allows it: half the store instructions, and no sector is
+                // written in two pieces (the stores of a warp go to 32 different rows).
+                if (p.wideStores) {
 #pragma unroll
-                for (int j = 0; j < NV; j += 8) {
-                    uint4 pk;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+                    for (int j = 0; j < NV; j += 16) {
+                        uint32_t pk[8];
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                        for (int q = 0; q < 8; q++) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                            pk[q] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        StGlobal32B(o + j, pk);
                     }
-                    *reinterpret_cast<uint4 *>(o + j) = pk;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NV; j += 8) {
+                        uint4 pk;
+                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                        }
+                        *reinterpret_cast<uint4 *>(o + j) = pk;
+                    }
                 }
             } else if (BN % 128 == 0) {
                 // Every 64 columns hold 32 gate projections followed by the 32 matching up projections.
@@ -475,15 +491,26 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                         const uint32_t e = Ue8m0Ceil(amax * (1.f / 448.f));
                         const float inv = __uint_as_float((254u - e) << 23);
                         unsigned char *o = reinterpret_cast<unsigned char *>(p.out) + (size_t)row * (p.N / 2) + hcol;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 16) {
-                            uint4 pk;
-                            unsigned short *ps = reinterpret_cast<unsigned short *>(&pk);
+                        if (p.wideStores) {
+                            uint32_t pk[8];
 #pragma unroll
                             for (int t = 0; t < 8; t++) {
-                                ps[t] = __nv_cvt_float2_to_fp8x2(make_float2(h[j + 2 * t] * inv, h[j + 2 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * t] * inv, h[4 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * t + 2] * inv, h[4 * t + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                                pk[t] = lo | (hi << 16);
                             }
-                            *reinterpret_cast<uint4 *>(o + j) = pk;
+                            StGlobal32B(o, pk);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 16) {
+                                uint4 pk;
+                                unsigned short *ps = reinterpret_cast<unsigned short *>(&pk);
+#pragma unroll
+                                for (int t = 0; t < 8; t++) {
+                                    ps[t] = __nv_cvt_float2_to_fp8x2(make_float2(h[j + 2 * t] * inv, h[j + 2 * t + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                }
+                                *reinterpret_cast<uint4 *>(o + j) = pk;
+                            }
                         }
                         p.outSf[(size_t)row * (p.N / 64) + hcol / 32] = (unsigned char)e;
                     }
@@ -615,6 +642,7 @@ int GemmMx(const void *a, const uint32_t *aSf, const void *b, const float *bScal
     p.mode = mode;
     p.rowsTotal = rowsTotal;
     p.arrive = arrive;
+    p.wideStores = ((uintptr_t)out & 31) == 0 ? 1 : 0;
     // Shorter than the 2 s limit of the pipeline waits, so that a tile that never arrives is reported as such.
     p.waitNs = (waitNs == 0 || waitNs > 1500000000ull) ? 1500000000ull : waitNs;
     if (tileN == 224) {

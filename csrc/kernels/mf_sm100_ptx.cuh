@@ -44,29 +44,43 @@ __device__ __forceinline__ uint64_t GlobalTimerNs()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Waits for the phase with the given parity; gives up after limitNs of wall time (and at most 2^22 polls) or when
-// *abortFlag becomes non-zero. On expiry it raises *abortFlag so that the other roles of the CTA unwind too.
+// Waits for the phase with the given parity; gives up after about limitNs (counted on the SM's cycle counter at two cycles
+// per nanosecond, so between limitNs and twice that when the clock is low) or when *abortFlag becomes non-zero. On expiry it
+// raises *abortFlag so that the other roles of the CTA unwind too. The wait sits on the hand-shake path of every pipeline
+// stage, so the common case stays cheap: the counter and the flag are looked at once per 256 polls, and the global
+// nanosecond timer (slow to read) not at all.
 __device__ __forceinline__ bool MbarWaitBounded(uint64_t *bar, uint32_t parity, volatile int *abortFlag, uint64_t limitNs = 2000000000ull)
 {
     if (MbarTryWait(bar, parity)) {
         return true;
     }
-    const uint64_t t0 = GlobalTimerNs();
-    for (uint32_t i = 0; i < (1u << 22); i++) {
+    long long t0 = 0;
+    for (uint32_t i = 1; i < (1u << 30); i++) {
         if (MbarTryWait(bar, parity)) {
             return true;
         }
-        if ((i & 15u) == 15u) {
+        if ((i & 255u) == 0u) {
             if (*abortFlag != 0) {
                 return false;
             }
-            if (GlobalTimerNs() - t0 > limitNs) {
+            const long long now = clock64();
+            if (t0 == 0) {
+                t0 = now;
+            } else if ((uint64_t)(now - t0) > 2 * limitNs) {
                 break;
             }
         }
     }
     *abortFlag = 1;
     return false;
+}
+
+// One 32-byte store (a whole sector) to global memory; the address must be 32-byte aligned.
+__device__ __forceinline__ void StGlobal32B(void *p, const uint32_t (&w)[8])
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                 "r"(w[6]), "r"(w[7])
+                 : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------- TMA
