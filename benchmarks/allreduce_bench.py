@@ -41,7 +41,8 @@ def main():
     H = args.hidden
     max_bytes = 1 << args.max_log2
     max_T = max(1, max_bytes // (H * 2))
-    heap = SymmetricHeap(rank, world, local, 3 * max_T * H * 2 + (8 << 20), nvls=bool(args.nvls))
+    # two alternating input buffers and the residual of the large instance, the same for the small (CUDA-graph) instance
+    heap = SymmetricHeap(rank, world, local, 3 * max_T * H * 2 + (64 << 20), nvls=bool(args.nvls))
     sizes = [1 << lg for lg in range(args.min_log2, args.max_log2 + 1) if (1 << lg) >= H * 2]
     rows = workloads.allreduce_sizes(heap, sizes, hidden=H, iters=args.iters)
     if rank == 0:

@@ -2,7 +2,7 @@
 """Small, self-ending single-GPU cases for profiler captures: each runs ONE kernel of the library a few times on inputs that
 are larger than L2 (126 MB) where DRAM figures matter but hold at most a few GB on the device.
 
-    python benchmarks/profile_cases.py xcopy | peer | batch | gemm | allreduce | dispatch | reshard
+    python benchmarks/profile_cases.py xcopy | peer | batch | gemm | gemm2 | allreduce | dispatch | reshard
 
 `peer` needs two GPUs in ONE process (no second rank): GPU 0 pushes 256 MiB into GPU 1's memory over NVLink, so the link's byte
 counters (nvltx__bytes / nvlrx__bytes) can be read next to the kernel's duration.
@@ -98,6 +98,28 @@ def case_gemm():
     torch.cuda.synchronize()
 
 
+def case_gemm2():
+    """The second FFN GEMM of the expert layer: short K, bf16 epilogue (12 experts x 512 rows, N 7168, K 2048; weights 176 MB)."""
+    import torch
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+
+    G, per, N, K = 12, 512, 7168, 2048
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rows = G * per
+    a_q, a_s = F.quant_act_mx_torch(torch.randn(rows, K, generator=g, device="cuda"), block=32)
+    w_q = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device="cuda")
+    w_s = torch.empty(G, N // 128, K // 128, dtype=torch.float32, device="cuda")
+    for e in range(G):
+        w_q[e], w_s[e] = F.quant_weight_mx_torch(torch.randn(N, K, generator=g, device="cuda") * 0.02)
+    offs = torch.arange(0, rows + 1, per, dtype=torch.int32, device="cuda")
+    cnts = torch.full((G,), per, dtype=torch.int32, device="cuda")
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(3):
+        F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs, cnts, mode="bf16", out=out)
+    torch.cuda.synchronize()
+
+
 def case_allreduce():
     import torch
     from memfabric_hybrid_b200.ops.allreduce import emulated_allreduce
@@ -163,5 +185,5 @@ if __name__ == "__main__":
     import torch
 
     torch.cuda.set_device(0)
-    {"xcopy": case_xcopy, "peer": case_peer, "batch": case_batch, "gemm": case_gemm, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
+    {"xcopy": case_xcopy, "peer": case_peer, "batch": case_batch, "gemm": case_gemm, "gemm2": case_gemm2, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
     print("ok", sys.argv[1])

@@ -4,13 +4,19 @@
 // SMs read both halves, so a K block costs each SM 32 KiB of operand traffic instead of the 48 KiB of the one-SM 128 x 256 tile:
 // one third less shared-memory fill per FLOP, and a ring of six stages instead of four in the same shared memory, i.e. more K
 // blocks in flight to cover the latency of L2 and DRAM. The one-SM kernel keeps the tensor pipe about 60 % busy with L2, DRAM
-// and the TMA unit all below 40 % of their peaks; the fill latency, not a throughput limit, paces it.
+// and the TMA unit all below 40 % of their peaks; the fill latency, not a throughput limit, paces it. Measured, the pair's longer
+// hand-shakes (commit to both CTAs, byte counts and arrivals crossing to the leader) cost what the deeper ring gains: 0.89 ms
+// against 0.83 ms for the one-SM kernel on the first FFN GEMM of the benchmark, equal on the second; the one-SM kernel stays
+// the default.
 //
 // Roles per CTA (384 threads): warp 0 TMA producer (per-CTA tiled loads, no multicast, completing on the LEADER's "full"
-// barrier), warp 2 scale-factor producer (this CTA's 128 A rows, all 256 weight columns), warp 1 of the leader issues the
-// scale-factor copies and the MMAs for the pair; tcgen05.commit with a two-CTA mask releases the stage and publishes the
-// accumulator in both CTAs; warps 4-11 run the epilogue on the CTA's own 128 TMEM lanes and release the accumulator by
-// arriving on the leader's barrier (through distributed shared memory from the second CTA). Every wait is bounded.
+// barrier), warp 2 scale-factor producer (this CTA's 128 A rows, all 256 weight columns; the atoms have a ring of their own —
+// two groups of four K blocks, one hand-shake per group on the leader's "sfFull" — so that the operand ring turns on the TMA
+// loads alone and no remote arrival sits in its revolution), warp 1 of the leader issues the scale-factor copies (alternating
+// between two sets of TMEM columns) and the MMAs for the pair; tcgen05.commit with a two-CTA mask releases the stage (and, per
+// group, the atoms) and publishes the accumulator in both CTAs; warps 4-11 run the epilogue on the CTA's own 128 TMEM lanes and
+// release the accumulator by arriving on the leader's barrier (through distributed shared memory from the second CTA). Every
+// wait is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
