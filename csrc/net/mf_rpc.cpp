@@ -1,5 +1,7 @@
 #include "mf_rpc.h"
 
+#include <algorithm>
+
 #include "../util/mf_net_util.h"
 #include "mf_tls.h"
 
@@ -841,7 +843,11 @@ int RpcClient::Connect(const Endpoint &ep, uint64_t peerId, int retries, int ret
             hello.body.assign((const char *)&hb, sizeof(hb));
             std::string bytes = Encode(hello);
             WireHeader h{};
-            timeval tv{10, 0};
+            // The acknowledgement may take long when the server's process is stalled by the kernel (eight ranks pinning 8 GiB
+            // of host memory each held a server's loop for ten seconds in one run): wait as long as the caller allowed for
+            // connecting, at least 30 s.
+            const long budgetMs = (long)retries * (long)retryDelayMs;
+            timeval tv{std::max(30L, budgetMs / 1000), 0};
             setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
             fd_ = fd;
             tls_.reset();
