@@ -81,7 +81,9 @@ __device__ __forceinline__ int4 mf_ld_meta(const int4 *p)
     return make_int4((int)u.x, (int)u.y, (int)u.z, (int)u.w);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// Two CTAs per SM (71 KB of shared memory and at most 128 registers each): a warp works on one token at a time through chains
+// of dependent loads, shuffles and stores, so the kernel lives on the number of warps in flight, not on any one unit.
+__global__ void __launch_bounds__(kThreads, 2)
 mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
