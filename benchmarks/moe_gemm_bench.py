@@ -26,6 +26,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tile-n", type=int, default=0, help="0 = let the launcher choose; 128, 224 (bf16 epilogue only) or 256")
     ap.add_argument("--cases", default="", help="comma list of case names to run (default: all)")
+    ap.add_argument("--packed", action="store_true", help="weights in the 4 KiB-block layout of ops.fp8_gemm.pack_weight_mx")
+    ap.add_argument("--ctas", type=int, default=0, help="persistent CTAs of the GEMM (0 = one per SM)")
     ap.add_argument("--no-baseline", action="store_true", help="skip the cuBLAS comparison")
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -58,6 +60,9 @@ def main():
         for e in range(G):  # random-init expert by expert to bound the fp32 temporaries
             q, s_ = F.quant_weight_mx_torch(torch.randn(N, K, generator=g, device=dev) * 0.02)
             w_q[e], w_s[e] = q, s_
+        w_ref = w_q
+        if args.packed:
+            w_q = F.pack_weight_mx(w_q)
         out = torch.empty(cur, N // 2 if mode == "swiglu" else N, dtype=torch.bfloat16, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
 
@@ -67,9 +72,9 @@ def main():
         def run():
             # the layer's configuration: SwiGLU + 1x32 quantisation fused into the first GEMM, bf16 out of the second
             if mode == "swiglu":
-                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="swiglu_fp8", out=out_q, out_sf=out_sf, status=status, tile_n=args.tile_n)
+                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="swiglu_fp8", out=out_q, out_sf=out_sf, status=status, tile_n=args.tile_n, ctas=args.ctas)
             else:
-                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="bf16", out=out, status=status, tile_n=args.tile_n)
+                F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs_t, cnts_t, mode="bf16", out=out, status=status, tile_n=args.tile_n, ctas=args.ctas)
 
         for _ in range(3):
             run()
@@ -89,7 +94,7 @@ def main():
         a_bf = F.dequant_act_mx(a_q, a_s).to(torch.bfloat16)
         w_bf = torch.empty(G, N, K, dtype=torch.bfloat16, device=dev)
         for e in range(G):
-            w_bf[e] = F.dequant_weight(w_q[e], w_s[e]).to(torch.bfloat16)
+            w_bf[e] = F.dequant_weight(w_ref[e], w_s[e]).to(torch.bfloat16)
 
         def base():
             for e in range(G):
@@ -113,7 +118,7 @@ def main():
             bt.append(a_ev.elapsed_time(b_ev))
         bms = sorted(bt)[len(bt) // 2]
         # correctness on one expert
-        ref = F.grouped_gemm_mx_reference(a_q[:offs[1]], a_s[:offs[1]], w_q[:1], w_s[:1], offs_t[:2], cnts_t[:1], mode=mode)
+        ref = F.grouped_gemm_mx_reference(a_q[:offs[1]], a_s[:offs[1]], w_ref[:1], w_s[:1], offs_t[:2], cnts_t[:1], mode=mode)
         got = F.dequant_act_mx(out_q[:counts[0]], out_sf[:counts[0]]) if mode == "swiglu" else out[:counts[0]].float()
         err = float((got - ref[:counts[0]]).abs().max() / (ref[:counts[0]].abs().max() + 1e-9))
         weight_bytes = G * N * K
@@ -123,7 +128,7 @@ def main():
         rows_out.append(row)
         print(json.dumps(row), flush=True)
         row["tile_n"] = args.tile_n
-        del a_bf, w_bf, w_q, w_s, a_q, a_s, out
+        del a_bf, w_bf, w_q, w_ref, w_s, a_q, a_s, out
         torch.cuda.empty_cache()
     if args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)

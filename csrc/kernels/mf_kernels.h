@@ -79,6 +79,10 @@ int mf_k_allreduce_rmsnorm(const mf_allreduce_args_t *argsDev, int nEmulatedRank
 // ------------------------------------------------------------------------------------------------ MoE expert FFN (K5b)
 
 enum { MF_GEMM_EPI_BF16 = 0, MF_GEMM_EPI_SWIGLU = 1, MF_GEMM_EPI_SWIGLU_FP8 = 2 };
+// OR-ed into `mode` of mf_k_moe_grouped_gemm_mx: the weights are pre-packed for streaming, b = [G][N/32][K/128][32][128] bytes
+// (blocks of 32 rows x 128 K-bytes stored contiguously, 4 KiB each), so that a weight tile is read from DRAM in 4 KiB pieces
+// instead of 128-byte pieces 'K' bytes apart. Same values, same result.
+enum { MF_GEMM_B_PACKED = 1 << 8 };
 
 // Grouped block-scaled FP8 GEMM on tcgen05 tensor cores. Group g owns rows [groupOffset[g], groupOffset[g] + groupCount[g])
 // of A (group starts must be multiples of 128 rows; rows between count and the next start are ignored) and weights
@@ -96,8 +100,8 @@ int mf_k_moe_grouped_gemm(const void *a, const float *aScale, const void *b, con
 // MF_GEMM_EPI_SWIGLU (out bf16 [rowsTotal, N/2]) and MF_GEMM_EPI_SWIGLU_FP8: out e4m3 [rowsTotal, N/2] plus outSf
 // [rowsTotal, N/64] UE8M0 bytes, one per 32 outputs, i.e. exactly the a / aSf operands of a following GEMM with K = N/2.
 // tileN: 0 = pick from the sizes; 128, 256 (N % 256 == 0), 224 (N % 224 == 0, bf16 epilogue only: two accumulators), or 512 =
-// the two-SM kernel (256 x 256 tiles computed by pairs of CTAs with cta_group::2, N % 256 == 0). a, b, out and aSf must be
-// 16-byte aligned.
+// the two-SM kernel (256 x 256 tiles computed by pairs of CTAs with cta_group::2, N % 256 == 0; row-major weights only). a, b,
+// out and aSf must be 16-byte aligned.
 int mf_k_moe_grouped_gemm_mx(const void *a, const uint32_t *aSf, const void *b, const float *bScale, void *out, void *outSf,
                              const int *groupOffset, const int *groupCount, int G, int rowsTotal, int N, int K, int mode, int tileN,
                              int *status, int ctas, mf_stream_t stream);

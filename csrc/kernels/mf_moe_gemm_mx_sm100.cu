@@ -92,6 +92,7 @@ struct MxParams {
     const int *arrive;  // optional: rows landed per 128-row tile of A
     uint64_t waitNs;
     int wideStores;  // out is 32-byte aligned: the epilogue stores whole sectors
+    int bPacked;     // weights are stored as [G][N/32][K/128][32][128] and tmapB is the 4-D map of that layout
 };
 
 __device__ __forceinline__ int LdAcquireSys(const int *p)
@@ -224,7 +225,11 @@ mf_moe_grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmapA, const _
                     }
                     MbarExpectTx(&s.full[st], C::kATile + C::kBTile);
                     TmaLoad2D(s.a[st], &tmapA, &s.full[st], kb * BK, rowA);
-                    TmaLoad2D(s.b[st], &tmapB, &s.full[st], kb * BK, rowB);
+                    if (p.bPacked) {
+                        TmaLoad4D(s.b[st], &tmapB, &s.full[st], 0, 0, kb, rowB / 32);  // BN/32 blocks of 32 rows, 4 KiB each
+                    } else {
+                        TmaLoad2D(s.b[st], &tmapB, &s.full[st], kb * BK, rowB);
+                    }
                 }
             }
         }
@@ -562,6 +567,23 @@ bool MakeMap(CUtensorMap *m, const void *base, uint64_t rows, uint64_t K, uint32
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Packed weights: [rows/32][K/128][32][128] bytes seen as a 4-D tensor {128, 32, K/128, rows/32}; a box is {128, 32, 1, boxRows/32},
+// which lands in shared memory as boxRows consecutive 128-byte rows, exactly like the 2-D box of the row-major layout.
+bool MakeMapPacked(CUtensorMap *m, const void *base, uint64_t rows, uint64_t K, uint32_t boxRows)
+{
+    EncodeTiledFn enc = GetEncodeTiled();
+    if (enc == nullptr) {
+        return false;
+    }
+    const uint64_t KB = K / BK;
+    cuuint64_t dims[4] = {BK, 32, KB, rows / 32};
+    cuuint64_t strides[3] = {BK, 32 * BK, KB * 32 * BK};
+    cuuint32_t box[4] = {BK, 32, 1, boxRows / 32};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN>
 int Launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const MxParams &p, int ctas, cudaStream_t stream)
 {
@@ -588,8 +610,9 @@ int GemmMx(const void *a, const uint32_t *aSf, const void *b, const float *bScal
            mf_stream_t stream)
 {
     const int epi = mode & 15;
+    const bool packed = (mode & MF_GEMM_B_PACKED) != 0;
     if (tileN == 512) {
-        if (arrive != nullptr) {
+        if (arrive != nullptr || packed) {
             return MF_K_INVALID;
         }
         return mf_k_moe_grouped_gemm_mx_2sm(a, aSf, b, bScale, out, outSf, groupOffset, groupCount, G, rowsTotal, N, K, mode, status, ctas, stream);
@@ -625,7 +648,8 @@ int GemmMx(const void *a, const uint32_t *aSf, const void *b, const float *bScal
         return MF_K_INVALID;
     }
     CUtensorMap mapA, mapB;
-    if (!MakeMap(&mapA, a, (uint64_t)rowsTotal, (uint64_t)K, BM) || !MakeMap(&mapB, b, (uint64_t)G * N, (uint64_t)K, (uint32_t)tileN)) {
+    if (!MakeMap(&mapA, a, (uint64_t)rowsTotal, (uint64_t)K, BM) ||
+        !(packed ? MakeMapPacked(&mapB, b, (uint64_t)G * N, (uint64_t)K, (uint32_t)tileN) : MakeMap(&mapB, b, (uint64_t)G * N, (uint64_t)K, (uint32_t)tileN))) {
         return MF_K_LAUNCH_FAILED;
     }
     MxParams p;
@@ -643,6 +667,7 @@ int GemmMx(const void *a, const uint32_t *aSf, const void *b, const float *bScal
     p.rowsTotal = rowsTotal;
     p.arrive = arrive;
     p.wideStores = ((uintptr_t)out & 31) == 0 ? 1 : 0;
+    p.bPacked = packed ? 1 : 0;
     // Shorter than the 2 s limit of the pipeline waits, so that a tile that never arrives is reported as such.
     p.waitNs = (waitNs == 0 || waitNs > 1500000000ull) ? 1500000000ull : waitNs;
     if (tileN == 224) {

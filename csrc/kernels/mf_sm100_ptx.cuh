@@ -96,6 +96,14 @@ __device__ __forceinline__ void TmaLoad2D(void *smemDst, const CUtensorMap *m, u
                  "l"((uint64_t)m), "r"(SmemAddr(bar)), "r"(c0), "r"(c1)
                  : "memory");
 }
+// The same for a 4-D tensor map (c0 innermost).
+__device__ __forceinline__ void TmaLoad4D(void *smemDst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+                     SmemAddr(smemDst)),
+                 "l"((uint64_t)m), "r"(SmemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------- TMEM
 // Allocates `cols` (power of two, >= 32) TMEM columns; the base address is written to *smemSlot. Whole warp must call.

@@ -53,6 +53,7 @@ void BindOps(py::module_ &m)
     }, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_scale"), py::arg("out"), py::arg("out_sf"), py::arg("group_offset"),
             py::arg("group_count"), py::arg("G"), py::arg("rows_total"), py::arg("N"), py::arg("K"), py::arg("mode"), py::arg("tile_n") = 0,
             py::arg("status") = 0, py::arg("ctas") = 0, py::arg("stream") = 0, py::arg("arrive") = 0, py::arg("wait_ns") = 0);
+    ops.attr("GEMM_B_PACKED") = (int)MF_GEMM_B_PACKED;
     ops.attr("GEMM_ARRIVAL_EXPIRED") = (int)MF_K_GEMM_ARRIVAL_EXPIRED;
     ops.attr("GEMM_PIPELINE_EXPIRED") = (int)MF_K_GEMM_PIPELINE_EXPIRED;
     ops.def("moe_grouped_gemm", [](uint64_t a, uint64_t aScale, uint64_t b, uint64_t bScale, uint64_t out, uint64_t groupOffset, uint64_t groupCount,

@@ -179,6 +179,26 @@ def quant_weight_mx_torch(w):
     return q, scale.contiguous()
 
 
+def pack_weight_mx(w_q):
+    """Re-orders quantised weights [G, N, K] (e4m3) for streaming: [G, N/32, K/128, 32, 128], i.e. blocks of 32 rows x 128
+    K-bytes stored contiguously (4 KiB). grouped_gemm_mx takes either layout (it tells them apart by the number of dimensions)
+    and gives the same result; with the packed one a weight tile is read from DRAM in 4 KiB pieces instead of 128-byte
+    pieces K bytes apart, which is what counts when few rows per expert make the GEMM a weight stream (decode)."""
+    import torch
+
+    G, N, K = w_q.shape
+    assert N % 32 == 0 and K % 128 == 0 and w_q.is_contiguous()
+    return w_q.view(torch.uint8).view(G, N // 32, 32, K // 128, 128).permute(0, 1, 3, 2, 4).contiguous().view(w_q.dtype)
+
+
+def unpack_weight_mx(w_p):
+    """Inverse of pack_weight_mx: [G, N/32, K/128, 32, 128] → [G, N, K]."""
+    import torch
+
+    G, nb, kb, _, _ = w_p.shape
+    return w_p.view(torch.uint8).permute(0, 1, 3, 2, 4).contiguous().view(G, nb * 32, kb * 128).view(w_p.dtype)
+
+
 def grouped_gemm_mx(a_q, a_sf, b_q, b_scale, group_offset, group_count, mode: str = "bf16", out=None, out_sf=None, status=None, tile_n: int = 0,
                     ctas: int = 0, stream=None, arrive=None, wait_ns: int = 0):
     """out[rows of group g] = dequant(a)[rows] @ dequant(b[g]).T on the block-scaled tensor-core path.
@@ -193,10 +213,17 @@ def grouped_gemm_mx(a_q, a_sf, b_q, b_scale, group_offset, group_count, mode: st
     import torch
 
     R, K = a_q.shape
-    G, N, K2 = b_q.shape
+    packed = b_q.dim() == 5  # pack_weight_mx layout
+    if packed:
+        G, N, K2 = b_q.shape[0], b_q.shape[1] * 32, b_q.shape[2] * 128
+        assert tuple(b_q.shape[3:]) == (32, 128)
+    else:
+        G, N, K2 = b_q.shape
     assert K == K2 and K % 128 == 0 and a_q.is_contiguous() and b_q.is_contiguous() and a_sf.is_contiguous() and b_scale.is_contiguous()
     assert a_sf.numel() * a_sf.element_size() == R * (K // 32)
     epi = {"bf16": _ops.GEMM_EPI_BF16, "swiglu": _ops.GEMM_EPI_SWIGLU, "swiglu_fp8": _ops.GEMM_EPI_SWIGLU_FP8}[mode]
+    if packed:
+        epi |= _ops.GEMM_B_PACKED
     dev = a_q.device
     if mode == "bf16":
         out = out if out is not None else torch.empty(R, N, dtype=torch.bfloat16, device=dev)

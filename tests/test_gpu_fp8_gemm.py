@@ -233,3 +233,31 @@ def test_gated_gemm_runs_on_complete_counters_and_gives_up_on_a_missing_tile(til
     t1.record()
     torch.cuda.synchronize()
     assert t0.elapsed_time(t1) < 100.0
+
+
+@pytest.mark.parametrize("tile_n,N", [(128, 512), (256, 512), (224, 896), (0, 7168)])
+def test_packed_weights_give_the_same_result(tile_n, N):
+    """Weights re-ordered into 4 KiB blocks (pack_weight_mx) are the same operand: the outputs match bit for bit."""
+    import torch
+
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+
+    dev = "cuda"
+    counts, K = [200, 0, 37, 129], 1024
+    offs, cnts, rows = _groups(counts, dev)
+    g = torch.Generator(device=dev).manual_seed(5 + N)
+    a_q, a_sf = F.quant_act_mx_torch(torch.randn(rows, K, generator=g, device=dev))
+    w_q, w_s = F.quant_weight_mx_torch(torch.randn(len(counts), N, K, generator=g, device=dev) * 0.05)
+    w_p = F.pack_weight_mx(w_q)
+    assert w_p.shape == (len(counts), N // 32, K // 128, 32, 128) and torch.equal(F.unpack_weight_mx(w_p).view(torch.uint8), w_q.view(torch.uint8))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    modes = ["bf16"] if tile_n == 224 else ["bf16", "swiglu_fp8"]
+    for mode in modes:
+        ref = F.grouped_gemm_mx(a_q, a_sf, w_q, w_s, offs, cnts, mode=mode, status=status, tile_n=tile_n)
+        got = F.grouped_gemm_mx(a_q, a_sf, w_p, w_s, offs, cnts, mode=mode, status=status, tile_n=tile_n)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        pairs = zip(ref, got) if mode == "swiglu_fp8" else [(ref, got)]
+        for r, o in pairs:
+            for off, n in zip(offs.tolist(), cnts.tolist()):
+                assert torch.equal(r[off:off + n].view(torch.uint8), o[off:off + n].view(torch.uint8))
