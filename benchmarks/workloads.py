@@ -211,7 +211,8 @@ def moe_layer(heap, token_list: List[int], hidden: int = 7168, experts_per_rank:
     dev = "cuda"
     Tmax = max(token_list)
     w13_q, w13_s, w2_q, w2_s = make_moe_weights(EL, H, I, 1000 + rank)
-    layer = FusedMoE(heap, Tmax, H, E, K, I, w13_q, w13_s, w2_q, w2_s, capacity_factor=capacity_factor)
+    # device-resident epochs, so that the layer can also be replayed from a CUDA graph (eager calls work the same way)
+    layer = FusedMoE(heap, Tmax, H, E, K, I, w13_q, w13_s, w2_q, w2_s, capacity_factor=capacity_factor, device_epochs=True)
     w13_bf = w2_bf = None
     if baselines:
         w13_bf = torch.empty(EL, 2 * I, H, dtype=torch.bfloat16, device=dev)
@@ -270,6 +271,10 @@ def moe_layer(heap, token_list: List[int], hidden: int = 7168, experts_per_rank:
         it = iters if T <= 512 else max(3, iters // 2)
         row = {"tokens_per_rank": T, "world": world, "experts": E}
         row["fused_total_us"] = round(timed_us(lambda: layer(x, idx, w), it), 1)
+        if T <= 512:
+            # decode-sized call: four calls of the layer captured into one CUDA graph, replayed
+            row["fused_total_graph_us"] = round(_graph_us(lambda s_: layer(x, idx, w, stream=s_), lambda: None, it, calls_per_graph=4,
+                                                          check=layer.check_status), 1)
         row["dispatch_us"] = round(timed_us(lambda: layer.dispatch(x, idx, w), it), 1)
         row["experts_us"] = round(timed_us(lambda: layer.experts(), it), 1)
         layer.dispatch(x, idx, w)

@@ -141,6 +141,9 @@ typedef struct {
     int *arrive;          // heap, optional: [cap / 128] rows landed in each 128-row tile of the receive buffer (arrival mode: no
                           // closing barrier; the consumer waits per tile, see mf_k_moe_grouped_gemm_mx_gated). Between two
                           // dispatches in this mode a consumer must have waited for every tile of the first.
+    unsigned long long *epochState;  // optional, [2] zero-initialised to {last finished epoch, 0}: with epoch argument 0 the kernel
+                                     // takes its epoch from here and advances it itself, so launches can be replayed from a CUDA
+                                     // graph. The same choice and the same starting epoch on every rank.
     int T;
     int cap;
     int dedupMinPairs;    // pairs per rank (average over the ranks) from which a token crosses the link once per owner and the owner
@@ -162,6 +165,7 @@ typedef struct {
     const int *topkIdx;       // [T, K] as given to dispatch
     void *out;                // [T, H] bf16
     int *status;
+    unsigned long long *epochState;  // optional: as in mf_moe_dispatch_args_t (a separate pair of words for this kernel)
     int T;
     int cap;                  // rows of the receive buffer (and of y)
     int retRows;              // rows of every rank's landing zone (max tokens * K)
@@ -169,7 +173,7 @@ typedef struct {
 } mf_moe_combine_args_t;
 
 // H: hidden (multiple of 128), K: experts per token, E: experts in total (multiple of the rank count). Both kernels are
-// cooperative launches; epoch must grow by one per call and channel on every rank alike.
+// cooperative launches; epoch must grow by one per call and channel on every rank alike (epoch 0: taken from args.epochState).
 int mf_k_moe_dispatch(const mf_moe_dispatch_args_t *argsDev, int nEmulatedRanks, int rankCount, int H, int K, int E, uint32_t channel,
                       uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream);
 int mf_k_moe_combine(const mf_moe_combine_args_t *argsDev, int nEmulatedRanks, int rankCount, int H, int K, int EL, uint32_t channel,

@@ -74,6 +74,36 @@ __device__ __forceinline__ int ReadAbort(int *status, int *smemFlag)
     return v;
 }
 
+// Epoch of this call: the kernel argument, or (argument 0) one more than the device-resident count of finished calls. Every CTA
+// of the launch reads the same value: the count only moves when the LAST CTA of a launch retires (FinishEpochD).
+template <typename Args>
+__device__ __forceinline__ uint64_t ResolveEpochD(const Args &a, uint64_t epochArg)
+{
+    if (epochArg != 0 || a.epochState == nullptr) {
+        return epochArg;
+    }
+    return *(volatile unsigned long long *)a.epochState + 1;
+}
+
+// Called by every thread of every CTA on every way out of the kernel (after its last use of the epoch).
+template <typename Args>
+__device__ __forceinline__ void FinishEpochD(const Args &a, uint64_t epochArg, uint64_t epoch)
+{
+    if (epochArg != 0 || a.epochState == nullptr) {
+        return;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned long long done = atomicAdd(a.epochState + 1, 1ull);
+        if (done == (unsigned long long)gridDim.x - 1) {
+            a.epochState[1] = 0;
+            *(volatile unsigned long long *)a.epochState = epoch;
+            __threadfence();
+        }
+    }
+}
+
 // Meta words are written by other GPUs during this kernel: read them past the non-coherent path.
 __device__ __forceinline__ int4 mf_ld_meta(const int4 *p)
 {
@@ -84,10 +114,15 @@ __device__ __forceinline__ int4 mf_ld_meta(const int4 *p)
 // Two CTAs per SM (71 KB of shared memory and at most 128 registers each): a warp works on one token at a time through chains
 // of dependent loads, shuffles and stores, so the kernel lives on the number of warps in flight, not on any one unit.
 __global__ void __launch_bounds__(kThreads, 2)
-mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
+mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, int K, int E, uint32_t channel, uint64_t epochArg, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
     const mf_moe_dispatch_args_t a = args[blockIdx.y];
+    const uint64_t epoch = ResolveEpochD(a, epochArg);
+    if (epoch == 0) {
+        FailD(a.status, MF_DEV_ERR_BOUNDS);  // neither an epoch argument nor a device-resident epoch
+        return;
+    }
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     const int R = (int)m->rankCount, me = (int)m->rankId, EL = E / R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,6 +141,7 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
           mf_shm_in_own_window(m, a.recvSf, (uint64_t)a.cap * nblk * 4) && mf_shm_in_own_window(m, a.recvMeta, (uint64_t)a.cap * 16) &&
           mf_shm_in_own_window(m, a.recvSib, (uint64_t)a.cap * MF_MOE_MAX_SIBLINGS * 8))) {
         FailD(a.status, MF_DEV_ERR_BOUNDS);  // the receive buffers are addressed by offset on every owner: they must be heap memory
+        FinishEpochD(a, epochArg, epoch);
         return;
     }
 
@@ -345,11 +381,13 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
         }
     }
     if (!dedup) {
+        FinishEpochD(a, epochArg, epoch);
         return;  // every row came with its payload (in arrival mode the consumers wait on the tile counters)
     }
     // ---- (e) every leader row that arrived here is copied into the rows of its followers (local memory only)
     grid.sync();
     if (dead || ReadAbort(a.status, &abortFlag) != 0) {
+        FinishEpochD(a, epochArg, epoch);
         return;
     }
     {
@@ -404,13 +442,19 @@ mf_moe_dispatch_kernel(const mf_moe_dispatch_args_t *__restrict__ args, int H, i
             }
         }
     }
+    FinishEpochD(a, epochArg, epoch);
 }
 
 __global__ void __launch_bounds__(kThreads, 3)
-mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int K, int EL, uint32_t channel, uint64_t epoch, uint64_t timeoutNs)
+mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int K, int EL, uint32_t channel, uint64_t epochArg, uint64_t timeoutNs)
 {
     cg::grid_group grid = cg::this_grid();
     const mf_moe_combine_args_t a = args[blockIdx.y];
+    const uint64_t epoch = ResolveEpochD(a, epochArg);
+    if (epoch == 0) {
+        FailD(a.status, MF_DEV_ERR_BOUNDS);  // neither an epoch argument nor a device-resident epoch
+        return;
+    }
     const MfDeviceMeta *m = reinterpret_cast<const MfDeviceMeta *>(a.meta);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warpsTotal = gridDim.x * kWarps;
@@ -419,6 +463,7 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
     __shared__ int abortFlag;
     if (mf_check_bounds_enabled(m) && !mf_shm_in_own_window(m, a.retY, (uint64_t)a.retRows * H * 2)) {
         FailD(a.status, MF_DEV_ERR_BOUNDS);
+        FinishEpochD(a, epochArg, epoch);
         return;
     }
     for (int i = threadIdx.x; i <= EL; i += kThreads) {
@@ -524,6 +569,7 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
     }
     grid.sync();
     if (ReadAbort(a.status, &abortFlag) != 0) {
+        FinishEpochD(a, epochArg, epoch);
         return;
     }
     // ---- add the owners' partial sums (fp32, fixed order): pair k carries one iff no earlier pair of the token has the same owner
@@ -593,6 +639,7 @@ mf_moe_combine_kernel(const mf_moe_combine_args_t *__restrict__ args, int H, int
             }
         }
     }
+    FinishEpochD(a, epochArg, epoch);
 }
 
 // Resident-CTA capacity of a kernel on the current device for a given dynamic shared-memory size; remembered per (device,
@@ -643,7 +690,7 @@ extern "C" int mf_k_moe_dispatch(const mf_moe_dispatch_args_t *argsDev, int nEmu
                                  uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream)
 {
     if (argsDev == nullptr || nEmulatedRanks < 1 || rankCount < 1 || rankCount > (int)MF_SIGNAL_MAX_RANKS || H <= 0 || H % 128 != 0 || K < 1 ||
-        K > 32 || E < rankCount || E % rankCount != 0 || E > kMaxExperts || channel >= MF_SIGNAL_CHANNELS || epoch == 0) {
+        K > 32 || E < rankCount || E % rankCount != 0 || E > kMaxExperts || channel >= MF_SIGNAL_CHANNELS) {
         return MF_K_INVALID;
     }
     if (timeoutNs == 0) {
@@ -683,7 +730,7 @@ extern "C" int mf_k_moe_combine(const mf_moe_combine_args_t *argsDev, int nEmula
                                 uint64_t epoch, uint64_t timeoutNs, int ctas, mf_stream_t stream)
 {
     if (argsDev == nullptr || nEmulatedRanks < 1 || rankCount < 1 || rankCount > (int)MF_SIGNAL_MAX_RANKS || H <= 0 || H % 8 != 0 || K < 1 || K > 32 ||
-        EL < 1 || EL > kMaxExperts || channel >= MF_SIGNAL_CHANNELS || epoch == 0) {
+        EL < 1 || EL > kMaxExperts || channel >= MF_SIGNAL_CHANNELS) {
         return MF_K_INVALID;
     }
     if (timeoutNs == 0) {

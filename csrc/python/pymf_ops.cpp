@@ -69,10 +69,11 @@ void BindOps(py::module_ &m)
     ops.attr("MOE_COMBINE_ARGS_BYTES") = (int)sizeof(mf_moe_combine_args_t);
     ops.def("pack_moe_dispatch_args", [](uint64_t meta, uint64_t x, uint64_t topkIdx, uint64_t topkW, uint64_t cnt, uint64_t recvX, uint64_t recvSf,
                                          uint64_t recvMeta, uint64_t recvSib, uint64_t localCnt, uint64_t cursor, uint64_t expertOffset, uint64_t expertCount,
-                                         uint64_t sendSlot, uint64_t status, int T, int cap, uint64_t arrive, int dedupMinPairs) {
+                                         uint64_t sendSlot, uint64_t status, int T, int cap, uint64_t arrive, int dedupMinPairs, uint64_t epochState) {
         mf_moe_dispatch_args_t a{};
         a.arrive = (int *)arrive;
         a.dedupMinPairs = dedupMinPairs;
+        a.epochState = (unsigned long long *)epochState;
         a.meta = (const void *)meta;
         a.x = (const void *)x;
         a.topkIdx = (const int *)topkIdx;
@@ -93,10 +94,11 @@ void BindOps(py::module_ &m)
         return py::bytes((const char *)&a, sizeof(a));
     }, py::arg("meta"), py::arg("x"), py::arg("topk_idx"), py::arg("topk_w"), py::arg("cnt"), py::arg("recv_x"), py::arg("recv_sf"), py::arg("recv_meta"),
             py::arg("recv_sib"), py::arg("local_cnt"), py::arg("cursor"), py::arg("expert_offset"), py::arg("expert_count"), py::arg("send_slot"),
-            py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("arrive") = 0, py::arg("dedup_min_pairs") = 0);
+            py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("arrive") = 0, py::arg("dedup_min_pairs") = 0, py::arg("epoch_state") = 0);
     ops.def("pack_moe_combine_args", [](uint64_t meta, uint64_t y, uint64_t recvMeta, uint64_t recvSib, uint64_t expertOffset, uint64_t expertCount,
-                                        uint64_t retY, uint64_t topkIdx, uint64_t out, uint64_t status, int T, int cap, int retRows) {
+                                        uint64_t retY, uint64_t topkIdx, uint64_t out, uint64_t status, int T, int cap, int retRows, uint64_t epochState) {
         mf_moe_combine_args_t a{};
+        a.epochState = (unsigned long long *)epochState;
         a.meta = (const void *)meta;
         a.y = (const void *)y;
         a.recvMeta = (const int4 *)recvMeta;
@@ -111,7 +113,8 @@ void BindOps(py::module_ &m)
         a.cap = cap;
         a.retRows = retRows;
         return py::bytes((const char *)&a, sizeof(a));
-    });
+    }, py::arg("meta"), py::arg("y"), py::arg("recv_meta"), py::arg("recv_sib"), py::arg("expert_offset"), py::arg("expert_count"), py::arg("ret_y"),
+            py::arg("topk_idx"), py::arg("out"), py::arg("status"), py::arg("T"), py::arg("cap"), py::arg("ret_rows"), py::arg("epoch_state") = 0);
     ops.def("moe_dispatch", [](uint64_t argsDev, int nEmulated, int rankCount, int H, int K, int E, uint32_t channel, uint64_t epoch, uint64_t timeoutNs,
                                int ctas, uint64_t stream) {
         return mf_k_moe_dispatch((const mf_moe_dispatch_args_t *)argsDev, nEmulated, rankCount, H, K, E, channel, epoch, timeoutNs, ctas,

@@ -14,6 +14,10 @@ on the owner and the first GEMM starts each 128-row tile when its counter is com
 while slower senders are still pushing (every pair then carries its payload over the link; without it a token crosses once per
 owner and the owner replicates it).
 
+CUDA graphs: with ``device_epochs=True`` the epochs that order the cross-rank flags of dispatch and combine live in device
+memory and are advanced by the kernels themselves, so a call of the layer may be captured into a graph and replayed (call it once
+eagerly with the same tensors first: the argument blocks are uploaded on first use). Every rank must use the same setting.
+
 ``EmulatedMoE`` drives the same kernels for all ranks of an ``EmulatedHeap`` on one GPU (dispatch and combine each as one
 cooperative launch over all ranks; the per-rank GEMMs in between are ordinary launches) — this is how the multi-rank logic
 is tested without several GPUs.
@@ -113,7 +117,7 @@ class FusedMoE(_MoEBase):
     """One rank of an expert-parallel MoE layer on a real SymmetricHeap."""
 
     def __init__(self, heap, max_tokens: int, hidden: int, n_experts: int, topk: int, inter: int, w13_q, w13_s, w2_q, w2_s,
-                 capacity_factor: float = 2.0, timeout_ns: int = 0, overlap: bool = False):
+                 capacity_factor: float = 2.0, timeout_ns: int = 0, overlap: bool = False, device_epochs: bool = False):
         import torch
 
         super().__init__(hidden, n_experts, topk, inter, heap.world)
@@ -126,6 +130,13 @@ class FusedMoE(_MoEBase):
         self._dargs = torch.empty(_ops.MOE_DISPATCH_ARGS_BYTES, dtype=torch.uint8, device=dev)
         self._cargs = torch.empty(_ops.MOE_COMBINE_ARGS_BYTES, dtype=torch.uint8, device=dev)
         self._key = None
+        self.device_epochs = device_epochs
+        self._epoch_d = self._epoch_c = None
+        if device_epochs:
+            # {epoch of the last finished call, CTAs of the running call that have retired}, starting from the channels' host-side
+            # epochs (the same numbers on every rank) so that flags left by earlier calls are stale
+            self._epoch_d = torch.tensor([heap.next_epoch(CH_DISPATCH), 0], dtype=torch.int64, device=dev)
+            self._epoch_c = torch.tensor([heap.next_epoch(CH_COMBINE), 0], dtype=torch.int64, device=dev)
         torch.cuda.synchronize()
         heap.barrier()  # everybody's count matrix is zeroed before the first dispatch touches it
 
@@ -139,10 +150,11 @@ class FusedMoE(_MoEBase):
         d = _ops.pack_moe_dispatch_args(h.meta_ptr, x.data_ptr(), idx.data_ptr(), w.data_ptr(), st.cnt.data_ptr(), st.recv_x.data_ptr(), st.recv_s.data_ptr(),
                                         st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.local_cnt.data_ptr(), st.cursor.data_ptr(), st.expert_offset.data_ptr(),
                                         st.expert_count.data_ptr(), st.send_slot.data_ptr(), st.status.data_ptr(), T, st.cap,
-                                        st.arrive.data_ptr() if self.overlap else 0, self.dedup_min_pairs)
+                                        st.arrive.data_ptr() if self.overlap else 0, self.dedup_min_pairs,
+                                        self._epoch_d.data_ptr() if self.device_epochs else 0)
         c = _ops.pack_moe_combine_args(h.meta_ptr, st.y.data_ptr(), st.recv_m.data_ptr(), st.recv_sib.data_ptr(), st.expert_offset.data_ptr(),
                                        st.expert_count.data_ptr(), st.ret_y.data_ptr(), idx.data_ptr(), st.out.data_ptr(), st.status.data_ptr(), T,
-                                       st.cap, st.max_rows_ret)
+                                       st.cap, st.max_rows_ret, self._epoch_c.data_ptr() if self.device_epochs else 0)
         self._dargs.copy_(torch.frombuffer(bytearray(d), dtype=torch.uint8))
         self._cargs.copy_(torch.frombuffer(bytearray(c), dtype=torch.uint8))
         self._key = key
@@ -156,7 +168,7 @@ class FusedMoE(_MoEBase):
         # One warp per token: small batches get a small grid (its grid-wide barriers are cheaper), large ones every SM.
         ctas = max(1, min(1 << 16, (T + 7) // 8))
         rc = _ops.moe_dispatch(self._dargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.n_experts, CH_DISPATCH,
-                               self.heap.next_epoch(CH_DISPATCH), self.timeout_ns, ctas, s.cuda_stream)
+                               0 if self.device_epochs else self.heap.next_epoch(CH_DISPATCH), self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"moe_dispatch launch failed ({rc})")
         self.launches += 1
@@ -169,8 +181,8 @@ class FusedMoE(_MoEBase):
 
         s = stream or torch.cuda.current_stream()
         ctas = max(1, min(1 << 16, (T * self.topk * ((self.hidden // 8 + 127) // 128) + 7) // 8))  # one warp per 2 KiB piece of a returned row
-        rc = _ops.moe_combine(self._cargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.el, CH_COMBINE, self.heap.next_epoch(CH_COMBINE),
-                              self.timeout_ns, ctas, s.cuda_stream)
+        rc = _ops.moe_combine(self._cargs.data_ptr(), 1, self.world, self.hidden, self.topk, self.el, CH_COMBINE,
+                              0 if self.device_epochs else self.heap.next_epoch(CH_COMBINE), self.timeout_ns, ctas, s.cuda_stream)
         if rc != 0:
             raise RuntimeError(f"moe_combine launch failed ({rc})")
         self.launches += 1

@@ -228,3 +228,62 @@ def test_real_ranks_one_per_gpu(overlap):
     for p in ps:
         p.join(timeout=60)
     assert res == [(r, "ok") for r in range(world)], res
+
+
+def _graph_rank(rank, world, port, q):
+    try:
+        import torch
+
+        from memfabric_hybrid_b200.ops.moe import FusedMoE, moe_reference
+        from memfabric_hybrid_b200.parallel.heap import SymmetricHeap
+
+        torch.cuda.set_device(rank)
+        T, hidden, n_experts, topk, inter = 32, 1024, 8 * world, 4, 256
+        heap = SymmetricHeap(rank, world, rank, 256 << 20, store_url=f"tcp://127.0.0.1:{port}")
+        weights = _weights(world, n_experts, hidden, inter, 31)
+        layer = FusedMoE(heap, T, hidden, n_experts, topk, inter, *weights[rank], capacity_factor=float(world) + 1.0, device_epochs=True)
+        xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 32)
+        x, idx, w = xs[rank].clone(), idxs[rank].clone(), ws[rank].clone()
+        layer(x, idx, w)  # eager: uploads the argument blocks, advances the device-resident epochs like any other call
+        torch.cuda.synchronize()
+        heap.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = layer(x, idx, w)
+        for it in range(3):
+            xs, idxs, ws = _inputs(world, T, hidden, n_experts, topk, 40 + it)  # same seed on every rank: every rank knows all inputs
+            x.copy_(xs[rank])
+            idx.copy_(idxs[rank])
+            w.copy_(ws[rank])
+            torch.cuda.synchronize()
+            heap.barrier()
+            g.replay()
+            torch.cuda.synchronize()
+            assert layer.check_status() == 0
+            _check([out], [moe_reference(xs, idxs, ws, weights, n_experts, inter)[rank]])
+        heap.barrier()
+        heap.close()
+        q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(e)))
+
+
+def test_layer_replays_from_a_cuda_graph():
+    """Device-resident epochs: one call of the layer (dispatch, two GEMMs, combine) is captured once and replayed on new inputs.
+    One rank on one GPU, two real ranks when two GPUs are visible."""
+    import torch
+
+    world = min(torch.cuda.device_count(), 2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    ps = [ctx.Process(target=_graph_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in ps)
+    for p in ps:
+        p.join(timeout=60)
+    assert res == [(r, "ok") for r in range(world)], res
