@@ -2,7 +2,7 @@
 """Small, self-ending single-GPU cases for profiler captures: each runs ONE kernel of the library a few times on inputs that
 are larger than L2 (126 MB) where DRAM figures matter but hold at most a few GB on the device.
 
-    python benchmarks/profile_cases.py xcopy | peer | batch | gemm | gemm2 | allreduce | dispatch | reshard
+    python benchmarks/profile_cases.py xcopy | peer | batch | gemm | gemm_2sm | gemm2 | allreduce | dispatch | reshard
 
 `peer` needs two GPUs in ONE process (no second rank): GPU 0 pushes 256 MiB into GPU 1's memory over NVLink, so the link's byte
 counters (nvltx__bytes / nvlrx__bytes) can be read next to the kernel's duration.
@@ -76,7 +76,7 @@ def case_batch():
     torch.cuda.synchronize()
 
 
-def case_gemm():
+def case_gemm(tile_n: int = 0):
     import torch
     from memfabric_hybrid_b200.ops import fp8_gemm as F
 
@@ -94,8 +94,13 @@ def case_gemm():
     out_sf = torch.empty(rows, N // 64, dtype=torch.uint8, device="cuda")
     torch.cuda.synchronize()
     for _ in range(3):
-        F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu_fp8", out=out, out_sf=out_sf)
+        F.grouped_gemm_mx(a_q, a_s, w_q, w_s, offs, cnts, mode="swiglu_fp8", out=out, out_sf=out_sf, tile_n=tile_n)
     torch.cuda.synchronize()
+
+
+def case_gemm_2sm():
+    """The `gemm` case on the two-SM kernel (256 x 256 tiles by CTA pairs)."""
+    case_gemm(tile_n=512)
 
 
 def case_gemm2():
@@ -185,5 +190,5 @@ if __name__ == "__main__":
     import torch
 
     torch.cuda.set_device(0)
-    {"xcopy": case_xcopy, "peer": case_peer, "batch": case_batch, "gemm": case_gemm, "gemm2": case_gemm2, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
+    {"xcopy": case_xcopy, "peer": case_peer, "batch": case_batch, "gemm": case_gemm, "gemm_2sm": case_gemm_2sm, "gemm2": case_gemm2, "allreduce": case_allreduce, "dispatch": case_dispatch, "reshard": case_reshard}[sys.argv[1]]()
     print("ok", sys.argv[1])
