@@ -162,3 +162,19 @@ def test_reference_package_names_resolve():
 
     assert os.path.isfile(os.path.join(mf.get_include_path(), "mf", "mf_bm.h"))
     assert os.path.isfile(os.path.join(mf.get_lib_path(), "libmf_core.so"))
+
+
+def test_weight_packing_layout_round_trips():
+    """pack_weight_mx: block (nb, kb) of the packed tensor holds rows 32 nb .. 32 nb + 31, K bytes 128 kb .. 128 kb + 127."""
+    import torch
+
+    from memfabric_hybrid_b200.ops import fp8_gemm as F
+
+    G, N, K = 2, 96, 384
+    w = torch.arange(G * N * K, dtype=torch.int64).remainder(251).to(torch.uint8).view(G, N, K).view(torch.float8_e4m3fn)
+    p = F.pack_weight_mx(w)
+    assert p.shape == (G, N // 32, K // 128, 32, 128) and p.is_contiguous()
+    wb, pb = w.view(torch.uint8), p.view(torch.uint8)
+    for g, nb, kb in [(0, 0, 0), (1, 2, 1), (0, 1, 2)]:
+        assert torch.equal(pb[g, nb, kb], wb[g, 32 * nb:32 * nb + 32, 128 * kb:128 * kb + 128])
+    assert torch.equal(F.unpack_weight_mx(p).view(torch.uint8), wb)
