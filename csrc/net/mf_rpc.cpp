@@ -624,6 +624,7 @@ void RpcServer::Loop()
 {
     std::vector<epoll_event> evs(128);
     while (running_.load()) {
+        loopBeatMs_.store(NowMs(), std::memory_order_relaxed);
         int n = epoll_wait(epfd_, evs.data(), (int)evs.size(), 200);
         if (n < 0 && errno != EINTR) {
             break;

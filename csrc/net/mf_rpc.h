@@ -90,6 +90,9 @@ public:
     void Stop();
     uint16_t Port() const { return port_; }
     bool Running() const { return running_.load(); }
+    // Time (NowMs) of the event loop's latest pass: a supervisor that judges peers by what the loop has read from them must
+    // first know that the loop itself has been running.
+    uint64_t LoopBeatMs() const { return loopBeatMs_.load(std::memory_order_relaxed); }
     // Thread-safe. Returns 0 when queued/sent, -1 if the link is gone.
     int Send(LinkId link, const Frame &f);
     // A frame whose body is `payload` (f.body is ignored): on a plain link the bytes go to the socket from where they lie and
@@ -114,6 +117,7 @@ private:
     int listenFd_{-1}, epfd_{-1}, wakeFd_{-1};
     uint16_t port_{0};
     std::atomic<bool> running_{false};
+    std::atomic<uint64_t> loopBeatMs_{0};
     std::thread io_;
     std::mutex mu_;  // guards conns_ and every Conn::out queue
     std::unordered_map<LinkId, std::shared_ptr<Conn>> conns_;

@@ -704,6 +704,7 @@ void StoreServer::HouseKeeping()
 {
     std::unique_lock<std::mutex> lk(mu_);
     uint64_t nextBeatCheck = NowMs() + GlobalTiming().heartbeatIntervalMs;
+    uint64_t lastBeatCheck = NowMs();
     while (!stop_.load()) {
         uint64_t now = NowMs();
         uint64_t wake = nextBeatCheck;
@@ -743,9 +744,27 @@ void StoreServer::HouseKeeping()
         if (now >= nextBeatCheck) {
             const ServerTiming &t = GlobalTiming();
             nextBeatCheck = now + t.heartbeatIntervalMs;
-            for (auto &kv : lastSeenMs_) {
-                if ((now - kv.second) / t.heartbeatIntervalMs > t.heartbeatMissLimit) {
-                    dead.push_back(kv.first);
+            // A link is judged by what the event loop has read from it. If this thread overslept (the whole process was held:
+            // eight ranks pinning 8 GiB of host memory each stopped one for ten seconds) or the event loop has not come round
+            // lately, the silence is this server's, not the peers': their heartbeats sit unread in the sockets. Then every link
+            // is taken as seen one interval ago and judged again on later passes.
+            const uint64_t gap = now - lastBeatCheck;
+            const uint64_t loopBeat = rpc_.LoopBeatMs();
+            // (thresholds well above the jitter of a loaded machine: this thread wakes at least every interval, the event loop
+            // at least every 200 ms)
+            const uint64_t slack = std::max<uint64_t>(2ull * t.heartbeatIntervalMs, 1000);
+            const bool ownStall = gap > t.heartbeatIntervalMs + slack || (loopBeat != 0 && now > loopBeat && now - loopBeat > slack);
+            lastBeatCheck = now;
+            if (ownStall) {
+                MF_WARN("store server: was held for " << gap << " ms; heartbeat supervision starts over");
+                for (auto &kv : lastSeenMs_) {
+                    kv.second = std::max(kv.second, now - std::min<uint64_t>(now, t.heartbeatIntervalMs));
+                }
+            } else {
+                for (auto &kv : lastSeenMs_) {
+                    if ((now - kv.second) / t.heartbeatIntervalMs > t.heartbeatMissLimit) {
+                        dead.push_back(kv.first);
+                    }
                 }
             }
         }

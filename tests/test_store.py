@@ -272,6 +272,59 @@ def test_heartbeat_loss_marks_rank_down(mf, port):
         n.set_heartbeat_ms(2000, 3)
 
 
+def _server_process(port, conn):
+    import memfabric_hybrid_b200 as mf
+
+    n = mf.native
+    n.set_heartbeat_ms(50, 3)
+    srv = n.StoreServer()
+    conn.send(srv.start("127.0.0.1", port))
+    conn.recv()  # lives until the parent says so
+    conn.send(srv.alive_links())
+    srv.stop()
+
+
+@pytest.mark.timeout(90)
+def test_a_held_server_does_not_blame_its_clients(mf, port):
+    """The server's process is stopped for much longer than the heartbeat deadline (as the kernel does to a process that pins
+    gigabytes of host memory). When it runs again the silence was its own: no link is declared dead, nobody is told that a
+    rank went down, the store keeps working."""
+    import multiprocessing as mp
+    import os
+    import signal
+
+    n = mf.native
+    ctx = mp.get_context("spawn")
+    parent, child = ctx.Pipe()
+    proc = ctx.Process(target=_server_process, args=(port, child))
+    proc.start()
+    n.set_heartbeat_ms(50, 3)
+    try:
+        assert parent.recv() == 0
+        a = n.TcpStore("127.0.0.1", port, False, 2, 0)
+        b = n.TcpStore("127.0.0.1", port, False, 2, 1)
+        assert a.startup(5, 100) == 0 and b.startup(5, 100) == 0
+        down = []
+        a.watch_rank_down(lambda r: down.append(r))
+        assert a.set("k", b"v1") == ST_OK
+        time.sleep(0.3)
+        os.kill(proc.pid, signal.SIGSTOP)
+        time.sleep(2.5)  # deadline for a silent link: 4 x 50 ms
+        os.kill(proc.pid, signal.SIGCONT)
+        time.sleep(0.8)  # several supervision passes after the hold
+        assert down == []
+        assert b.get("k", 1000) == (ST_OK, b"v1")
+        parent.send("stop")
+        assert parent.recv() == 2  # both links survived
+        a.shutdown()
+        b.shutdown()
+    finally:
+        n.set_heartbeat_ms(2000, 3)
+        if proc.is_alive():
+            os.kill(proc.pid, signal.SIGCONT)
+        proc.join(timeout=10)
+
+
 def test_store_cleared_when_last_client_leaves(mf, port):
     n = mf.native
     srv = n.StoreServer()
