@@ -276,7 +276,7 @@ def _server_process(port, conn):
     import memfabric_hybrid_b200 as mf
 
     n = mf.native
-    n.set_heartbeat_ms(50, 3)
+    n.set_heartbeat_ms(100, 3)
     srv = n.StoreServer()
     conn.send(srv.start("127.0.0.1", port))
     conn.recv()  # lives until the parent says so
@@ -298,7 +298,7 @@ def test_a_held_server_does_not_blame_its_clients(mf, port):
     parent, child = ctx.Pipe()
     proc = ctx.Process(target=_server_process, args=(port, child))
     proc.start()
-    n.set_heartbeat_ms(50, 3)
+    n.set_heartbeat_ms(100, 3)
     try:
         assert parent.recv() == 0
         a = n.TcpStore("127.0.0.1", port, False, 2, 0)
@@ -309,9 +309,9 @@ def test_a_held_server_does_not_blame_its_clients(mf, port):
         assert a.set("k", b"v1") == ST_OK
         time.sleep(0.3)
         os.kill(proc.pid, signal.SIGSTOP)
-        time.sleep(2.5)  # deadline for a silent link: 4 x 50 ms
+        time.sleep(3.0)  # deadline for a silent link: 4 x 100 ms
         os.kill(proc.pid, signal.SIGCONT)
-        time.sleep(0.8)  # several supervision passes after the hold
+        time.sleep(1.0)  # several supervision passes after the hold
         assert down == []
         assert b.get("k", 1000) == (ST_OK, b"v1")
         parent.send("stop")
