@@ -24,6 +24,7 @@ using namespace ock::smem;
 struct Shared {
     double barrierUs[64];
     double setGetUs[64];
+    double allGatherUs[64];
     int failed;
 };
 
@@ -80,6 +81,17 @@ static int RunRank(int rank, int world, int port, int iters, Shared *sh)
     }
     t1 = std::chrono::steady_clock::now();
     sh->setGetUs[rank] = std::chrono::duration<double, std::micro>(t1 - t0).count() / iters;
+    // all-gather of one 64-byte record per rank (what the memory layers exchange when they publish slices and entities)
+    std::string mine(64, (char)('a' + rank % 26)), all((size_t)world * 64, '\0');
+    t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < iters; i++) {
+        if (group->GroupAllGather(mine.data(), 64, &all[0], (uint32_t)all.size()) != 0 || all[(size_t)(world - 1) * 64] != (char)('a' + (world - 1) % 26)) {
+            sh->failed = 1;
+            return 1;
+        }
+    }
+    t1 = std::chrono::steady_clock::now();
+    sh->allGatherUs[rank] = std::chrono::duration<double, std::micro>(t1 - t0).count() / iters;
     group->GroupBarrier();
     if (rank != 0) {
         return 0;
@@ -111,15 +123,17 @@ int main(int argc, char **argv)
         waitpid(kids[r], &st, 0);
         rc |= WIFEXITED(st) ? WEXITSTATUS(st) : 1;
     }
-    double b = 0, s = 0;
+    double b = 0, s = 0, ag = 0;
     for (int r = 0; r < world; r++) {
         b = sh->barrierUs[r] > b ? sh->barrierUs[r] : b;
         s = sh->setGetUs[r] > s ? sh->setGetUs[r] : s;
+        ag = sh->allGatherUs[r] > ag ? sh->allGatherUs[r] : ag;
     }
     if (rc != 0 || sh->failed) {
         std::printf("{\"impl\": \"reference\", \"error\": \"store benchmark failed\"}\n");
         return 1;
     }
-    std::printf("{\"impl\": \"reference\", \"ranks\": %d, \"iters\": %d, \"group_barrier_us\": %.1f, \"set_get_us\": %.1f}\n", world, iters, b, s);
+    std::printf("{\"impl\": \"reference\", \"ranks\": %d, \"iters\": %d, \"group_barrier_us\": %.1f, \"set_get_us\": %.1f, \"group_allgather_us\": %.1f}\n",
+                world, iters, b, s, ag);
     return 0;
 }
