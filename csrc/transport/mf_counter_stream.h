@@ -45,6 +45,13 @@ public:
         firstError_ = 0;
         return rc;
     }
+    // Nothing submitted that has not finished (a blocking operation may then run on the caller's thread without overtaking
+    // anything queued before it).
+    bool Idle()
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        return finished_ >= submitted_;
+    }
     uint64_t Submitted()
     {
         std::lock_guard<std::mutex> g(mu_);

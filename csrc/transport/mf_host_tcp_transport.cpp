@@ -561,6 +561,52 @@ void HostTcpTransport::WorkerLoop()
     }
 }
 
+// The access token of the peer's region that covers [remoteAddr, +size) with the access the operation needs; checks the role rule.
+int HostTcpTransport::TokenFor(const std::shared_ptr<Peer> &p, uint32_t rankId, bool write, uint64_t remoteAddr, uint64_t size, uint64_t *token)
+{
+    *token = 0;
+    {
+        std::lock_guard<std::mutex> g(p->linkMu);
+        if (!RolePermitsLink(opt_.role, p->info.role)) {
+            MF_ERROR("host transport: role " << opt_.role << " may not address rank " << rankId << " of role " << p->info.role);
+            return BM_INVALID_PARAM;
+        }
+        const uint32_t need = write ? MR_ACCESS_REMOTE_WRITE : MR_ACCESS_REMOTE_READ;
+        for (const auto &k : p->info.keys) {
+            if (k.Covers(remoteAddr, size) && (k.access & need) != 0) {
+                *token = k.token;
+                break;
+            }
+        }
+    }
+    if (*token == 0) {
+        MF_ERROR("host transport: rank " << rankId << " has no region that covers 0x" << std::hex << remoteAddr << "+0x" << size << std::dec
+                                         << " with the access asked for");
+        return BM_INVALID_PARAM;
+    }
+    return BM_OK;
+}
+
+// A blocking operation of at most one slice, with nothing queued before it for that peer, runs on the caller's thread: two
+// thread hand-overs (to a worker and back) are most of the latency of a small transfer. Everything else is queued and waited for.
+int HostTcpTransport::Blocking(uint32_t rankId, bool write, uint64_t localAddr, uint64_t remoteAddr, uint64_t size)
+{
+    if (open_.load() && rankId != opt_.rankId && localAddr != 0 && remoteAddr != 0 && size != 0 && size <= opt_.sliceBytes &&
+        remoteAddr + size >= remoteAddr) {
+        auto p = FindPeer(rankId);
+        if (p && p->counter.Idle()) {
+            uint64_t token = 0;
+            int rc = TokenFor(p, rankId, write, remoteAddr, size, &token);
+            if (rc != BM_OK) {
+                return rc;
+            }
+            return RunSlice(Slice{p, rankId, write, localAddr, remoteAddr, size, token});
+        }
+    }
+    int rc = Submit(rankId, write, localAddr, remoteAddr, size);
+    return rc != BM_OK ? rc : Synchronize(rankId);
+}
+
 int HostTcpTransport::Submit(uint32_t rankId, bool write, uint64_t localAddr, uint64_t remoteAddr, uint64_t size)
 {
     if (!open_.load()) {
@@ -593,24 +639,9 @@ int HostTcpTransport::Submit(uint32_t rankId, bool write, uint64_t localAddr, ui
         return BM_INVALID_PARAM;
     }
     uint64_t token = 0;
-    {
-        std::lock_guard<std::mutex> g(p->linkMu);
-        if (!RolePermitsLink(opt_.role, p->info.role)) {
-            MF_ERROR("host transport: role " << opt_.role << " may not address rank " << rankId << " of role " << p->info.role);
-            return BM_INVALID_PARAM;
-        }
-        const uint32_t need = write ? MR_ACCESS_REMOTE_WRITE : MR_ACCESS_REMOTE_READ;
-        for (const auto &k : p->info.keys) {
-            if (k.Covers(remoteAddr, size) && (k.access & need) != 0) {
-                token = k.token;
-                break;
-            }
-        }
-    }
-    if (token == 0) {
-        MF_ERROR("host transport: rank " << rankId << " has no region that covers 0x" << std::hex << remoteAddr << "+0x" << size << std::dec
-                                         << " with the access asked for");
-        return BM_INVALID_PARAM;
+    int trc = TokenFor(p, rankId, write, remoteAddr, size, &token);
+    if (trc != BM_OK) {
+        return trc;
     }
     const uint64_t step = opt_.sliceBytes;
     const uint64_t pieces = (size + step - 1) / step;
@@ -659,14 +690,12 @@ int HostTcpTransport::ReadRemoteAsync(uint32_t rankId, uint64_t localAddr, uint6
 
 int HostTcpTransport::WriteRemote(uint32_t rankId, uint64_t localAddr, uint64_t remoteAddr, uint64_t size)
 {
-    int rc = Submit(rankId, true, localAddr, remoteAddr, size);
-    return rc != BM_OK ? rc : Synchronize(rankId);
+    return Blocking(rankId, true, localAddr, remoteAddr, size);
 }
 
 int HostTcpTransport::ReadRemote(uint32_t rankId, uint64_t localAddr, uint64_t remoteAddr, uint64_t size)
 {
-    int rc = Submit(rankId, false, localAddr, remoteAddr, size);
-    return rc != BM_OK ? rc : Synchronize(rankId);
+    return Blocking(rankId, false, localAddr, remoteAddr, size);
 }
 
 }  // namespace transport

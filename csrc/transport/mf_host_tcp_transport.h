@@ -90,6 +90,8 @@ private:
     std::shared_ptr<Peer> FindPeer(uint32_t rankId);
     int EnsureLink(const std::shared_ptr<Peer> &p, uint32_t rankId, bool force);
     int Submit(uint32_t rankId, bool write, uint64_t localAddr, uint64_t remoteAddr, uint64_t size);
+    int Blocking(uint32_t rankId, bool write, uint64_t localAddr, uint64_t remoteAddr, uint64_t size);
+    int TokenFor(const std::shared_ptr<Peer> &p, uint32_t rankId, bool write, uint64_t remoteAddr, uint64_t size, uint64_t *token);
     int RunSlice(const Slice &s);
     int RunSliceOnce(const Slice &s);
     void WorkerLoop();
