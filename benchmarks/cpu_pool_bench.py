@@ -48,7 +48,8 @@ def worker(rank, port, bar, q):
     for lg in range(12, 26):
         n = 1 << lg
         data = np.random.default_rng(lg * 10 + rank).integers(0, 256, n, dtype=np.uint8)
-        out = np.empty(n, dtype=np.uint8)
+        out = np.zeros(n, dtype=np.uint8)
+        out.fill(1)  # touched before it is timed: a fresh array would charge its page faults to the first copies
         iters = max(3, min(2000, (64 << 20) // n))
         # addresses are taken once: the loop times the library call, not numpy's ctypes view or the pointer query
         src_p, dst_p, peer_p, mine_p = data.ctypes.data, out.ctypes.data, b.peer_rank_ptr(H, peer), b.peer_rank_ptr(H, rank)

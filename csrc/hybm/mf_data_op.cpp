@@ -5,7 +5,11 @@
 #include <memory>
 
 #include <algorithm>
+#include <atomic>
+#include <condition_variable>
 #include <cstdlib>
+#include <functional>
+#include <mutex>
 #include <cstring>
 #include <thread>
 #include <unistd.h>
@@ -399,33 +403,96 @@ private:
 
 // =============================================================================================== CPU engine
 
+// A few helper threads that stay around for large host copies and for batches of them: spawning threads per call costs more
+// than a 4 MiB copy takes. One job at a time; a caller that finds the pool busy (or in a forked child, where the threads do
+// not exist) copies on its own thread.
+class CopyPool {
+public:
+    static CopyPool &Get()
+    {
+        static CopyPool *pool = new CopyPool();  // never destroyed: its threads may outlive static destruction order
+        return *pool;
+    }
+    unsigned Width() const { return helpers_ + 1; }
+    // Runs fn(0..parts-1) on the helpers and the caller. False: nothing ran (pool busy or unusable), the caller does the work.
+    bool Run(unsigned parts, const std::function<void(unsigned)> &fn)
+    {
+        if (helpers_ == 0 || parts < 2 || ownerPid_ != getpid()) {
+            return false;
+        }
+        std::unique_lock<std::mutex> job(jobMu_, std::try_to_lock);
+        if (!job.owns_lock()) {
+            return false;
+        }
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            fn_ = &fn;
+            parts_ = parts;
+            next_.store(0);
+            pendingHelpers_ = helpers_;
+            generation_++;
+        }
+        cv_.notify_all();
+        Work();
+        std::unique_lock<std::mutex> lk(mu_);
+        doneCv_.wait(lk, [this]() { return pendingHelpers_ == 0; });
+        fn_ = nullptr;
+        return true;
+    }
+
+private:
+    CopyPool()
+    {
+        unsigned hw = std::thread::hardware_concurrency();
+        helpers_ = hw >= 4 ? std::min(3u, hw / 2 - 1) : 0;
+        ownerPid_ = getpid();
+        for (unsigned i = 0; i < helpers_; i++) {
+            std::thread([this]() { HelperLoop(); }).detach();
+        }
+    }
+    void Work()
+    {
+        for (unsigned i = next_.fetch_add(1); i < parts_; i = next_.fetch_add(1)) {
+            (*fn_)(i);
+        }
+    }
+    void HelperLoop()
+    {
+        uint64_t seen = 0;
+        std::unique_lock<std::mutex> lk(mu_);
+        while (true) {
+            cv_.wait(lk, [&]() { return generation_ != seen; });
+            seen = generation_;
+            lk.unlock();
+            Work();
+            lk.lock();
+            if (--pendingHelpers_ == 0) {
+                doneCv_.notify_one();
+            }
+        }
+    }
+    std::mutex jobMu_, mu_;
+    std::condition_variable cv_, doneCv_;
+    const std::function<void(unsigned)> *fn_{nullptr};
+    unsigned parts_{0}, helpers_{0}, pendingHelpers_{0};
+    std::atomic<unsigned> next_{0};
+    uint64_t generation_{0};
+    pid_t ownerPid_{0};
+};
+
 void ParallelMemcpy(void *dst, const void *src, size_t n)
 {
-    constexpr size_t kParallelMin = 16ull << 20;
-    if (n < kParallelMin) {
-        std::memcpy(dst, src, n);
-        return;
-    }
-    unsigned hw = std::thread::hardware_concurrency();
-    unsigned parts = std::min<unsigned>(hw > 1 ? hw / 2 : 1, 4);
-    if (parts <= 1) {
-        std::memcpy(dst, src, n);
-        return;
-    }
-    size_t share = (n / parts + 4095) & ~(size_t)4095;
-    std::vector<std::thread> ts;
-    for (unsigned i = 1; i < parts; i++) {
-        size_t off = share * i;
-        if (off >= n) {
-            break;
+    constexpr size_t kParallelMin = 2ull << 20, kPiece = 512ull << 10;
+    if (n >= kParallelMin) {
+        const unsigned parts = (unsigned)((n + kPiece - 1) / kPiece);
+        if (CopyPool::Get().Run(parts, [&](unsigned i) {
+                const size_t off = (size_t)i * kPiece;
+                std::memcpy((char *)dst + off, (const char *)src + off, std::min(kPiece, n - off));
+            })) {
+            return;
         }
-        size_t len = std::min(share, n - off);
-        ts.emplace_back([=]() { std::memcpy((char *)dst + off, (const char *)src + off, len); });
     }
-    std::memcpy(dst, src, std::min(share, n));
-    for (auto &t : ts) {
-        t.join();
-    }
+    std::memcpy(dst, src, n);
 }
 
 class CpuDataOp : public DataOperator {
@@ -449,6 +516,15 @@ public:
     {
         if (!Supports(dir, opt)) {
             return BM_NOT_SUPPORTED;
+        }
+        // Many small elements: spread the elements over the pool; few large ones: spread each of them.
+        uint64_t total = 0;
+        for (uint32_t i = 0; i < p.batchSize; i++) {
+            total += p.dataSizes[i];
+        }
+        if (p.batchSize >= 8 && total >= (4ull << 20) &&
+            CopyPool::Get().Run(p.batchSize, [&](unsigned i) { std::memcpy(p.destinations[i], p.sources[i], p.dataSizes[i]); })) {
+            return BM_OK;
         }
         for (uint32_t i = 0; i < p.batchSize; i++) {
             ParallelMemcpy(p.destinations[i], p.sources[i], p.dataSizes[i]);

@@ -123,6 +123,60 @@ def test_two_cpu_ranks_all_sizes_and_batch():
     assert res == [(0, "ok"), (1, "ok")], res
 
 
+def _large_copy_worker(rank, port, bar, q):
+    try:
+        import threading
+
+        import memfabric_hybrid_b200 as mf
+
+        b = _open(mf, rank, 1, port)
+        T, H = mf.bm.BmCopyType, mf.bm.BmMemType.HOST
+        g = b.peer_rank_ptr(H, 0)
+        # sizes around the piece and threshold boundaries of the pooled copy (2 MiB threshold, 512 KiB pieces)
+        for i, n in enumerate([2 * MiB - 1, 2 * MiB, 2 * MiB + 1, 5 * MiB + 123, 16 * MiB + 4097]):
+            data = _seeded(n, 50 + i)
+            assert b.copy_data(data.ctypes.data, g + 64, n, T.H2GH, 0) == 0, mf.get_last_err_msg()
+            out = np.zeros(n, dtype=np.uint8)
+            assert b.copy_data(g + 64, out.ctypes.data, n, T.GH2H, 0) == 0
+            assert (out == data).all(), f"size {n}"
+        # a batch that is spread over the helper threads: 12 elements of different sizes, 6 MiB in all
+        sizes = [(256 + 64 * k) << 10 for k in range(12)]
+        blocks = [_seeded(n, 70 + k) for k, n in enumerate(sizes)]
+        offs = np.cumsum([0] + sizes[:-1]).tolist()
+        assert b.copy_data_batch([x.ctypes.data for x in blocks], [g + int(o) for o in offs], sizes, len(sizes), T.H2GH, 0) == 0
+        mine = mf.native.host_read(g, int(offs[-1]) + sizes[-1])
+        for k, n in enumerate(sizes):
+            assert bytes(mine[int(offs[k]):int(offs[k]) + n]) == blocks[k].tobytes(), f"batch element {k}"
+        # two threads copy at once: one gets the helpers, the other copies on its own thread; both must be exact
+        srcs = [_seeded(8 * MiB, 90 + t) for t in range(2)]
+        errs = []
+
+        def run(t):
+            for _ in range(5):
+                if b.copy_data(srcs[t].ctypes.data, g + t * 16 * MiB, 8 * MiB, T.H2GH, 0) != 0:
+                    errs.append(t)
+
+        ths = [threading.Thread(target=run, args=(t,)) for t in range(2)]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        assert not errs
+        for t in range(2):
+            assert bytes(mf.native.host_read(g + t * 16 * MiB, 8 * MiB)) == srcs[t].tobytes()
+        q.put((rank, "ok"))
+    except Exception as ex:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(ex)))
+
+
+def test_large_host_copies_through_the_helper_threads():
+    ps, q, _bar = _spawn(_large_copy_worker, 1)
+    res = [q.get(timeout=300) for _ in ps]
+    [p.join(30) for p in ps]
+    assert res == [(0, "ok")], res
+
+
 def _churn_worker(rank, port, bar, q):
     try:
         import memfabric_hybrid_b200 as mf
