@@ -170,6 +170,50 @@ def _large_copy_worker(rank, port, bar, q):
         q.put((rank, repr(ex)))
 
 
+def _fork_after_pool_worker(rank, port, bar, q):
+    try:
+        import warnings
+
+        import memfabric_hybrid_b200 as mf
+
+        b = _open(mf, rank, 1, port)
+        T, H = mf.bm.BmCopyType, mf.bm.BmMemType.HOST
+        g = b.peer_rank_ptr(H, 0)
+        src = _seeded(8 * MiB, 5)
+        assert b.copy_data(src.ctypes.data, g, 8 * MiB, T.H2GH, 0) == 0  # the helper threads exist from here on
+        warnings.simplefilter("ignore", DeprecationWarning)
+        pid = os.fork()
+        if pid == 0:  # the child has no helper threads: it must copy on its own thread, not wait for them
+            out = np.zeros(8 * MiB, dtype=np.uint8)
+            rc = b.copy_data(g, out.ctypes.data, 8 * MiB, T.GH2H, 0)
+            os._exit(0 if rc == 0 and (out == src).all() else 3)
+        deadline = time.time() + 30
+        status = None
+        while time.time() < deadline:
+            r, st = os.waitpid(pid, os.WNOHANG)
+            if r == pid:
+                status = os.WEXITSTATUS(st) if os.WIFEXITED(st) else -1
+                break
+            time.sleep(0.05)
+        if status is None:
+            os.kill(pid, 9)
+            os.waitpid(pid, 0)
+        assert status == 0, f"forked child: {status}"
+        q.put((rank, "ok"))
+    except Exception as ex:  # pragma: no cover
+        import traceback
+
+        traceback.print_exc()
+        q.put((rank, repr(ex)))
+
+
+def test_forked_child_copies_without_the_helper_threads():
+    ps, q, _bar = _spawn(_fork_after_pool_worker, 1)
+    res = [q.get(timeout=120) for _ in ps]
+    [p.join(30) for p in ps]
+    assert res == [(0, "ok")], res
+
+
 def test_large_host_copies_through_the_helper_threads():
     ps, q, _bar = _spawn(_large_copy_worker, 1)
     res = [q.get(timeout=300) for _ in ps]
